@@ -1,0 +1,187 @@
+/*
+ * libzmoe -- C ABI of the B200 (sm_100a) MoE decode hot path.
+ *
+ * Every entry point replaces one piece of the reference (ZMLX v0.8.5 on MLX);
+ * the reference interface each one stands in for is cited as file:line
+ * relative to the ZMLX tree ("patch:" = integrations/mlx_local_integration/
+ * gather_qmm_swiglu.patch, "moe.py" = src/zmlx/kernels/moe.py).
+ *
+ * Conventions (modelled on the reference's only C ABI, zig/shim/shim.h:48-127):
+ *   - plain pointers and sizes; all data pointers are DEVICE pointers owned by
+ *     the caller; the library allocates no user-visible memory;
+ *   - every call takes a cudaStream_t (passed as void*), only enqueues work and
+ *     returns; nothing synchronises the device;
+ *   - return value: 0 on success, a negative ZMOE_ERR_* otherwise; no call
+ *     throws, exits or traps the device; zmoe_last_error() gives the message
+ *     of the calling thread's last failure;
+ *   - dtype T is bfloat16 (16-bit pattern); packed 4-bit tensors are uint32
+ *     with code i of a row in word i/8 at bit 4*(i%8)
+ *     (src/zmlx/kernels/quant.py:109-120); affine scales/biases are T, shaped
+ *     (E, N, K/group_size); mxfp4 scales are e8m0 bytes shaped (E, N, K/32).
+ */
+#ifndef ZMOE_H_
+#define ZMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZMOE_ABI_VERSION 1
+
+enum zmoe_status {
+  ZMOE_OK = 0,
+  ZMOE_ERR_SHAPE = -1,
+  ZMOE_ERR_DTYPE = -2,
+  ZMOE_ERR_ALIGN = -3,
+  ZMOE_ERR_UNSUPPORTED = -4,
+  ZMOE_ERR_CUDA = -5,
+  ZMOE_ERR_TIMEOUT = -6,
+  ZMOE_ERR_WORKSPACE = -7
+};
+
+enum zmoe_dtype { ZMOE_F32 = 0, ZMOE_BF16 = 1 };
+
+/* Quantisation modes of the expert weights. */
+enum zmoe_qmode {
+  ZMOE_Q_AFFINE4 = 0, /* MLX affine 4-bit, w = q*scale + bias per group */
+  ZMOE_Q_MXFP4 = 1    /* e2m1 codes, one e8m0 scale per 32 along K      */
+};
+
+/* Rounding contract of the SwiGLU epilogue. */
+enum zmoe_swiglu_mode {
+  ZMOE_SWIGLU_CPU = 0,   /* gate, up rounded to T; g*1/(1+exp(-g))*u in float; one rounding (patch:47-55) */
+  ZMOE_SWIGLU_PER_OP = 1 /* every elementwise op rounded to T, sigmoid as 1/(1+exp|g|) (src/zmlx/msl.py:20-24,
+                            src/zmlx/kernels/transformer.py:882-897) */
+};
+
+/* Rounding contract of the weighted combine (slots summed in order 0..K-1). */
+enum zmoe_combine_mode {
+  ZMOE_COMBINE_FP32 = 0,        /* moe_combine_fp32          moe.py:1020-1026 : float acc (fma), float out   */
+  ZMOE_COMBINE_FP32_NO_FMA = 1, /* moe_combine_fp32_no_fma   moe.py:1075-1095 : product rounded, float out   */
+  ZMOE_COMBINE_T = 2,           /* moe_combine               moe.py:840-846   : float acc (fma), T out       */
+  ZMOE_COMBINE_NO_FMA = 3,      /* moe_combine_no_fma        moe.py:899-912   : product rounded, T out       */
+  ZMOE_COMBINE_EXACT = 4,       /* moe_combine_exact         moe.py:963-970   : product and sum rounded to T */
+  ZMOE_COMBINE_STREAM_T = 5     /* _weighted_accumulate_kernel moe.py:1821-1841: acc = T(float(acc) + w*v)   */
+};
+
+/* Router flavours of zmoe_router_softmax_topk. */
+enum zmoe_softmax_router {
+  ZMOE_ROUTER_TOPK_THEN_SOFTMAX = 0, /* top-k of logits, softmax over the k   moe.py:1287-1315, 1380-1386 */
+  ZMOE_ROUTER_SOFTMAX_THEN_TOPK = 1  /* full softmax [+bias], top-k, optional renorm   moe.py:1326-1396;
+                                        Qwen3: src/zmlx/patch/patterns/moe_mlp.py:260-266 */
+};
+
+int zmoe_abi_version(void);
+
+/* Message of this thread's last failing call ("" if none). Never NULL. */
+const char* zmoe_last_error(void);
+
+/* ------------------------------------------------------------------ routers */
+
+/*
+ * topk_gating_softmax / Qwen3 gating / GPT-OSS gating.
+ * Replaces: moe.py:1239-1396 (topk_gating_softmax), moe.py:1448-1490
+ * (router_argpartition_logits_topk), moe_mlp.py:226-274.
+ * logits (T, E) of logits_dtype; bias (E) float or NULL; renorm: 0 none, 1 divide
+ * by (sum + 1e-20) (moe.py:196), 2 divide by sum (moe_mlp.py:265).
+ * Outputs: weights (T, K) float, indices (T, K) uint32, slot order = score
+ * descending, ties to the lower expert id.  E <= 1024, K <= 16.
+ */
+int zmoe_router_softmax_topk(const void* logits, int logits_dtype, int T, int E, int K, int flavour,
+                             const float* bias, int renorm, float* weights, uint32_t* indices, void* stream);
+
+/*
+ * deepseek_router_topk_sigmoid (+ the routed_scaling_factor multiply of the gate).
+ * Replaces: moe.py:1745-1817 (kernel moe.py:1502-1679) and
+ * src/zmlx/patch/patterns/deepseek_router.py:108-120.
+ * score = sigmoid(l) + bias; with n_group > 1 a group's score is the sum of its two
+ * largest scores, the best topk_group groups are kept (ties to the lower group) and
+ * the others are scored 0.0; weights = sigmoid(l)[sel] / sum, then * scale.
+ */
+int zmoe_router_sigmoid_bias_topk(const void* logits, int logits_dtype, int T, int E, int K, const float* bias,
+                                  int n_group, int topk_group, float scale, float* weights, uint32_t* indices,
+                                  void* stream);
+
+/*
+ * Router linear: logits[t, e] = T( sum_k x[t,k] * Wr[e,k] ), x (T, d) T, Wr (E, d) T.
+ * Replaces the model's gate matmul (deepseek_router.py:107, `x @ weight.T`) on the
+ * fused-layer path.  out_dtype selects T or float logits.
+ */
+int zmoe_router_logits(const void* x, const void* wr, int T, int E, int d, void* logits, int out_dtype,
+                       void* stream);
+
+/* --------------------------------------------------- token-sorted expert plan */
+
+/*
+ * The gather ops take (lhs, rhs) index pairs (patch:754-781).  A "plan" groups the
+ * pairs by expert so that each expert's weights are streamed once for all of its
+ * rows.  Pair p, row m reads x row lhs[p]*M + m, uses expert rhs[p] and writes
+ * output row p*M + m.  lhs == NULL means lhs[p] = p / lhs_div (lhs_div >= 1).
+ * plan must hold zmoe_plan_bytes(P*M, E) bytes.  No reference counterpart: MLX
+ * re-reads an expert per row (patch:576).
+ */
+size_t zmoe_plan_bytes(int rows, int E);
+int zmoe_build_plan(const int32_t* lhs, int lhs_div, const int32_t* rhs, int P, int M, int E, void* plan,
+                    size_t plan_bytes, void* stream);
+
+/* ------------------------------------------------------------ expert matmuls */
+
+/*
+ * mx.gather_qmm_swiglu: out[r, :] = swiglu(x_r @ Wg[e_r].T, x_r @ Wu[e_r].T).
+ * Replaces: python binding patch:995-1013, op patch:695-800, Metal kernel
+ * patch:329-510, CPU eval patch:64-192; wrapper src/zmlx/kernels/fused_moe.py:39-106.
+ * x (x_rows, K) T with row stride ldx; weights (E, N, K/8) uint32; out (rows, N) T.
+ * biases are ignored for ZMOE_Q_MXFP4.  rows_hint is an upper bound on the rows of
+ * any one expert (e.g. the token count for top-k routing); it sizes shared memory.
+ * K % 64 == 0 (affine: K % group_size == 0, group_size == 64).
+ */
+int zmoe_gather_qmm_swiglu(const void* x, int x_rows, int ldx, const uint32_t* gate_w, const void* gate_scales,
+                           const void* gate_biases, const uint32_t* up_w, const void* up_scales,
+                           const void* up_biases, int E, int N, int K, int group_size, int qmode,
+                           const void* plan, int rows, int rows_hint, void* out, int swiglu_mode, void* stream);
+
+/*
+ * mx.gather_qmm(transpose=True): out[r, :] = T(x_r @ W[e_r].T).
+ * Replaces the third-party op at its call sites moe.py:1219-1229, 2147-2157 and
+ * moe_mlp.py:571-574 (switch_mlp.down_proj).  With x_by_output_row != 0 output row r
+ * reads x row r (the down projection after gather_qmm_swiglu, whose output rows are
+ * already one per pair) instead of the plan's lhs row.
+ */
+int zmoe_gather_qmm(const void* x, int x_rows, int ldx, const uint32_t* w, const void* scales, const void* biases,
+                    int E, int N, int K, int group_size, int qmode, const void* plan, int rows, int rows_hint,
+                    int x_by_output_row, void* out, void* stream);
+
+/* ------------------------------------------------------------------- combine */
+
+/*
+ * out[t, d] = sum_i w[t, i] * y[t, i, d] under one of the reference's five rounding
+ * contracts (+ the streaming one).  Replaces moe.py:859-1127 and the accumulate
+ * kernels moe.py:1821-1921; `post_scale` != 1 is unused by the reference (pass 1).
+ * y (T, K, D) of y_dtype; w (T, K) of w_dtype; out (T, D): float for the FP32
+ * modes, T otherwise.  residual (T, D) T or NULL is added after the combine and the
+ * sum rounded to T (the `y + shared_experts(x)` of moe_mlp.py:1059-1061); it needs a
+ * T-output mode, or an FP32 mode with out_t bit 0 set (cast to T first, moe_mlp.py:1002).
+ * out_t bit 1: round the weights to T before use (`weights.astype(x.dtype)`,
+ * moe_mlp.py:288).
+ */
+int zmoe_moe_combine(const void* y, int y_dtype, const void* w, int w_dtype, int T, int K, int D, int mode,
+                     void* out, int out_t, const void* residual, void* stream);
+
+/*
+ * gather_qmm_combine_quantized: out[t] = sum_k gate[t,k] * T(act[t,k] @ W[idx[t,k]].T).
+ * Replaces moe.py:2043-2174 (and the K-vectorised form moe.py:1198-1236).
+ * act (T*K, Kin) T; plan built over rhs = idx (T*K pairs, lhs = identity);
+ * scratch must hold T*K*N T values.
+ */
+int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w, const void* scales, const void* biases,
+                            int E, int N, int Kin, int group_size, int qmode, const void* plan, int T, int K,
+                            const void* gate, int gate_dtype, int mode, void* scratch, void* out, int out_t,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZMOE_H_ */

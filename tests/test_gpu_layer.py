@@ -1,0 +1,98 @@
+"""GPU parity: whole MoE block (router -> gate/up + SwiGLU -> down -> combine [+ shared expert])
+at the benchmark configurations' shapes, against the oracle's per-family recipe."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fast as F
+from oracle import semantics as S
+from tests.helpers import assert_close_rel, t2n
+from zmlx_b200 import synthetic
+from zmlx_b200.layer import MoELayer
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+_LAYERS: dict = {}
+
+
+def _layer(name):
+    if name not in _LAYERS:
+        cfg = synthetic.CONFIGS[name]
+        _LAYERS[name] = (cfg, synthetic.make_layer(cfg, device=DEV))
+    return _LAYERS[name]
+
+
+def _subset(params, experts):
+    """Copy only the selected experts to the host (the oracle touches nothing else)."""
+    sel = torch.as_tensor(experts, device=DEV, dtype=torch.int64)
+    out = {}
+    for k in ("gate", "up", "down"):
+        out[f"{k}_w"] = t2n(params[f"{k}_w"].view(torch.int32)[sel]).view(np.uint32)
+        out[f"{k}_s"] = t2n(params[f"{k}_s"][sel])
+        out[f"{k}_b"] = None if params[f"{k}_b"] is None else t2n(params[f"{k}_b"][sel])
+    return out
+
+
+def _oracle_layer(cfg, params, x, logits, idx_gpu):
+    """The oracle's recipe with the compiled matmuls; routing is recomputed by the oracle from the
+    kernel's own bf16 logits and must match the kernel's indices exactly."""
+    xn, ln = t2n(x), t2n(logits)
+    bias = None if params["expert_bias"] is None else t2n(params["expert_bias"])
+    if cfg.family == "generic":
+        w, idx = S.topk_gating_softmax(ln, cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
+        w = S.bf16(w)
+        cmode = "t"
+    elif cfg.family == "qwen3":
+        idx, w = S.qwen3_gating(ln, cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
+        cmode = "no_fma"
+    else:
+        w, idx = S.deepseek_router_topk_sigmoid(ln, bias, k=cfg.top_k, n_group=cfg.n_group,
+                                                topk_group=cfg.topk_group)
+        w = (w * np.float32(cfg.routed_scaling_factor)).astype(np.float32)
+        cmode = "fp32_no_fma" if cfg.family == "glm" else "t"
+    np.testing.assert_array_equal(t2n(idx_gpu).view(np.uint32), idx)  # expert indices bit-exact
+    experts = np.unique(idx)
+    remap = np.searchsorted(experts, idx).astype(np.int32)
+    sub = _subset(params, experts)
+    gs = 32 if cfg.mode == "mxfp4" else cfg.group_size
+    y, _ = F.experts_forward(xn, remap, sub, group_size=gs, mode=cfg.mode,
+                             swiglu="cpu" if cfg.mode == "affine" else "per_op")
+    out = S.moe_combine(y, w, mode=cmode)
+    if cmode == "fp32_no_fma":
+        out = S.bf16(out)
+    if cfg.n_shared:
+        sh = {}
+        for k, v in params["shared"].items():
+            if v is None:
+                sh[k] = None
+            elif k.endswith("_w"):
+                sh[k] = t2n(v.view(torch.int32)).view(np.uint32)[0]
+            else:
+                sh[k] = t2n(v)[0]
+        out = S.bf16(out + S.shared_expert_mlp(xn, sh, group_size=gs, mode=cfg.mode))
+    return out, w
+
+
+@pytest.mark.parametrize("name,T", [("c1", 1), ("c1", 5), ("c2", 1), ("c2", 4), ("c2", 16), ("c2", 64),
+                                    ("c5", 1), ("c5", 9)])
+def test_layer_matches_oracle(name, T):
+    cfg, params = _layer(name)
+    layer = MoELayer(cfg, params, max_tokens=64)
+    x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
+    out = layer(x).clone()
+    ref, w_ref = _oracle_layer(cfg, params, x, layer.logits[:T], layer.indices[:T])
+    np.testing.assert_allclose(t2n(layer.weights[:T]), w_ref, rtol=5e-6, atol=1e-7)
+    assert_close_rel(t2n(out), ref, 2e-2, f"{name} T={T}")
+    # a second pass over the same tokens is bit-identical
+    assert torch.equal(layer(x), out)
+
+
+def test_router_logits_match_a_float64_matmul():
+    cfg, params = _layer("c2")
+    layer = MoELayer(cfg, params, max_tokens=16)
+    x = synthetic.make_tokens(cfg, 16, device="cpu").to(DEV)
+    layer(x)
+    ref = (x.double() @ params["router_w"].double().T).cpu().numpy()
+    got = t2n(layer.logits[:16])
+    assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6

@@ -1,0 +1,340 @@
+// Router kernels: router linear, softmax-family top-k, sigmoid+bias top-k with
+// group-limited selection.  One warp owns one token row; the row's E scores live
+// in registers (E <= 1024), top-k runs as K rounds of a warp arg-max whose order
+// is (score descending, expert id ascending).
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace zmoe {
+
+constexpr int kMaxVPL = 32;  // values per lane: E <= 1024
+constexpr int kMaxK = 16;
+
+__device__ __forceinline__ float load_logit(const void* p, int dtype, size_t i) {
+  if (dtype == ZMOE_F32) return reinterpret_cast<const float*>(p)[i];
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// K rounds of arg-max over the lane-strided values v[j] (expert id = lane + 32*j);
+// all lanes end with the same winners in sel_val/sel_idx.  A lane keeps a bit
+// mask of the ids it has given away, so that genuine -inf scores cannot be
+// confused with retired entries.
+template <int VPL>
+__device__ __forceinline__ void warp_topk_masked(float (&v)[VPL], int E, int K, int lane, float* sel_val,
+                                                 int* sel_idx) {
+  uint32_t taken = 0;
+  for (int r = 0; r < K; ++r) {
+    float best = -CUDART_INF_F;
+    int bidx = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      int idx = lane + 32 * j;
+      bool avail = idx < E && !((taken >> j) & 1u);
+      if (avail && (bidx == 0x7fffffff || v[j] > best)) {
+        best = v[j];
+        bidx = idx;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+      bool other_valid = oi != 0x7fffffff;
+      bool mine_valid = bidx != 0x7fffffff;
+      if (other_valid && (!mine_valid || ov > best || (ov == best && oi < bidx))) {
+        best = ov;
+        bidx = oi;
+      }
+    }
+    sel_val[r] = best;
+    sel_idx[r] = bidx;
+    if (bidx != 0x7fffffff && (bidx & 31) == lane) taken |= 1u << (bidx >> 5);
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
+                                                           int K, int flavour, const float* __restrict__ bias,
+                                                           int renorm, float* __restrict__ weights,
+                                                           uint32_t* __restrict__ indices) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= T) return;
+  float v[VPL];
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int idx = lane + 32 * j;
+    v[j] = (idx < E) ? load_logit(logits, dtype, (size_t)row * E + idx) : -CUDART_INF_F;
+    mx = fmaxf(mx, v[j]);
+  }
+  float sel_val[kMaxK];
+  int sel_idx[kMaxK];
+  if (flavour == ZMOE_ROUTER_TOPK_THEN_SOFTMAX) {
+    warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+    if (lane == 0) {
+      float m = sel_val[0];
+      float s = 0.0f;
+      for (int i = 0; i < K; ++i) s += expf(sel_val[i] - m);
+      for (int i = 0; i < K; ++i) {
+        weights[(size_t)row * K + i] = expf(sel_val[i] - m) / s;
+        indices[(size_t)row * K + i] = (uint32_t)sel_idx[i];
+      }
+    }
+    return;
+  }
+  // full softmax [+ bias] -> top-k -> optional renormalisation
+  mx = warp_max(mx);
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int idx = lane + 32 * j;
+    v[j] = (idx < E) ? expf(v[j] - mx) : 0.0f;
+    sum += v[j];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int idx = lane + 32 * j;
+    if (idx < E) {
+      v[j] = v[j] / sum;
+      if (bias) v[j] += bias[idx];
+    }
+  }
+  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+  if (lane == 0) {
+    float denom = 1.0f;
+    if (renorm) {
+      float sk = 0.0f;
+      for (int i = 0; i < K; ++i) sk += sel_val[i];
+      denom = (renorm == 1) ? sk + 1e-20f : sk;
+    }
+    for (int i = 0; i < K; ++i) {
+      weights[(size_t)row * K + i] = renorm ? sel_val[i] / denom : sel_val[i];
+      indices[(size_t)row * K + i] = (uint32_t)sel_idx[i];
+    }
+  }
+}
+
+// sigmoid + selection bias, optional group-limited selection.  Per-warp shared
+// scratch holds the E scores so that one lane per group can scan its group.
+template <int VPL>
+__global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
+                                                           int K, const float* __restrict__ bias, int n_group,
+                                                           int topk_group, float scale, float* __restrict__ weights,
+                                                           uint32_t* __restrict__ indices) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + wid;
+  float* sc = sm + (size_t)wid * (E + 64);  // E scores, then 32 group scores, then 32 keep flags
+  float* gsc = sc + E;
+  float* gkeep = gsc + 32;
+  if (row >= T) return;
+  float v[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int idx = lane + 32 * j;
+    if (idx < E) {
+      float aff = sigmoid_stable(load_logit(logits, dtype, (size_t)row * E + idx));
+      v[j] = aff + bias[idx];
+      sc[idx] = v[j];
+    } else {
+      v[j] = -CUDART_INF_F;
+    }
+  }
+  if (n_group > 1) {
+    __syncwarp();
+    const int per = E / n_group;
+    for (int g0 = 0; g0 < n_group; g0 += 32) {
+      // this build keeps n_group <= 32 (validated on the host); loop kept for clarity
+      int g = g0 + lane;
+      if (g < n_group) {
+        float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+        for (int j = 0; j < per; ++j) {
+          float x = sc[g * per + j];
+          if (x > t1) {
+            t2 = t1;
+            t1 = x;
+          } else if (x > t2) {
+            t2 = x;
+          }
+        }
+        gsc[g] = t1 + t2;
+      }
+    }
+    __syncwarp();
+    if (lane < n_group) {
+      float mine = gsc[lane];
+      int rank = 0;
+      for (int h = 0; h < n_group; ++h) {
+        float o = gsc[h];
+        rank += (o > mine) || (o == mine && h < lane);
+      }
+      gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      int idx = lane + 32 * j;
+      if (idx < E && gkeep[idx / per] == 0.0f) v[j] = 0.0f;
+    }
+  }
+  float sel_val[kMaxK];
+  int sel_idx[kMaxK];
+  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+  if (lane == 0) {
+    float aff[kMaxK];
+    float sum = 0.0f;
+    for (int i = 0; i < K; ++i) {
+      aff[i] = sigmoid_stable(load_logit(logits, dtype, (size_t)row * E + sel_idx[i]));
+      sum += aff[i];
+    }
+    float inv = 1.0f / sum;
+    for (int i = 0; i < K; ++i) {
+      float w = aff[i] * inv;
+      if (scale != 1.0f) w = w * scale;
+      weights[(size_t)row * K + i] = w;
+      indices[(size_t)row * K + i] = (uint32_t)sel_idx[i];
+    }
+  }
+}
+
+// Router linear.  One warp per (expert, token tile of 8): 16-byte loads of the
+// expert's weight row, the token rows come from L1/L2.
+__global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ wr, int T, int E,
+                                                            int d, void* __restrict__ logits, int out_dtype) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  const int t0 = blockIdx.y * 8;
+  float acc[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
+  const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * d);
+  const int nvec = d >> 3;
+  for (int i = lane; i < nvec; i += 32) {
+    uint4 wv = __ldg(wrow + i);
+    float wf[8];
+    wf[0] = bf16_bits_to_float(wv.x & 0xffffu);
+    wf[1] = bf16_bits_to_float(wv.x >> 16);
+    wf[2] = bf16_bits_to_float(wv.y & 0xffffu);
+    wf[3] = bf16_bits_to_float(wv.y >> 16);
+    wf[4] = bf16_bits_to_float(wv.z & 0xffffu);
+    wf[5] = bf16_bits_to_float(wv.z >> 16);
+    wf[6] = bf16_bits_to_float(wv.w & 0xffffu);
+    wf[7] = bf16_bits_to_float(wv.w >> 16);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      if (t0 + t < T) {
+        uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + t) * d) + i);
+        acc[t] = fmaf(wf[0], bf16_bits_to_float(xv.x & 0xffffu), acc[t]);
+        acc[t] = fmaf(wf[1], bf16_bits_to_float(xv.x >> 16), acc[t]);
+        acc[t] = fmaf(wf[2], bf16_bits_to_float(xv.y & 0xffffu), acc[t]);
+        acc[t] = fmaf(wf[3], bf16_bits_to_float(xv.y >> 16), acc[t]);
+        acc[t] = fmaf(wf[4], bf16_bits_to_float(xv.z & 0xffffu), acc[t]);
+        acc[t] = fmaf(wf[5], bf16_bits_to_float(xv.z >> 16), acc[t]);
+        acc[t] = fmaf(wf[6], bf16_bits_to_float(xv.w & 0xffffu), acc[t]);
+        acc[t] = fmaf(wf[7], bf16_bits_to_float(xv.w >> 16), acc[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    float s = warp_sum(acc[t]);
+    if (lane == 0 && t0 + t < T) {
+      size_t o = (size_t)(t0 + t) * E + e;
+      if (out_dtype == ZMOE_F32)
+        reinterpret_cast<float*>(logits)[o] = s;
+      else
+        reinterpret_cast<__nv_bfloat16*>(logits)[o] = __float2bfloat16_rn(s);
+    }
+  }
+}
+
+template <typename F>
+static int dispatch_vpl(int E, F&& f) {
+  if (E <= 128) return f(std::integral_constant<int, 4>{});
+  if (E <= 256) return f(std::integral_constant<int, 8>{});
+  if (E <= 512) return f(std::integral_constant<int, 16>{});
+  return f(std::integral_constant<int, 32>{});
+}
+
+}  // namespace zmoe
+
+using namespace zmoe;
+
+extern "C" {
+
+int zmoe_router_softmax_topk(const void* logits, int logits_dtype, int T, int E, int K, int flavour,
+                             const float* bias, int renorm, float* weights, uint32_t* indices, void* stream) {
+  ZMOE_REQUIRE(logits && weights && indices, ZMOE_ERR_SHAPE, "zmoe_router_softmax_topk: null pointer");
+  ZMOE_REQUIRE(T >= 0 && E >= 1 && K >= 1, ZMOE_ERR_SHAPE, "zmoe_router_softmax_topk: bad sizes T=%d E=%d K=%d", T,
+               E, K);
+  ZMOE_REQUIRE(K <= E, ZMOE_ERR_SHAPE, "zmoe_router_softmax_topk: k=%d exceeds last dimension D=%d", K, E);
+  ZMOE_REQUIRE(E <= 32 * kMaxVPL && K <= kMaxK, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_router_softmax_topk: E=%d (max %d) or K=%d (max %d) unsupported", E, 32 * kMaxVPL, K, kMaxK);
+  ZMOE_REQUIRE(logits_dtype == ZMOE_F32 || logits_dtype == ZMOE_BF16, ZMOE_ERR_DTYPE,
+               "zmoe_router_softmax_topk: logits dtype %d", logits_dtype);
+  ZMOE_REQUIRE(flavour == ZMOE_ROUTER_TOPK_THEN_SOFTMAX || flavour == ZMOE_ROUTER_SOFTMAX_THEN_TOPK,
+               ZMOE_ERR_UNSUPPORTED, "zmoe_router_softmax_topk: flavour %d", flavour);
+  ZMOE_REQUIRE(!(flavour == ZMOE_ROUTER_TOPK_THEN_SOFTMAX && bias), ZMOE_ERR_UNSUPPORTED,
+               "zmoe_router_softmax_topk: bias needs the softmax-then-top-k flavour");
+  if (T == 0) return ZMOE_OK;
+  dim3 grid((T + 3) / 4), block(128);
+  cudaStream_t st = (cudaStream_t)stream;
+  dispatch_vpl(E, [&](auto vpl) {
+    softmax_topk_kernel<decltype(vpl)::value>
+        <<<grid, block, 0, st>>>(logits, logits_dtype, T, E, K, flavour, bias, renorm, weights, indices);
+    return 0;
+  });
+  return check_launch("zmoe_router_softmax_topk");
+}
+
+int zmoe_router_sigmoid_bias_topk(const void* logits, int logits_dtype, int T, int E, int K, const float* bias,
+                                  int n_group, int topk_group, float scale, float* weights, uint32_t* indices,
+                                  void* stream) {
+  ZMOE_REQUIRE(logits && bias && weights && indices, ZMOE_ERR_SHAPE, "zmoe_router_sigmoid_bias_topk: null pointer");
+  ZMOE_REQUIRE(T >= 0 && E >= 1, ZMOE_ERR_SHAPE, "zmoe_router_sigmoid_bias_topk: bad sizes T=%d E=%d", T, E);
+  ZMOE_REQUIRE(K >= 1, ZMOE_ERR_SHAPE, "deepseek_router_topk_sigmoid: k must be > 0");
+  ZMOE_REQUIRE(K <= E, ZMOE_ERR_SHAPE, "deepseek_router_topk_sigmoid: k=%d exceeds D=%d", K, E);
+  ZMOE_REQUIRE(n_group >= 1, ZMOE_ERR_SHAPE, "deepseek_router_topk_sigmoid: n_group must be > 0");
+  ZMOE_REQUIRE(topk_group >= 1 && topk_group <= n_group, ZMOE_ERR_SHAPE,
+               "deepseek_router_topk_sigmoid: invalid topk_group");
+  ZMOE_REQUIRE(E % n_group == 0, ZMOE_ERR_SHAPE, "deepseek_router_topk_sigmoid: n_group must divide D");
+  ZMOE_REQUIRE(E <= 32 * kMaxVPL && K <= kMaxK && n_group <= 32, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_router_sigmoid_bias_topk: E=%d K=%d n_group=%d beyond limits (%d, %d, 32)", E, K, n_group,
+               32 * kMaxVPL, kMaxK);
+  ZMOE_REQUIRE(logits_dtype == ZMOE_F32 || logits_dtype == ZMOE_BF16, ZMOE_ERR_DTYPE,
+               "zmoe_router_sigmoid_bias_topk: logits dtype %d", logits_dtype);
+  if (T == 0) return ZMOE_OK;
+  dim3 grid((T + 3) / 4), block(128);
+  size_t smem = 4 * (size_t)(E + 64) * sizeof(float);
+  cudaStream_t st = (cudaStream_t)stream;
+  dispatch_vpl(E, [&](auto vpl) {
+    sigmoid_topk_kernel<decltype(vpl)::value><<<grid, block, smem, st>>>(logits, logits_dtype, T, E, K, bias, n_group,
+                                                                        topk_group, scale, weights, indices);
+    return 0;
+  });
+  return check_launch("zmoe_router_sigmoid_bias_topk");
+}
+
+int zmoe_router_logits(const void* x, const void* wr, int T, int E, int d, void* logits, int out_dtype,
+                       void* stream) {
+  ZMOE_REQUIRE(x && wr && logits, ZMOE_ERR_SHAPE, "zmoe_router_logits: null pointer");
+  ZMOE_REQUIRE(T >= 0 && E >= 1 && d >= 8, ZMOE_ERR_SHAPE, "zmoe_router_logits: bad sizes T=%d E=%d d=%d", T, E, d);
+  ZMOE_REQUIRE(d % 8 == 0, ZMOE_ERR_ALIGN, "zmoe_router_logits: d=%d must be a multiple of 8", d);
+  ZMOE_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)wr % 16 == 0), ZMOE_ERR_ALIGN,
+               "zmoe_router_logits: x and wr must be 16-byte aligned");
+  ZMOE_REQUIRE(out_dtype == ZMOE_F32 || out_dtype == ZMOE_BF16, ZMOE_ERR_DTYPE, "zmoe_router_logits: out dtype %d",
+               out_dtype);
+  if (T == 0) return ZMOE_OK;
+  dim3 grid((E + 3) / 4, (T + 7) / 8), block(128);
+  router_logits_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wr, T,
+                                                                 E, d, logits, out_dtype);
+  return check_launch("zmoe_router_logits");
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""One MoE block forward on the GPU: router -> gate/up + SwiGLU -> down -> combine.
+
+This is the order of the reference's patched block
+(src/zmlx/patch/patterns/moe_mlp.py:883-1063) with every step running in a
+libzmoe kernel.  ``MoELayer`` owns the packed tensors of one layer and
+preallocated work buffers for a fixed maximum token count, so that a forward
+pass allocates nothing and can be captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, ops
+from .synthetic import MoEConfig
+
+_FAMILY_COMBINE = {"generic": "t", "qwen3": "no_fma", "glm": "fp32_no_fma", "deepseek": "t"}
+
+
+class MoELayer:
+    """Packed weights of one MoE layer plus the buffers of its forward pass."""
+
+    def __init__(self, cfg: MoEConfig, params: dict, *, max_tokens: int = 64, combine: str | None = None,
+                 swiglu: str | None = None):
+        self.cfg = cfg
+        self.p = params
+        dev = params["gate_w"].device
+        if dev.type != "cuda":
+            raise RuntimeError("MoELayer needs its tensors on a CUDA device (there is no CPU path)")
+        self.device = dev
+        self.combine_name = combine or _FAMILY_COMBINE[cfg.family]
+        self.combine_mode = _lib.COMBINE_MODES[self.combine_name]
+        sw = swiglu or ("cpu" if cfg.mode == "affine" else "per_op")
+        self.swiglu = _lib.SWIGLU_CPU if sw == "cpu" else _lib.SWIGLU_PER_OP
+        self.gs = 32 if cfg.mode == "mxfp4" else cfg.group_size
+        self._alloc(max_tokens)
+
+    def _alloc(self, T: int) -> None:
+        cfg, dev = self.cfg, self.device
+        K = cfg.top_k
+        self.max_tokens = T
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        self.logits = torch.empty((T, cfg.n_experts), dtype=bf, device=dev)
+        self.weights = torch.empty((T, K), dtype=f32, device=dev)
+        self.indices = torch.empty((T, K), dtype=i32, device=dev)
+        self.plan = torch.empty(ops.plan_bytes(T * K, cfg.n_experts) // 4, dtype=i32, device=dev)
+        self.h = torch.empty((T * K, cfg.d_ff), dtype=bf, device=dev)
+        self.y = torch.empty((T * K, cfg.d_model), dtype=bf, device=dev)
+        self.out = torch.empty((T, cfg.d_model), dtype=bf, device=dev)
+        if cfg.n_shared:
+            self.zero_idx = torch.zeros((T,), dtype=i32, device=dev)
+            self.shared_plan = torch.empty(ops.plan_bytes(T, 1) // 4, dtype=i32, device=dev)
+            self.sh_h = torch.empty((T, cfg.d_ff * cfg.n_shared), dtype=bf, device=dev)
+            self.sh_y = torch.empty((T, cfg.d_model), dtype=bf, device=dev)
+
+    # -- steps -------------------------------------------------------------
+    def route(self, x: torch.Tensor):
+        """Router linear (bf16 logits) and the family's top-k; fills weights/indices."""
+        cfg = self.cfg
+        T = x.shape[0]
+        lib = _lib.load()
+        st = ops._stream()
+        p = ops._ptr
+        _lib.check(lib.zmoe_router_logits(p(x), p(self.p["router_w"]), T, cfg.n_experts, cfg.d_model,
+                                          p(self.logits), _lib.BF16, st))
+        if cfg.family == "generic":
+            norm = cfg.norm_topk_prob
+            bias = self.p.get("expert_bias")
+            if bias is None and norm:
+                rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
+                                                  _lib.ROUTER_TOPK_THEN_SOFTMAX, None, 0, p(self.weights),
+                                                  p(self.indices), st)
+            else:
+                rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
+                                                  _lib.ROUTER_SOFTMAX_THEN_TOPK, p(bias), 1 if norm else 0,
+                                                  p(self.weights), p(self.indices), st)
+        elif cfg.family == "qwen3":
+            rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
+                                              _lib.ROUTER_SOFTMAX_THEN_TOPK, None, 2 if cfg.norm_topk_prob else 0,
+                                              p(self.weights), p(self.indices), st)
+        else:
+            rc = lib.zmoe_router_sigmoid_bias_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
+                                                   p(self.p["expert_bias"]), cfg.n_group, cfg.topk_group,
+                                                   ctypes.c_float(cfg.routed_scaling_factor), p(self.weights),
+                                                   p(self.indices), st)
+        _lib.check(rc)
+
+    def experts(self, x: torch.Tensor):
+        """Plan, fused gate/up + SwiGLU, down projection for all (token, slot) pairs."""
+        cfg = self.cfg
+        T = x.shape[0]
+        K = cfg.top_k
+        lib = _lib.load()
+        st = ops._stream()
+        p = ops._ptr
+        qm = ops.qmode_code(cfg.mode)
+        W = self.p
+        _lib.check(lib.zmoe_build_plan(None, K, p(self.indices), T * K, 1, cfg.n_experts, p(self.plan),
+                                       self.plan.numel() * 4, st))
+        _lib.check(lib.zmoe_gather_qmm_swiglu(p(x), T, x.stride(0), p(W["gate_w"]), p(W["gate_s"]), p(W["gate_b"]),
+                                              p(W["up_w"]), p(W["up_s"]), p(W["up_b"]), cfg.n_experts, cfg.d_ff,
+                                              cfg.d_model, self.gs, qm, p(self.plan), T * K, T, p(self.h),
+                                              self.swiglu, st))
+        _lib.check(lib.zmoe_gather_qmm(p(self.h), T * K, cfg.d_ff, p(W["down_w"]), p(W["down_s"]), p(W["down_b"]),
+                                       cfg.n_experts, cfg.d_model, cfg.d_ff, self.gs, qm, p(self.plan), T * K, T, 1,
+                                       p(self.y), st))
+
+    def shared(self, x: torch.Tensor):
+        """The always-on shared expert: the same kernels with a one-expert bank."""
+        cfg = self.cfg
+        T = x.shape[0]
+        lib = _lib.load()
+        st = ops._stream()
+        p = ops._ptr
+        qm = ops.qmode_code(cfg.mode)
+        S = self.p["shared"]
+        f = cfg.d_ff * cfg.n_shared
+        _lib.check(lib.zmoe_build_plan(None, 1, p(self.zero_idx), T, 1, 1, p(self.shared_plan),
+                                       self.shared_plan.numel() * 4, st))
+        _lib.check(lib.zmoe_gather_qmm_swiglu(p(x), T, x.stride(0), p(S["gate_w"]), p(S["gate_s"]), p(S["gate_b"]),
+                                              p(S["up_w"]), p(S["up_s"]), p(S["up_b"]), 1, f, cfg.d_model, self.gs,
+                                              qm, p(self.shared_plan), T, T, p(self.sh_h), _lib.SWIGLU_PER_OP, st))
+        _lib.check(lib.zmoe_gather_qmm(p(self.sh_h), T, f, p(S["down_w"]), p(S["down_s"]), p(S["down_b"]), 1,
+                                       cfg.d_model, f, self.gs, qm, p(self.shared_plan), T, T, 1, p(self.sh_y), st))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x (T, d_model) bfloat16 on this layer's device -> (T, d_model) bfloat16 (a view of an owned buffer)."""
+        cfg = self.cfg
+        if x.dtype != torch.bfloat16 or x.ndim != 2 or x.shape[1] != cfg.d_model:
+            raise ValueError(f"expected (T, {cfg.d_model}) bfloat16 activations, got {tuple(x.shape)} {x.dtype}")
+        if x.device != self.device:
+            raise RuntimeError(f"activations on {x.device}, layer on {self.device}")
+        T = x.shape[0]
+        if T > self.max_tokens:
+            self._alloc(T)
+        if T == 0:
+            return self.out[:0]
+        if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+            x = x.contiguous()
+        with torch.cuda.device(self.device):
+            self.route(x)
+            self.experts(x)
+            residual = None
+            if cfg.n_shared:
+                self.shared(x)
+                residual = self.sh_y
+            _lib.check(_lib.load().zmoe_moe_combine(
+                ops._ptr(self.y), _lib.BF16, ops._ptr(self.weights), _lib.F32, T, cfg.top_k, cfg.d_model,
+                self.combine_mode, ops._ptr(self.out), 3 if cfg.family == "generic" else 1, ops._ptr(residual),
+                ops._stream()))
+        return self.out[:T]
+
+    __call__ = forward
