@@ -1,0 +1,322 @@
+"""MoE-layer decode benchmark (one JSON line on stdout).
+
+A *step* is one batch of T decode tokens passing through L stacked MoE layers with
+distinct weights (the Qwen3-30B-A3B-shaped layer, 128 experts, top-8, 4-bit affine
+g64).  Rotating over L layers means every layer pass streams its experts from HBM:
+the bytes touched between two visits of the same layer exceed the 126 MB L2 several
+times over.  ``value`` = layer-tokens per second = T * L * n_gpus / step time, inputs
+resident in HBM; ``e2e`` is the same metric through the public Python call with the
+token rows starting in pinned host memory and the result read back every step.
+
+Multi-GPU (--gpus N under torchrun): the path shards by independent layers/experts
+with no data-path collective in this build; every rank runs the same workload on its
+own weights (weak scaling) and the step time is the max over ranks.
+
+``--impl reference`` times the CPU restatement of the reference's path (the compiled
+oracle, all host threads) on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "layer-tokens/s"
+
+
+def _args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="zmoe", choices=["zmoe", "reference"])
+    ap.add_argument("--config", default="c2")
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                return float(json.load(f)["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[tuple[float, float, list[str]]] = []
+        self._stop = threading.Event()
+        self._thr = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                parts = [p.strip() for p in out.split(",")]
+                reasons = [n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active")]
+                self.samples.append((float(parts[0]), float(parts[1]), reasons))
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thr.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = sorted(s[0] for s in self.samples)
+        reasons = sorted({r for s in self.samples for r in s[2]})
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.samples[0][1], "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def _cpu_baseline(cfg, tokens: int, budget_s: float = 12.0):
+    """Time the compiled oracle (a port of the reference's CPU arithmetic) on a bounded sample:
+    whole layer passes of the same shape, repeated until ~budget_s of CPU work."""
+    import numpy as np
+    import torch
+
+    from oracle import fast as F
+    from oracle import semantics as S
+    from zmlx_b200 import synthetic
+
+    small = cfg.scaled(n_experts=max(cfg.top_k * 2, 16))  # expert bank trimmed: routing still picks top_k distinct
+    p = synthetic.make_layer(small, device="cpu")
+
+    def n(t):
+        if t is None:
+            return None
+        if t.dtype == torch.bfloat16:
+            return t.float().numpy()
+        if t.dtype == torch.uint32:
+            return t.view(torch.int32).numpy().view(np.uint32)
+        return t.numpy()
+
+    pn = {k: n(v) for k, v in p.items() if k != "shared"}
+    x = n(synthetic.make_tokens(small, tokens))
+    rw = pn["router_w"]
+
+    def one_pass():
+        logits = S.bf16(x @ rw.T)
+        if small.family == "qwen3":
+            idx, w = S.qwen3_gating(logits, small.top_k)
+            mode = "no_fma"
+        else:
+            w, idx = S.topk_gating_softmax(logits, small.top_k)
+            mode = "t"
+        y, _ = F.experts_forward(x, idx.astype(np.int32), pn, group_size=small.group_size, mode=small.mode)
+        return S.moe_combine(y, w, mode=mode)
+
+    one_pass()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        one_pass()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 2000:
+            break
+    return {"value": tokens * reps / dt, "unit": UNIT, "cores": F.num_threads(), "kind": "port",
+            "sample": f"{reps} passes of one {cfg.name}-shaped layer (expert bank trimmed to {small.n_experts}, "
+                      f"top-{small.top_k} active) at T={tokens}, compiled oracle with OpenMP, {dt:.1f} s"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from zmlx_b200 import synthetic
+
+    cfg = synthetic.CONFIGS[args.config]
+    t0 = time.perf_counter()
+    # steps/warmup are honoured as repetitions of a bounded sample
+    base = _cpu_baseline(cfg, args.tokens, budget_s=min(20.0, 0.4 * max(args.steps, 1)))
+    wall = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * args.tokens / base["value"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} MoE layer decode, T={args.tokens}; CPU restatement of the reference "
+                               "path (MLX itself is not installable here)"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": wall,
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    args = _args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from zmlx_b200 import synthetic
+    from zmlx_b200.layer import MoELayer
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = synthetic.CONFIGS[args.config]
+    T, L = args.tokens, args.layers
+    layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T)
+              for i in range(L)]
+    x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
+    x_dev = x_host.to(dev)
+    out_host = torch.empty((T, cfg.d_model), dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.Stream(device=dev)
+
+    def step_eager():
+        h = x_dev
+        for ly in layers:
+            h = ly.forward(x_dev)  # every layer sees the same token rows: layers are independent work units
+        return h
+
+    # --- distinct experts touched per step (for the algorithmic byte count), from one eager pass
+    with torch.cuda.stream(stream):
+        step_eager()
+    stream.synchronize()
+    distinct = [int(torch.unique(ly.indices[:T]).numel()) for ly in layers]
+    alg_bytes_step = sum(cfg.algorithmic_bytes(dn, T) for dn in distinct)
+
+    graph = None
+    if not args.no_graph:
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                step_eager()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_eager()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step_eager()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # launches per step: router linear, router top-k, plan, gate/up, down, combine (+3 for a shared expert)
+    launches_per_layer = 6 + (3 if cfg.n_shared else 0)
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            run_step()
+    barrier()
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+            for _ in range(args.steps):
+                run_step()
+            ev1.record(stream)
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = T * L * world / (ms_per_step * 1e-3)
+
+    # --- end to end: pinned host rows in, result read back, every step
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            x_dev.copy_(x_host, non_blocking=True)
+            run_step()
+            out_host.copy_(layers[-1].out[:T], non_blocking=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            x_dev.copy_(x_host, non_blocking=True)
+            run_step()
+            out_host.copy_(layers[-1].out[:T], non_blocking=True)
+            stream.synchronize()  # the caller reads the result before issuing the next step
+        e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = T * L * world / (e2e_ms / args.steps * 1e-3)
+
+    if rank == 0:
+        peak, peak_kind = _peaks()
+        achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{cfg.name}: d_model={cfg.d_model}, {cfg.n_experts} experts, top-{cfg.top_k}, "
+                                   f"d_ff={cfg.d_ff}, {cfg.mode} 4-bit; T={T} decode tokens per step through "
+                                   f"L={L} independent layers",
+                       "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
+                       f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
+                       "cuda_graph": graph is not None, "parallelism": f"replicated layers x{world}"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes_per_step": alg_bytes_step,
+                         "note": "whole layer pass (6 kernels); per-kernel figures in profiles/"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
+                    "d2h_bytes_per_step": T * cfg.d_model * 2},
+            "gpu_launches": launches_per_layer * L * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = _cpu_baseline(cfg, T)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -132,6 +132,8 @@ def gather_qmm_swiglu(
     ub_ = None if up_biases is None else up_biases.reshape(E, N, -1).contiguous()
 
     P = lhs.numel()
+    if P * M == 0:
+        return torch.empty(out_batch + (M, N), dtype=torch.bfloat16, device=dev)
     plan = ops.build_plan(rhs.reshape(-1), E, M=M, lhs=lhs.reshape(-1))
     sw = _lib.SWIGLU_CPU if swiglu_contract == "cpu" else _lib.SWIGLU_PER_OP
     out = ops.gather_qmm_swiglu_rows(x2, gw.contiguous(), gs_, gb_, uw.contiguous(), us_, ub_, plan, P * M,

@@ -321,6 +321,8 @@ def _project_quantized(act, weights, scales, biases, indices, group_size, bits, 
     E, D_out = int(weights.shape[0]), int(weights.shape[1])
     if act.dtype != torch.bfloat16:
         raise TypeError(f"gather_qmm_combine_quantized: activations must be bfloat16, got {act.dtype}")
+    if B * K == 0:
+        return torch.empty((B, K, D_out), dtype=torch.bfloat16, device=act.device)
     a2 = act.reshape(B * K, D_in)
     if a2.stride(-1) != 1 or a2.stride(0) % 8 != 0 or a2.data_ptr() % 16 != 0:
         a2 = a2.contiguous()

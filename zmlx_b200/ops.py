@@ -166,8 +166,9 @@ def router_softmax_topk(logits: torch.Tensor, k: int, *, flavour: int, bias: tor
     w = torch.empty((T, k), dtype=torch.float32, device=dev)
     idx = torch.empty((T, k), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().zmoe_router_softmax_topk(_ptr(l2), _dtype_code(l2), T, E, int(k), int(flavour),
-                                                        _ptr(bias), int(renorm), _ptr(w), _ptr(idx), _stream()))
+        if T > 0:
+            _lib.check(_lib.load().zmoe_router_softmax_topk(_ptr(l2), _dtype_code(l2), T, E, int(k), int(flavour),
+                                                            _ptr(bias), int(renorm), _ptr(w), _ptr(idx), _stream()))
     shape = logits.shape[:-1] + (k,)
     return w.reshape(shape), idx.view(torch.uint32).reshape(shape)
 
@@ -182,10 +183,11 @@ def router_sigmoid_topk(logits: torch.Tensor, bias: torch.Tensor, k: int, *, n_g
     w = torch.empty((T, k), dtype=torch.float32, device=dev)
     idx = torch.empty((T, k), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().zmoe_router_sigmoid_bias_topk(_ptr(l2), _dtype_code(l2), T, E, int(k), _ptr(bias),
-                                                             int(n_group), int(topk_group),
-                                                             ctypes.c_float(float(scale)), _ptr(w), _ptr(idx),
-                                                             _stream()))
+        if T > 0:
+            _lib.check(_lib.load().zmoe_router_sigmoid_bias_topk(_ptr(l2), _dtype_code(l2), T, E, int(k), _ptr(bias),
+                                                                 int(n_group), int(topk_group),
+                                                                 ctypes.c_float(float(scale)), _ptr(w), _ptr(idx),
+                                                                 _stream()))
     shape = logits.shape[:-1] + (k,)
     return w.reshape(shape), idx.view(torch.uint32).reshape(shape)
 
@@ -200,6 +202,7 @@ def router_logits(x: torch.Tensor, wr: torch.Tensor, *, out_dtype: torch.dtype =
     T, E = x2.shape[0], wr.shape[0]
     out = torch.empty((T, E), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().zmoe_router_logits(_ptr(x2), _ptr(wr), T, E, d, _ptr(out), _dtype_code(out),
-                                                  _stream()))
+        if T > 0:
+            _lib.check(_lib.load().zmoe_router_logits(_ptr(x2), _ptr(wr), T, E, d, _ptr(out), _dtype_code(out),
+                                                      _stream()))
     return out.reshape(x.shape[:-1] + (E,))
