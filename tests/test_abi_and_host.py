@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_argument_errors_do_not_touch_the_gpu():
     lib = _lib.load()
-    assert lib.zmoe_plan_bytes(8, 128) == 4 * (4 + 129 + 128 + 16)
+    assert lib.zmoe_plan_bytes(8, 128) == 4 * (4 + 4 * 128 + 129 + 128 + 16)
     rc = lib.zmoe_router_softmax_topk(None, 0, 1, 8, 2, 0, None, 0, None, None, None)
     assert rc == _lib.ERR_SHAPE and "null pointer" in _lib.last_error()
     with pytest.raises(ValueError):

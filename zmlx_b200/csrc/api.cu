@@ -89,11 +89,16 @@ __global__ void __launch_bounds__(kPlanThreads) build_plan_kernel(const int* __r
       int off = base + incl - c;
       pv.offset[e] = off;
       cursor[e] = off;
-      if (flag) pv.active[abase + aincl - 1] = e;
+      if (flag) {
+        const int a = abase + aincl - 1;
+        pv.active[a] = e;
+        reinterpret_cast<int4*>(pv.tasks)[a] = make_int4(e, off, c, 0);
+      }
     }
     base += total;
     abase += atotal;
   }
+  for (int a = abase + tid; a < E; a += kPlanThreads) reinterpret_cast<int4*>(pv.tasks)[a] = make_int4(0, 0, 0, 0);
   if (tid == 0) {
     pv.offset[E] = base;
     pv.hdr[0] = abase;

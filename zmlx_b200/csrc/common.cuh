@@ -24,10 +24,12 @@ int check_launch(const char* what);
 
 // --------------------------------------------------------------- plan layout
 // int32 words: [0] n_active experts, [1] rows, [2] status (nonzero: a bad expert
-// id was seen and its row dropped), [3] E; then offset[E+1], active[E],
-// row_src[rows], row_dst[rows].
+// id was seen and its row dropped), [3] E; then tasks[E] (int4 {expert, offset,
+// count, 0}, compact: entries past n_active have count 0), offset[E+1],
+// active[E], row_src[rows], row_dst[rows].
 struct PlanView {
   int* hdr;
+  int* tasks;
   int* offset;
   int* active;
   int* row_src;
@@ -38,14 +40,17 @@ __host__ __device__ inline PlanView plan_view(void* base, int rows, int E) {
   PlanView v;
   int* p = reinterpret_cast<int*>(base);
   v.hdr = p;
-  v.offset = p + 4;
+  v.tasks = p + 4;
+  v.offset = v.tasks + 4 * (size_t)E;
   v.active = v.offset + (E + 1);
   v.row_src = v.active + E;
   v.row_dst = v.row_src + rows;
   return v;
 }
 
-inline size_t plan_words(int rows, int E) { return 4 + (size_t)(E + 1) + (size_t)E + 2 * (size_t)rows; }
+inline size_t plan_words(int rows, int E) {
+  return 4 + 4 * (size_t)E + (size_t)(E + 1) + (size_t)E + 2 * (size_t)rows;
+}
 
 // ------------------------------------------------------------- device helpers
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t h) { return __uint_as_float(h << 16); }

@@ -1,17 +1,23 @@
 // Token-grouped 4-bit quantised expert matmul (gate/up + SwiGLU, and down).
 //
-// Work unit: one expert (from the plan's list of experts that own rows) times a
-// tile of 16*WM weight rows.  The expert's packed weights are streamed from HBM
-// exactly once per CTA with 8-byte loads straight into registers, software
-// pipelined PD groups deep; the expert's token rows (a handful at decode) sit in
-// shared memory.  Codes are turned into bf16 in registers with one shift and one
-// lop3 per pair -- code q becomes the bf16 value 128+q -- and contracted on the
-// tensor cores (mma.sync m16n8k16, fp32 accumulate; weights are the 16-row A
-// operand, tokens the 8-column B operand).  The 128 offset, the group scale and
-// the group bias are applied in fp32 once per 64-wide group:
+// Work unit: one expert (a task record of the plan) times a tile of 16*WM weight
+// rows.  The expert's packed weights are streamed from HBM exactly once per CTA
+// with 8-byte loads straight into registers, software pipelined PD groups deep;
+// the expert's token rows (a handful at decode) sit in shared memory.  Codes are
+// turned into bf16 in registers with one shift and one lop3 per pair -- code q
+// becomes the bf16 value 128+q -- and contracted on the tensor cores (mma.sync
+// m16n8k16, fp32 accumulate; weights are the 16-row A operand, tokens the
+// 8-column B operand).  The 128 offset, the group scale and the group bias are
+// applied in fp32:
 //     sum_k x_k (q_k s + b) = s * sum_k x_k (128 + q_k) + (b - 128 s) * sum_k x_k.
 // A group of 64 codes of one row is held by the 4 lanes of a quad (16 codes
 // each), so every mma accumulates inside one group and the scale factors out.
+//
+// Column multiplexing: the mma has 8 token columns but decode brings TT = 1, 2 or
+// 4 tokens per expert.  The spare columns carry *other groups*: column n is
+// (group slot n / TT, token n % TT), and the B fragment of slot j is zero except
+// in its own columns.  8/TT consecutive groups then accumulate side by side in one
+// accumulator and the per-group fix-up above runs once per 8/TT groups.
 //
 // The kernel is HBM-bound by design: per weight it issues ~0.9 integer ops and
 // 1/256 of an mma, independent of the number of tokens (up to 8*NT per pass).
@@ -22,7 +28,7 @@ namespace zmoe {
 struct QmmParams {
   const __nv_bfloat16* x;  // (x_rows, K) token rows, row stride ldx elements
   int ldx;
-  const uint32_t* w[2];  // (E, N, K/8)
+  const uint32_t* w[2];       // (E, N, K/8)
   const __nv_bfloat16* s[2];  // (E, N, K/64)
   const __nv_bfloat16* b[2];
   const int* plan;
@@ -30,38 +36,53 @@ struct QmmParams {
   __nv_bfloat16* out;  // (rows, N)
   int ldo;
   int N, K, ngroups;
-  int rs;        // token rows staged per pass (<= 8*NT)
+  int rs;        // token rows staged per pass (<= TT*NT)
   int epilogue;  // 0: store T; 1: SwiGLU CPU contract; 2: SwiGLU per-op contract
   int x_by_dst;  // token row r of the output reads x row r instead of the plan's source row
 };
 
-__host__ __device__ inline size_t qmm_xs_stride(int K) { return (size_t)K * 2 + 16; }
+__host__ __device__ inline int qmm_xs_stride(int K) { return K * 2 + 16; }
+__host__ __device__ inline int qmm_sc_stride(int ngroups) { return ((ngroups + 3) & ~3) * 2 + 8; }
 
 // Shared-memory carve-up, identical on host and device.
 struct QmmSmem {
-  size_t xs, xsum, sc, total;
+  int xs, xsum, sc, zero, total;
 };
 __host__ __device__ inline QmmSmem qmm_smem(int K, int ngroups, int rs, int rc, int nmat, int wm, int wk, int nt) {
   QmmSmem m;
-  size_t xs_bytes = (size_t)rs * qmm_xs_stride(K);
-  size_t red_bytes = (wk > 1) ? (size_t)wk * wm * 32 * nmat * nt * 4 * sizeof(float) : 0;
+  int xs_bytes = rs * qmm_xs_stride(K);
+  int red_bytes = (wk > 1) ? wk * wm * 32 * nmat * nt * 4 * (int)sizeof(float) : 0;
   m.xs = 0;
-  size_t a = xs_bytes > red_bytes ? xs_bytes : red_bytes;
-  a = (a + 15) & ~(size_t)15;
+  int a = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+  a = (a + 15) & ~15;
   m.xsum = a;
-  a += (size_t)ngroups * rc * sizeof(float);
-  a = (a + 15) & ~(size_t)15;
+  a += ngroups * rc * (int)sizeof(float);
+  a = (a + 15) & ~15;
   m.sc = a;
-  a += (size_t)nmat * 16 * wm * (ngroups + 1) * sizeof(float2);
+  a += nmat * 2 * 16 * wm * qmm_sc_stride(ngroups);  // raw T scales and biases of the CTA's rows
+  a = (a + 15) & ~15;
+  m.zero = a;  // 32 zero bytes: the B fragment of columns that carry another group
+  a += 32;
   m.total = a;
   return m;
 }
 
+// 8-byte streaming load at a compile-time byte offset from a register base: the offset
+// lives in the instruction, so a quad of groups costs no address arithmetic.
+template <int OFF>
 __device__ __forceinline__ uint2 ldg_stream_u2(const uint32_t* p) {
   uint2 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2+%3];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p), "n"(OFF));
   return v;
 }
+
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                   uint32_t b0, uint32_t b1) {
@@ -72,8 +93,17 @@ __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, ui
 }
 
 // codes at bits [sh, sh+4) and [sh+16, sh+20) -> bf16x2 (128+q_lo, 128+q_hi)
-__device__ __forceinline__ uint32_t deq_pair(uint32_t word, int sh) {
-  return ((word >> sh) & 0x000F000Fu) | 0x43004300u;
+template <int SH>
+__device__ __forceinline__ uint32_t deq_pair(uint32_t word) {
+  uint32_t r;
+  if (SH == 0) {
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(word));
+  } else {
+    asm("{ .reg .b32 t; shr.b32 t, %1, %2; lop3.b32 %0, t, 0x000F000F, 0x43004300, 0xEA; }"
+        : "=r"(r)
+        : "r"(word), "n"(SH));
+  }
+  return r;
 }
 
 __device__ __forceinline__ float swiglu_cpu_contract(float g, float u) {
@@ -92,8 +122,68 @@ __device__ __forceinline__ float swiglu_per_op(float g, float u) {
   return round_bf16(g * sig) * u;
 }
 
-template <int NMAT, int NT, int WK, int WM, int PD>
-__global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParams p) {
+// Warp wk owns the quads (4 consecutive groups) wk, wk+WK, ...; item gi of its
+// stream is group (wk + (gi/4)*WK)*4 + gi%4.
+template <int WK>
+__device__ __forceinline__ int stream_group(int wk, int gi) {
+  return (wk + (gi >> 2) * WK) * 4 + (gi & 3);
+}
+
+// Loads one quad (4 consecutive groups: 32 bytes of each of the lane's rows) into registers.
+template <int NMAT, bool FULLQ>
+__device__ __forceinline__ void load_quad(uint2 (&buf)[4][NMAT][2], const uint32_t* (&wp)[NMAT][2], int G0,
+                                          int ngroups) {
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (FULLQ || G0 + 0 < ngroups) buf[0][m][h] = ldg_stream_u2<0>(wp[m][h]);
+      if (FULLQ || G0 + 1 < ngroups) buf[1][m][h] = ldg_stream_u2<32>(wp[m][h]);
+      if (FULLQ || G0 + 2 < ngroups) buf[2][m][h] = ldg_stream_u2<64>(wp[m][h]);
+      if (FULLQ || G0 + 3 < ngroups) buf[3][m][h] = ldg_stream_u2<96>(wp[m][h]);
+    }
+  }
+}
+
+// Applies scale, bias and the 128 offset to a block of 8/TT multiplexed groups whose first
+// item in the warp's stream is gi0.  Lane (g, tig) owns columns 2*tig and 2*tig+1.
+template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
+__device__ __forceinline__ void fixup_block(float (&acc)[NMAT][NT][4], const float (&dg)[NMAT][NT][4],
+                                            const float* xsum, const unsigned char* sraw, int sc_stride, int wk,
+                                            int wm, int g, int tig, int gi0, int nq_w, int ngroups) {
+  constexpr int RC = 8 * NT;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int col = 2 * tig + c;
+    const int gi_c = gi0 + ((TT == 8) ? 0 : col / TT);
+    const int G_c = (wk + (gi_c >> 2) * WK) * 4 + (gi_c & 3);
+    if ((gi_c >> 2) < nq_w && (FULLQ || G_c < ngroups)) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float X = xsum[G_c * RC + ((TT == 8) ? nt * 8 + col : col % TT)];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = wm * 16 + g + 8 * h;
+            const float sv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+                sraw + ((m * 2 + 0) * 16 * WM + r) * sc_stride + G_c * 2));
+            const float bv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+                sraw + ((m * 2 + 1) * 16 * WM + r) * sc_stride + G_c * 2));
+            const float cv = fmaf(-128.0f, sv, bv);
+            acc[m][nt][h * 2 + c] = fmaf(sv, dg[m][nt][h * 2 + c], fmaf(cv, X, acc[m][nt][h * 2 + c]));
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
+__global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM) : 1)
+    qmm_affine_kernel(const QmmParams p) {
+  static_assert(NT == 1 || TT == 8, "token tiles beyond the first are full");
+  constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
   constexpr int NTH = 32 * WK * WM;
   constexpr int RC = 8 * NT;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -105,24 +195,29 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
   const int wm = wid / WK;
   const int g = lane >> 2;
   const int tig = lane & 3;
+  // column g of the B operand is (slot g / TT, token g % TT)
+  const int slot_g = g / TT;
+  const int tok_g = g % TT;
 
   const int K = p.K, N = p.N, ngroups = p.ngroups;
   const int K8 = K >> 3;
-  const size_t xs_stride = qmm_xs_stride(K);
+  const int xs_stride = qmm_xs_stride(K);
+  const int sc_stride = qmm_sc_stride(ngroups);
   const QmmSmem lay = qmm_smem(K, ngroups, p.rs, RC, NMAT, WM, WK, NT);
   unsigned char* xs = smem + lay.xs;
   float* xsum = reinterpret_cast<float*>(smem + lay.xsum);
-  float2* scs = reinterpret_cast<float2*>(smem + lay.sc);
+  unsigned char* sraw = smem + lay.sc;
   float* red = reinterpret_cast<float*>(smem + lay.xs);
 
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.rows, p.E);
-  const int n_active = pv.hdr[0];
-  const int ng_w = (ngroups > wk) ? (ngroups - wk + WK - 1) / WK : 0;  // groups of this warp: wk, wk+WK, ...
+  const int nq = (ngroups + 3) >> 2;
+  const int nq_w = (nq > wk) ? (nq - wk + WK - 1) / WK : 0;
+  bool first_pass = true;
 
-  for (int a = blockIdx.y; a < n_active; a += gridDim.y) {
-    const int e = pv.active[a];
-    const int off = pv.offset[e];
-    const int cnt = pv.offset[e + 1] - off;
+  for (int a = blockIdx.y; a < p.E; a += gridDim.y) {
+    const int4 task = __ldg(reinterpret_cast<const int4*>(pv.tasks) + a);  // {expert, offset, count, -}
+    const int e = task.x, off = task.y, cnt = task.z;
+    if (cnt == 0) break;  // tasks are compact: nothing beyond the first empty one
     const int n_cta = blockIdx.x * 16 * WM;
     const int n_lo = min(n_cta + wm * 16 + g, N - 1);
     const int n_hi = min(n_cta + wm * 16 + g + 8, N - 1);
@@ -138,78 +233,94 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
     for (int rc = 0; rc < cnt; rc += p.rs) {
       const int nrow = min(p.rs, cnt - rc);
 
-      // ---- prefetch the first PD groups of packed weights into registers
-      uint2 wbuf[PD][NMAT][2];
+      if (!first_pass) __syncthreads();  // the previous pass is done with shared memory
+      first_pass = false;
+
+      // ---- (1) prefetch the first two quads (8 groups) of packed weights into registers
+      const uint32_t* wp[NMAT][2];  // this warp's next quad to fetch, per matrix and row half
 #pragma unroll
-      for (int s = 0; s < PD; ++s) {
-        if (s < ng_w) {
-          const int G = wk + s * WK;
+      for (int m = 0; m < NMAT; ++m) {
+        wp[m][0] = wrow[m][0] + wk * 32;
+        wp[m][1] = wrow[m][1] + wk * 32;
+      }
+      uint2 wbuf[2][4][NMAT][2];
+#pragma unroll
+      for (int bq = 0; bq < 2; ++bq) {
+        if (bq < nq_w) {
+          load_quad<NMAT, FULLQ>(wbuf[bq], wp, (wk + bq * WK) * 4, ngroups);
 #pragma unroll
           for (int m = 0; m < NMAT; ++m) {
-            wbuf[s][m][0] = ldg_stream_u2(wrow[m][0] + G * 8);
-            wbuf[s][m][1] = ldg_stream_u2(wrow[m][1] + G * 8);
+            wp[m][0] += WK * 32;
+            wp[m][1] += WK * 32;
           }
         }
       }
 
-      if (rc > 0 || a != (int)blockIdx.y) __syncthreads();  // previous pass is done with shared memory
+      // ---- (2) scales and biases of this CTA's rows: asynchronous copies, raw T values
+      if (rc == 0) {
+        constexpr int ROWS = 16 * WM;
+#pragma unroll
+        for (int arr = 0; arr < NMAT * 2; ++arr) {
+          const __nv_bfloat16* base = (arr & 1) ? p.b[arr >> 1] : p.s[arr >> 1];
+          base += (size_t)e * N * ngroups;
+          unsigned char* dst = sraw + arr * ROWS * sc_stride;
+          if ((ngroups & 3) == 0) {
+            const int cpr = ngroups >> 2;  // 8-byte chunks per row
+            for (int i = tid; i < ROWS * cpr; i += NTH) {
+              const int r = i / cpr;
+              const int c = i - r * cpr;
+              const int n = min(n_cta + r, N - 1);
+              cp_async_8(dst + r * sc_stride + c * 8, base + (size_t)n * ngroups + c * 4);
+            }
+          } else {
+            for (int i = tid; i < ROWS * ngroups; i += NTH) {
+              const int r = i / ngroups;
+              const int c = i - r * ngroups;
+              const int n = min(n_cta + r, N - 1);
+              reinterpret_cast<__nv_bfloat16*>(dst + r * sc_stride)[c] = base[(size_t)n * ngroups + c];
+            }
+          }
+        }
+      }
 
-      // ---- stage the token rows: 8-element blocks permuted to (0,4,1,5,2,6,3,7), plus group sums
-      {
-        const int items = nrow * K8;
-        for (int i0 = 0; i0 < items; i0 += NTH) {
-          const int i = i0 + tid;
-          float part = 0.0f;
-          if (i < items) {
-            const int t = i / K8;
-            const int blk = i - t * K8;
-            const int src = p.x_by_dst ? pv.row_dst[off + rc + t] : pv.row_src[off + rc + t];
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx) + blk);
+      // ---- (3) stage the token rows: 8-element blocks permuted to (0,4,1,5,2,6,3,7), plus group sums
+      for (int t = 0; t < nrow; ++t) {
+        const int src = p.x_by_dst ? pv.row_dst[off + rc + t] : pv.row_src[off + rc + t];
+        const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx);
+        for (int b0 = wid * 32; b0 < K8; b0 += NTH) {  // warp-uniform trip count (K8 is a multiple of 8)
+          const int blk = b0 + lane;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (blk < K8) {
+            v = __ldg(xrow + blk);
             uint4 o;
             o.x = __byte_perm(v.x, v.z, 0x5410);
             o.y = __byte_perm(v.x, v.z, 0x7632);
             o.z = __byte_perm(v.y, v.w, 0x5410);
             o.w = __byte_perm(v.y, v.w, 0x7632);
-            *reinterpret_cast<uint4*>(xs + (size_t)t * xs_stride + (size_t)blk * 16) = o;
-            part = ((bf16_bits_to_float(v.x & 0xffffu) + bf16_bits_to_float(v.x >> 16)) +
-                    (bf16_bits_to_float(v.y & 0xffffu) + bf16_bits_to_float(v.y >> 16))) +
-                   ((bf16_bits_to_float(v.z & 0xffffu) + bf16_bits_to_float(v.z >> 16)) +
-                    (bf16_bits_to_float(v.w & 0xffffu) + bf16_bits_to_float(v.w >> 16)));
+            *reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16) = o;
           }
+          float part = ((bf16_bits_to_float(v.x & 0xffffu) + bf16_bits_to_float(v.x >> 16)) +
+                        (bf16_bits_to_float(v.y & 0xffffu) + bf16_bits_to_float(v.y >> 16))) +
+                       ((bf16_bits_to_float(v.z & 0xffffu) + bf16_bits_to_float(v.z >> 16)) +
+                        (bf16_bits_to_float(v.w & 0xffffu) + bf16_bits_to_float(v.w >> 16)));
           part += __shfl_xor_sync(0xffffffffu, part, 1);
           part += __shfl_xor_sync(0xffffffffu, part, 2);
           part += __shfl_xor_sync(0xffffffffu, part, 4);
-          if (i < items && (lane & 7) == 0) {
-            const int t = i / K8;
-            const int blk = i - t * K8;
-            xsum[(blk >> 3) * RC + t] = part;
-          }
+          if (blk < K8 && (lane & 7) == 0) xsum[(blk >> 3) * RC + t] = part;
         }
-        // token slots beyond nrow contribute nothing
+      }
+      if (tid < 8) reinterpret_cast<uint32_t*>(smem + lay.zero)[tid] = 0u;
+      if (nrow < RC) {  // token slots beyond nrow contribute nothing
         for (int i = tid; i < ngroups * RC; i += NTH) {
           if ((i % RC) >= nrow) xsum[i] = 0.0f;
         }
       }
-      // ---- stage (scale, bias - 128*scale) of this CTA's rows, once per expert
-      if (rc == 0) {
-        const int per_mat = 16 * WM * ngroups;
-        for (int i = tid; i < NMAT * per_mat; i += NTH) {
-          const int m = i / per_mat;
-          const int r = (i - m * per_mat) / ngroups;
-          const int G = i - m * per_mat - r * ngroups;
-          const int n = min(n_cta + r, N - 1);
-          const size_t o = ((size_t)e * N + n) * ngroups + G;
-          const __nv_bfloat16* sp = (NMAT == 2 && m) ? p.s[1] : p.s[0];
-          const __nv_bfloat16* bp = (NMAT == 2 && m) ? p.b[1] : p.b[0];
-          const float sv = __bfloat162float(sp[o]);
-          const float bv = __bfloat162float(bp[o]);
-          scs[(size_t)(m * 16 * WM + r) * (ngroups + 1) + G] = make_float2(sv, fmaf(-128.0f, sv, bv));
-        }
-      }
+      cp_async_wait_all();
       __syncthreads();
 
-      // ---- main loop over this warp's groups
+      // ---- (4) main loop over this warp's groups
       float acc[NMAT][NT][4];
+      float dg[NMAT][NT][4];
 #pragma unroll
       for (int m = 0; m < NMAT; ++m)
 #pragma unroll
@@ -217,88 +328,96 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[m][nt][j] = 0.0f;
 
-      for (int it = 0; it < ng_w; it += PD) {
+      // per-lane shared-memory bases: token row (or the zero page) and the scale rows
+      const int xlane = lay.xs + ((TT == 8) ? g : tok_g) * xs_stride + tig * 32;  // byte offsets into smem
+      const int zpage = lay.zero;
+      const bool tok_ok = ((TT == 8) ? g : tok_g) < nrow;
+
+      for (int qi = 0; qi < nq_w; qi += 2) {
 #pragma unroll
-        for (int s = 0; s < PD; ++s) {
-          const int gi = it + s;
-          if (gi < ng_w) {
-            const int G = wk + gi * WK;
-            uint4 xb[NT][2];
-            float2 xs2[NT];
+        for (int bq = 0; bq < 2; ++bq) {
+          const int quad = wk + (qi + bq) * WK;
+          if (qi + bq < nq_w) {  // warp-uniform
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const int tb = nt * 8 + g;
-              if (tb < nrow) {
-                const unsigned char* xp = xs + (size_t)tb * xs_stride + ((size_t)G * 64 + tig * 16) * 2;
-                xb[nt][0] = *reinterpret_cast<const uint4*>(xp);
-                xb[nt][1] = *reinterpret_cast<const uint4*>(xp + 16);
-              } else {
-                xb[nt][0] = make_uint4(0, 0, 0, 0);
-                xb[nt][1] = make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < 4; ++j) {
+              const int s = bq * 4 + j;
+              const int slot = s % GPB;
+              const int G = quad * 4 + j;
+              if (slot == 0) {
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) dg[m][nt][jj] = 0.0f;
               }
-              xs2[nt] = *reinterpret_cast<const float2*>(xsum + G * RC + nt * 8 + 2 * tig);
+              if (FULLQ || G < ngroups) {
+                uint4 xb[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                  const bool mine = (TT == 8) ? (nt * 8 + g < nrow) : (tok_ok && slot_g == slot);
+                  const int xo = mine ? (xlane + nt * 8 * xs_stride + quad * 512 + j * 128) : zpage;
+                  xb[nt][0] = *reinterpret_cast<const uint4*>(smem + xo);
+                  xb[nt][1] = *reinterpret_cast<const uint4*>(smem + xo + 16);
+                }
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                  const uint2 wa = wbuf[bq][j][m][0];
+                  const uint2 wb = wbuf[bq][j][m][1];
+                  {
+                    const uint32_t a0 = deq_pair<0>(wa.x), a1 = deq_pair<0>(wb.x);
+                    const uint32_t a2 = deq_pair<4>(wa.x), a3 = deq_pair<4>(wb.x);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
+                  }
+                  {
+                    const uint32_t a0 = deq_pair<8>(wa.x), a1 = deq_pair<8>(wb.x);
+                    const uint32_t a2 = deq_pair<12>(wa.x), a3 = deq_pair<12>(wb.x);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
+                  }
+                  {
+                    const uint32_t a0 = deq_pair<0>(wa.y), a1 = deq_pair<0>(wb.y);
+                    const uint32_t a2 = deq_pair<4>(wa.y), a3 = deq_pair<4>(wb.y);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
+                  }
+                  {
+                    const uint32_t a0 = deq_pair<8>(wa.y), a1 = deq_pair<8>(wb.y);
+                    const uint32_t a2 = deq_pair<12>(wa.y), a3 = deq_pair<12>(wb.y);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
+                  }
+                }
+              }
+              if (GPB <= 4 && slot == GPB - 1)
+                fixup_block<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig,
+                                                         (qi + bq) * 4 + j - (GPB - 1), nq_w, ngroups);
             }
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-              const uint2 wa = wbuf[s][m][0];
-              const uint2 wb = wbuf[s][m][1];
-              float dg[NT][4];
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) dg[nt][j] = 0.0f;
-              {
-                const uint32_t a0 = deq_pair(wa.x, 0), a1 = deq_pair(wb.x, 0);
-                const uint32_t a2 = deq_pair(wa.x, 4), a3 = deq_pair(wb.x, 4);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
-              }
-              {
-                const uint32_t a0 = deq_pair(wa.x, 8), a1 = deq_pair(wb.x, 8);
-                const uint32_t a2 = deq_pair(wa.x, 12), a3 = deq_pair(wb.x, 12);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
-              }
-              {
-                const uint32_t a0 = deq_pair(wa.y, 0), a1 = deq_pair(wb.y, 0);
-                const uint32_t a2 = deq_pair(wa.y, 4), a3 = deq_pair(wb.y, 4);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
-              }
-              {
-                const uint32_t a0 = deq_pair(wa.y, 8), a1 = deq_pair(wb.y, 8);
-                const uint32_t a2 = deq_pair(wa.y, 12), a3 = deq_pair(wb.y, 12);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
-              }
-              const float2 s_lo = scs[(size_t)(m * 16 * WM + wm * 16 + g) * (ngroups + 1) + G];
-              const float2 s_hi = scs[(size_t)(m * 16 * WM + wm * 16 + g + 8) * (ngroups + 1) + G];
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                acc[m][nt][0] = fmaf(s_lo.x, dg[nt][0], fmaf(s_lo.y, xs2[nt].x, acc[m][nt][0]));
-                acc[m][nt][1] = fmaf(s_lo.x, dg[nt][1], fmaf(s_lo.y, xs2[nt].y, acc[m][nt][1]));
-                acc[m][nt][2] = fmaf(s_hi.x, dg[nt][2], fmaf(s_hi.y, xs2[nt].x, acc[m][nt][2]));
-                acc[m][nt][3] = fmaf(s_hi.x, dg[nt][3], fmaf(s_hi.y, xs2[nt].y, acc[m][nt][3]));
-              }
-            }
-            // refill this pipeline slot
-            const int gn = gi + PD;
-            if (gn < ng_w) {
-              const int Gn = wk + gn * WK;
+            // refill this pipeline slot with the quad two steps ahead
+            if (qi + bq + 2 < nq_w) {
+              load_quad<NMAT, FULLQ>(wbuf[bq], wp, (quad + 2 * WK) * 4, ngroups);
 #pragma unroll
               for (int m = 0; m < NMAT; ++m) {
-                wbuf[s][m][0] = ldg_stream_u2(wrow[m][0] + Gn * 8);
-                wbuf[s][m][1] = ldg_stream_u2(wrow[m][1] + Gn * 8);
+                wp[m][0] += WK * 32;
+                wp[m][1] += WK * 32;
               }
             }
           }
         }
+        if (GPB == 8)
+          fixup_block<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig, qi * 4, nq_w,
+                                                   ngroups);
       }
 
-      // ---- reduce the K-split across warps (fixed order), then the epilogue
+      // ---- (5) reduce the K-split across warps (fixed order)
       if (WK > 1) {
         __syncthreads();  // every warp is done reading the staged rows; reuse their space
-        float* mine = red + ((size_t)(wm * WK + wk) * 32 + lane) * (NMAT * NT * 4);
+        float* mine = red + ((wm * WK + wk) * 32 + lane) * (NMAT * NT * 4);
 #pragma unroll
         for (int m = 0; m < NMAT; ++m)
 #pragma unroll
@@ -309,7 +428,7 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
         if (wk == 0) {
 #pragma unroll
           for (int o = 1; o < WK; ++o) {
-            const float* other = red + ((size_t)(wm * WK + o) * 32 + lane) * (NMAT * NT * 4);
+            const float* other = red + ((wm * WK + o) * 32 + lane) * (NMAT * NT * 4);
 #pragma unroll
             for (int m = 0; m < NMAT; ++m)
 #pragma unroll
@@ -320,13 +439,35 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
         }
       }
       if (wk == 0) {
+        // ---- (6) fold the multiplexed columns back onto their tokens (fixed order), then the epilogue
+        if (TT < 8) {
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (TT == 1) {
+                acc[m][0][h * 2] += acc[m][0][h * 2 + 1];
+                acc[m][0][h * 2 + 1] = 0.0f;
+              }
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                float v = acc[m][0][h * 2 + c];
+                if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                acc[m][0][h * 2 + c] = v;
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int t = nt * 8 + 2 * tig + (j & 1);
+            const int col = 2 * tig + (j & 1);
+            const int t = (TT == 8) ? nt * 8 + col : col;
             const int n = n_cta + wm * 16 + g + ((j >> 1) ? 8 : 0);
-            if (t < nrow && n < N) {
+            const bool writer = (TT == 8) || (col < TT);
+            if (writer && t < nrow && n < N) {
               float v;
               if (NMAT == 2) {
                 v = (p.epilogue == 2) ? swiglu_per_op(acc[0][nt][j], acc[NMAT - 1][nt][j])
@@ -347,16 +488,18 @@ __global__ void __launch_bounds__(32 * WK * WM) qmm_affine_kernel(const QmmParam
 // ------------------------------------------------------------------ host side
 
 struct QmmChoice {
-  int nt, wk, wm;
+  int nt, tt, wk, wm;
 };
 
 static QmmChoice choose_config(int ngroups, int rows_hint) {
   QmmChoice c;
   c.nt = rows_hint <= 8 ? 1 : (rows_hint <= 16 ? 2 : 4);
-  if (ngroups >= 16) {
+  c.tt = rows_hint <= 1 ? 1 : (rows_hint <= 2 ? 2 : (rows_hint <= 4 ? 4 : 8));
+  const int nq = (ngroups + 3) / 4;
+  if (nq >= 8) {
     c.wk = 4;
     c.wm = 1;
-  } else if (ngroups >= 8) {
+  } else if (nq >= 4) {
     c.wk = 2;
     c.wm = 2;
   } else {
@@ -366,36 +509,46 @@ static QmmChoice choose_config(int ngroups, int rows_hint) {
   return c;
 }
 
-template <int NMAT, int NT, int WK, int WM>
-static int launch_cfg(const QmmParams& p, int max_groups, cudaStream_t st) {
-  constexpr int PD = 8;
-  auto kern = qmm_affine_kernel<NMAT, NT, WK, WM, PD>;
+template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
+static int launch_full(const QmmParams& p, int max_groups, cudaStream_t st) {
+  auto kern = qmm_affine_kernel<NMAT, NT, TT, WK, WM, FULLQ>;
   QmmSmem lay = qmm_smem(p.K, p.ngroups, p.rs, 8 * NT, NMAT, WM, WK, NT);
   if (lay.total > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
-    if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "qmm: shared memory of %zu bytes refused: %s", lay.total,
-                                      cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total);
+    if (e != cudaSuccess)
+      return fail(ZMOE_ERR_CUDA, "qmm: shared memory of %d bytes refused: %s", lay.total, cudaGetErrorString(e));
   }
   dim3 grid((p.N + 16 * WM - 1) / (16 * WM), max_groups);
   kern<<<grid, 32 * WK * WM, lay.total, st>>>(p);
   return check_launch("qmm_affine_kernel");
 }
 
+template <int NMAT, int NT, int TT, int WK, int WM>
+static int launch_cfg(const QmmParams& p, int max_groups, cudaStream_t st) {
+  if ((p.ngroups & 3) == 0) return launch_full<NMAT, NT, TT, WK, WM, true>(p, max_groups, st);
+  return launch_full<NMAT, NT, TT, WK, WM, false>(p, max_groups, st);
+}
+
+template <int NMAT, int WK, int WM>
+static int launch_tokens(const QmmParams& p, const QmmChoice& c, int max_groups, cudaStream_t st) {
+  if (c.nt == 1) {
+    switch (c.tt) {
+      case 1: return launch_cfg<NMAT, 1, 1, WK, WM>(p, max_groups, st);
+      case 2: return launch_cfg<NMAT, 1, 2, WK, WM>(p, max_groups, st);
+      case 4: return launch_cfg<NMAT, 1, 4, WK, WM>(p, max_groups, st);
+      default: return launch_cfg<NMAT, 1, 8, WK, WM>(p, max_groups, st);
+    }
+  }
+  if (c.nt == 2) return launch_cfg<NMAT, 2, 8, WK, WM>(p, max_groups, st);
+  return launch_cfg<NMAT, 4, 8, WK, WM>(p, max_groups, st);
+}
+
 template <int NMAT>
 static int launch_nmat(const QmmParams& p, const QmmChoice& c, int max_groups, cudaStream_t st) {
-#define ZMOE_CASE(NT_, WK_, WM_) \
-  if (c.nt == NT_ && c.wk == WK_ && c.wm == WM_) return launch_cfg<NMAT, NT_, WK_, WM_>(p, max_groups, st);
-  ZMOE_CASE(1, 4, 1)
-  ZMOE_CASE(2, 4, 1)
-  ZMOE_CASE(4, 4, 1)
-  ZMOE_CASE(1, 2, 2)
-  ZMOE_CASE(2, 2, 2)
-  ZMOE_CASE(4, 2, 2)
-  ZMOE_CASE(1, 1, 4)
-  ZMOE_CASE(2, 1, 4)
-  ZMOE_CASE(4, 1, 4)
-#undef ZMOE_CASE
-  return fail(ZMOE_ERR_UNSUPPORTED, "qmm: no kernel for nt=%d wk=%d wm=%d", c.nt, c.wk, c.wm);
+  if (c.wk == 4 && c.wm == 1) return launch_tokens<NMAT, 4, 1>(p, c, max_groups, st);
+  if (c.wk == 2 && c.wm == 2) return launch_tokens<NMAT, 2, 2>(p, c, max_groups, st);
+  if (c.wk == 1 && c.wm == 4) return launch_tokens<NMAT, 1, 4>(p, c, max_groups, st);
+  return fail(ZMOE_ERR_UNSUPPORTED, "qmm: no kernel for wk=%d wm=%d", c.wk, c.wm);
 }
 
 int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* const* w, const void* const* s,
@@ -414,7 +567,8 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
   ZMOE_REQUIRE(ldx >= K && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0, ZMOE_ERR_ALIGN,
                "%s: x rows must be 16-byte aligned (ldx=%d)", who, ldx);
   for (int m = 0; m < nmat; ++m)
-    ZMOE_REQUIRE(((uintptr_t)w[m] % 8) == 0, ZMOE_ERR_ALIGN, "%s: packed weights must be 8-byte aligned", who);
+    ZMOE_REQUIRE(((uintptr_t)w[m] % 8) == 0 && ((uintptr_t)s[m] % 8) == 0 && ((uintptr_t)b[m] % 8) == 0,
+                 ZMOE_ERR_ALIGN, "%s: packed weights, scales and biases must be 8-byte aligned", who);
   if (rows == 0) return ZMOE_OK;
   if (rows_hint <= 0 || rows_hint > rows) rows_hint = rows;
 
@@ -440,10 +594,17 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
 
   QmmChoice c = choose_config(p.ngroups, rows_hint);
   // keep the staged token rows within ~96 KB so that several CTAs share an SM
-  int rs = 8 * c.nt;
-  if (rows_hint < rs) rs = rows_hint;
-  while (rs > 1 && (size_t)rs * qmm_xs_stride(K) > 96 * 1024) rs = (rs + 1) / 2;
-  while (c.nt > 1 && 8 * (c.nt / 2) >= rs) c.nt /= 2;
+  int rs = (c.nt == 1) ? c.tt : 8 * c.nt;
+  while (rs > 1 && (size_t)rs * qmm_xs_stride(K) > 96 * 1024) rs = rs / 2;
+  if (rs < 8) {
+    c.nt = 1;
+    c.tt = rs >= 4 ? 4 : (rs >= 2 ? 2 : 1);
+    rs = c.tt;
+  } else {
+    c.tt = 8;
+    c.nt = rs >= 32 ? 4 : (rs >= 16 ? 2 : 1);
+    rs = 8 * c.nt;
+  }
   p.rs = rs;
   int max_groups = rows < E ? rows : E;
   if (max_groups > 65535) max_groups = 65535;
