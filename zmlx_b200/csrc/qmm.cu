@@ -51,7 +51,7 @@ struct QmmSmem {
 __host__ __device__ inline QmmSmem qmm_smem(int K, int ngroups, int rs, int rc, int nmat, int wm, int wk, int nt) {
   QmmSmem m;
   int xs_bytes = rs * qmm_xs_stride(K);
-  int red_bytes = (wk > 1) ? wk * wm * 32 * nmat * nt * 4 * (int)sizeof(float) : 0;
+  int red_bytes = (wk * nmat > 1) ? wk * wm * nmat * 32 * nt * 4 * (int)sizeof(float) : 0;
   m.xs = 0;
   int a = xs_bytes > red_bytes ? xs_bytes : red_bytes;
   a = (a + 15) & ~15;
@@ -93,15 +93,17 @@ __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, ui
 }
 
 // codes at bits [sh, sh+4) and [sh+16, sh+20) -> bf16x2 (128+q_lo, 128+q_hi)
+// The mask and the magic constant are passed in registers so that the and-or is a
+// single three-register LOP3.
 template <int SH>
-__device__ __forceinline__ uint32_t deq_pair(uint32_t word) {
+__device__ __forceinline__ uint32_t deq_pair(uint32_t word, uint32_t mask, uint32_t magic) {
   uint32_t r;
   if (SH == 0) {
-    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(word));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(word), "r"(mask), "r"(magic));
   } else {
-    asm("{ .reg .b32 t; shr.b32 t, %1, %2; lop3.b32 %0, t, 0x000F000F, 0x43004300, 0xEA; }"
+    asm("{ .reg .b32 t; shr.b32 t, %1, %4; lop3.b32 %0, t, %2, %3, 0xEA; }"
         : "=r"(r)
-        : "r"(word), "n"(SH));
+        : "r"(word), "r"(mask), "r"(magic), "n"(SH));
   }
   return r;
 }
@@ -129,28 +131,26 @@ __device__ __forceinline__ int stream_group(int wk, int gi) {
   return (wk + (gi >> 2) * WK) * 4 + (gi & 3);
 }
 
-// Loads one quad (4 consecutive groups: 32 bytes of each of the lane's rows) into registers.
-template <int NMAT, bool FULLQ>
-__device__ __forceinline__ void load_quad(uint2 (&buf)[4][NMAT][2], const uint32_t* (&wp)[NMAT][2], int G0,
-                                          int ngroups) {
+// Loads one quad (4 consecutive groups: 32 bytes of each of the lane's two rows) into registers.
+template <bool FULLQ>
+__device__ __forceinline__ void load_quad(uint2 (&buf)[4][2], const uint32_t* (&wp)[2], int G0, int ngroups) {
 #pragma unroll
-  for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (FULLQ || G0 + 0 < ngroups) buf[0][m][h] = ldg_stream_u2<0>(wp[m][h]);
-      if (FULLQ || G0 + 1 < ngroups) buf[1][m][h] = ldg_stream_u2<32>(wp[m][h]);
-      if (FULLQ || G0 + 2 < ngroups) buf[2][m][h] = ldg_stream_u2<64>(wp[m][h]);
-      if (FULLQ || G0 + 3 < ngroups) buf[3][m][h] = ldg_stream_u2<96>(wp[m][h]);
-    }
+  for (int h = 0; h < 2; ++h) {
+    if (FULLQ || G0 + 0 < ngroups) buf[0][h] = ldg_stream_u2<0>(wp[h]);
+    if (FULLQ || G0 + 1 < ngroups) buf[1][h] = ldg_stream_u2<32>(wp[h]);
+    if (FULLQ || G0 + 2 < ngroups) buf[2][h] = ldg_stream_u2<64>(wp[h]);
+    if (FULLQ || G0 + 3 < ngroups) buf[3][h] = ldg_stream_u2<96>(wp[h]);
   }
 }
 
 // Applies scale, bias and the 128 offset to a block of 8/TT multiplexed groups whose first
 // item in the warp's stream is gi0.  Lane (g, tig) owns columns 2*tig and 2*tig+1.
-template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
-__device__ __forceinline__ void fixup_block(float (&acc)[NMAT][NT][4], const float (&dg)[NMAT][NT][4],
-                                            const float* xsum, const unsigned char* sraw, int sc_stride, int wk,
-                                            int wm, int g, int tig, int gi0, int nq_w, int ngroups) {
+// srow points at the lane's scale row (row g of the warp's 16), brow at its bias row;
+// the rows of g+8 sit 8 * sc_stride bytes further.
+template <int NT, int TT, int WK, bool FULLQ>
+__device__ __forceinline__ void fixup_block(float (&acc)[NT][4], const float (&dg)[NT][4], const float* xsum,
+                                            const unsigned char* srow, const unsigned char* brow, int sc_stride,
+                                            int wk, int tig, int gi0, int nq_w, int ngroups) {
   constexpr int RC = 8 * NT;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
@@ -159,32 +159,30 @@ __device__ __forceinline__ void fixup_block(float (&acc)[NMAT][NT][4], const flo
     const int G_c = (wk + (gi_c >> 2) * WK) * 4 + (gi_c & 3);
     if ((gi_c >> 2) < nq_w && (FULLQ || G_c < ngroups)) {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const float X = xsum[G_c * RC + ((TT == 8) ? nt * 8 + col : col % TT)];
+      for (int h = 0; h < 2; ++h) {
+        const float sv = __bfloat162float(
+            *reinterpret_cast<const __nv_bfloat16*>(srow + h * 8 * sc_stride + G_c * 2));
+        const float bv = __bfloat162float(
+            *reinterpret_cast<const __nv_bfloat16*>(brow + h * 8 * sc_stride + G_c * 2));
+        const float cv = fmaf(-128.0f, sv, bv);
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int r = wm * 16 + g + 8 * h;
-            const float sv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
-                sraw + ((m * 2 + 0) * 16 * WM + r) * sc_stride + G_c * 2));
-            const float bv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
-                sraw + ((m * 2 + 1) * 16 * WM + r) * sc_stride + G_c * 2));
-            const float cv = fmaf(-128.0f, sv, bv);
-            acc[m][nt][h * 2 + c] = fmaf(sv, dg[m][nt][h * 2 + c], fmaf(cv, X, acc[m][nt][h * 2 + c]));
-          }
+        for (int nt = 0; nt < NT; ++nt) {
+          const float X = xsum[G_c * RC + ((TT == 8) ? nt * 8 + col : col % TT)];
+          acc[nt][h * 2 + c] = fmaf(sv, dg[nt][h * 2 + c], fmaf(cv, X, acc[nt][h * 2 + c]));
         }
       }
     }
   }
 }
 
+// Warp layout of a CTA: warp = ((wm * NMAT) + mat) * WK + wk.  Each warp streams one
+// matrix (gate or up) for 16 weight rows over its share of the K quads.
 template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
-__global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM) : 1)
+__global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * WK * WM * NMAT) : 1)
     qmm_affine_kernel(const QmmParams p) {
   static_assert(NT == 1 || TT == 8, "token tiles beyond the first are full");
   constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
-  constexpr int NTH = 32 * WK * WM;
+  constexpr int NTH = 32 * WK * WM * NMAT;
   constexpr int RC = 8 * NT;
   extern __shared__ __align__(16) unsigned char smem[];
 
@@ -192,7 +190,8 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
   const int lane = tid & 31;
   const int wid = tid >> 5;
   const int wk = wid % WK;
-  const int wm = wid / WK;
+  const int mat = (wid / WK) % NMAT;
+  const int wm = wid / (WK * NMAT);
   const int g = lane >> 2;
   const int tig = lane & 3;
   // column g of the B operand is (slot g / TT, token g % TT)
@@ -222,13 +221,10 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
     const int n_lo = min(n_cta + wm * 16 + g, N - 1);
     const int n_hi = min(n_cta + wm * 16 + g + 8, N - 1);
 
-    const uint32_t* wrow[NMAT][2];
-#pragma unroll
-    for (int m = 0; m < NMAT; ++m) {
-      const uint32_t* we = p.w[m] + (size_t)e * N * K8;
-      wrow[m][0] = we + (size_t)n_lo * K8 + tig * 2;
-      wrow[m][1] = we + (size_t)n_hi * K8 + tig * 2;
-    }
+    const uint32_t* wmat = (NMAT == 2 && mat) ? p.w[1] : p.w[0];
+    const uint32_t* we = wmat + (size_t)e * N * K8;
+    const uint32_t* wrow0 = we + (size_t)n_lo * K8 + tig * 2 + wk * 32;
+    const uint32_t* wrow1 = we + (size_t)n_hi * K8 + tig * 2 + wk * 32;
 
     for (int rc = 0; rc < cnt; rc += p.rs) {
       const int nrow = min(p.rs, cnt - rc);
@@ -237,22 +233,14 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
       first_pass = false;
 
       // ---- (1) prefetch the first two quads (8 groups) of packed weights into registers
-      const uint32_t* wp[NMAT][2];  // this warp's next quad to fetch, per matrix and row half
-#pragma unroll
-      for (int m = 0; m < NMAT; ++m) {
-        wp[m][0] = wrow[m][0] + wk * 32;
-        wp[m][1] = wrow[m][1] + wk * 32;
-      }
-      uint2 wbuf[2][4][NMAT][2];
+      const uint32_t* wp[2] = {wrow0, wrow1};  // this warp's next quad to fetch, per row half
+      uint2 wbuf[2][4][2];
 #pragma unroll
       for (int bq = 0; bq < 2; ++bq) {
         if (bq < nq_w) {
-          load_quad<NMAT, FULLQ>(wbuf[bq], wp, (wk + bq * WK) * 4, ngroups);
-#pragma unroll
-          for (int m = 0; m < NMAT; ++m) {
-            wp[m][0] += WK * 32;
-            wp[m][1] += WK * 32;
-          }
+          load_quad<FULLQ>(wbuf[bq], wp, (wk + bq * WK) * 4, ngroups);
+          wp[0] += WK * 32;
+          wp[1] += WK * 32;
         }
       }
 
@@ -318,21 +306,23 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
       cp_async_wait_all();
       __syncthreads();
 
-      // ---- (4) main loop over this warp's groups
-      float acc[NMAT][NT][4];
-      float dg[NMAT][NT][4];
+      // ---- (4) main loop over this warp's quads
+      float acc[NT][4];
+      float dg[NT][4];
 #pragma unroll
-      for (int m = 0; m < NMAT; ++m)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[m][nt][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
 
       // per-lane shared-memory bases: token row (or the zero page) and the scale rows
       const int xlane = lay.xs + ((TT == 8) ? g : tok_g) * xs_stride + tig * 32;  // byte offsets into smem
       const int zpage = lay.zero;
       const bool tok_ok = ((TT == 8) ? g : tok_g) < nrow;
+      const unsigned char* srow = sraw + ((mat * 2 + 0) * 16 * WM + wm * 16 + g) * sc_stride;
+      const unsigned char* brow = sraw + ((mat * 2 + 1) * 16 * WM + wm * 16 + g) * sc_stride;
 
+      uint32_t kMask, kMagic;  // opaque to the compiler: keeps them in registers
+      asm volatile("mov.b32 %0, 0x000F000F; mov.b32 %1, 0x43004300;" : "=r"(kMask), "=r"(kMagic));
       for (int qi = 0; qi < nq_w; qi += 2) {
 #pragma unroll
         for (int bq = 0; bq < 2; ++bq) {
@@ -345,11 +335,9 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
               const int G = quad * 4 + j;
               if (slot == 0) {
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m)
+                for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) dg[m][nt][jj] = 0.0f;
+                  for (int jj = 0; jj < 4; ++jj) dg[nt][jj] = 0.0f;
               }
               if (FULLQ || G < ngroups) {
                 uint4 xb[NT][2];
@@ -360,101 +348,108 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
                   xb[nt][0] = *reinterpret_cast<const uint4*>(smem + xo);
                   xb[nt][1] = *reinterpret_cast<const uint4*>(smem + xo + 16);
                 }
+                const uint2 wa = wbuf[bq][j][0];
+                const uint2 wb = wbuf[bq][j][1];
+                {
+                  const uint32_t a0 = deq_pair<0>(wa.x, kMask, kMagic), a1 = deq_pair<0>(wb.x, kMask, kMagic);
+                  const uint32_t a2 = deq_pair<4>(wa.x, kMask, kMagic), a3 = deq_pair<4>(wb.x, kMask, kMagic);
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                  const uint2 wa = wbuf[bq][j][m][0];
-                  const uint2 wb = wbuf[bq][j][m][1];
-                  {
-                    const uint32_t a0 = deq_pair<0>(wa.x), a1 = deq_pair<0>(wb.x);
-                    const uint32_t a2 = deq_pair<4>(wa.x), a3 = deq_pair<4>(wb.x);
+                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
+                }
+                {
+                  const uint32_t a0 = deq_pair<8>(wa.x, kMask, kMagic), a1 = deq_pair<8>(wb.x, kMask, kMagic);
+                  const uint32_t a2 = deq_pair<12>(wa.x, kMask, kMagic), a3 = deq_pair<12>(wb.x, kMask, kMagic);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
-                  }
-                  {
-                    const uint32_t a0 = deq_pair<8>(wa.x), a1 = deq_pair<8>(wb.x);
-                    const uint32_t a2 = deq_pair<12>(wa.x), a3 = deq_pair<12>(wb.x);
+                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
+                }
+                {
+                  const uint32_t a0 = deq_pair<0>(wa.y, kMask, kMagic), a1 = deq_pair<0>(wb.y, kMask, kMagic);
+                  const uint32_t a2 = deq_pair<4>(wa.y, kMask, kMagic), a3 = deq_pair<4>(wb.y, kMask, kMagic);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
-                  }
-                  {
-                    const uint32_t a0 = deq_pair<0>(wa.y), a1 = deq_pair<0>(wb.y);
-                    const uint32_t a2 = deq_pair<4>(wa.y), a3 = deq_pair<4>(wb.y);
+                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
+                }
+                {
+                  const uint32_t a0 = deq_pair<8>(wa.y, kMask, kMagic), a1 = deq_pair<8>(wb.y, kMask, kMagic);
+                  const uint32_t a2 = deq_pair<12>(wa.y, kMask, kMagic), a3 = deq_pair<12>(wb.y, kMask, kMagic);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
-                  }
-                  {
-                    const uint32_t a0 = deq_pair<8>(wa.y), a1 = deq_pair<8>(wb.y);
-                    const uint32_t a2 = deq_pair<12>(wa.y), a3 = deq_pair<12>(wb.y);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
-                  }
+                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
                 }
               }
               if (GPB <= 4 && slot == GPB - 1)
-                fixup_block<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig,
-                                                         (qi + bq) * 4 + j - (GPB - 1), nq_w, ngroups);
+                fixup_block<NT, TT, WK, FULLQ>(acc, dg, xsum, srow, brow, sc_stride, wk, tig,
+                                               (qi + bq) * 4 + j - (GPB - 1), nq_w, ngroups);
             }
             // refill this pipeline slot with the quad two steps ahead
             if (qi + bq + 2 < nq_w) {
-              load_quad<NMAT, FULLQ>(wbuf[bq], wp, (quad + 2 * WK) * 4, ngroups);
-#pragma unroll
-              for (int m = 0; m < NMAT; ++m) {
-                wp[m][0] += WK * 32;
-                wp[m][1] += WK * 32;
-              }
+              load_quad<FULLQ>(wbuf[bq], wp, (quad + 2 * WK) * 4, ngroups);
+              wp[0] += WK * 32;
+              wp[1] += WK * 32;
             }
           }
         }
         if (GPB == 8)
-          fixup_block<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig, qi * 4, nq_w,
-                                                   ngroups);
+          fixup_block<NT, TT, WK, FULLQ>(acc, dg, xsum, srow, brow, sc_stride, wk, tig, qi * 4, nq_w, ngroups);
       }
 
-      // ---- (5) reduce the K-split across warps (fixed order)
-      if (WK > 1) {
+      // ---- (5) gather the K-split and the two matrices in the first warp of each row tile (fixed order)
+      float accu[NT][4];  // the second matrix (up) when NMAT == 2
+      if (WK * NMAT > 1) {
         __syncthreads();  // every warp is done reading the staged rows; reuse their space
-        float* mine = red + ((wm * WK + wk) * 32 + lane) * (NMAT * NT * 4);
+        float* mine = red + (wid * 32 + lane) * (NT * 4);
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mine[nt * 4 + j] = acc[nt][j];
+        __syncthreads();
+        if (wk == 0 && mat == 0) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) mine[(m * NT + nt) * 4 + j] = acc[m][nt][j];
-        __syncthreads();
-        if (wk == 0) {
+            for (int j = 0; j < 4; ++j) accu[nt][j] = 0.0f;
 #pragma unroll
-          for (int o = 1; o < WK; ++o) {
-            const float* other = red + ((wm * WK + o) * 32 + lane) * (NMAT * NT * 4);
+          for (int mm = 0; mm < NMAT; ++mm) {
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m)
+            for (int o = 0; o < WK; ++o) {
+              if (mm == 0 && o == 0) continue;
+              const float* other = red + ((((wm * NMAT) + mm) * WK + o) * 32 + lane) * (NT * 4);
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[m][nt][j] += other[(m * NT + nt) * 4 + j];
+                for (int j = 0; j < 4; ++j) {
+                  if (mm == 0)
+                    acc[nt][j] += other[nt * 4 + j];
+                  else
+                    accu[nt][j] += other[nt * 4 + j];
+                }
+            }
           }
         }
       }
-      if (wk == 0) {
+      if (wk == 0 && mat == 0) {
         // ---- (6) fold the multiplexed columns back onto their tokens (fixed order), then the epilogue
         if (TT < 8) {
 #pragma unroll
-          for (int m = 0; m < NMAT; ++m) {
+          for (int mm = 0; mm < NMAT; ++mm) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+              float v0 = mm ? accu[0][h * 2] : acc[0][h * 2];
+              float v1 = mm ? accu[0][h * 2 + 1] : acc[0][h * 2 + 1];
               if (TT == 1) {
-                acc[m][0][h * 2] += acc[m][0][h * 2 + 1];
-                acc[m][0][h * 2 + 1] = 0.0f;
+                v0 += v1;
+                v1 = 0.0f;
               }
-#pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                float v = acc[m][0][h * 2 + c];
-                if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                acc[m][0][h * 2 + c] = v;
+              if (TT <= 2) v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+              v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+              if (TT > 1) {
+                if (TT <= 2) v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+              }
+              if (mm) {
+                accu[0][h * 2] = v0;
+                accu[0][h * 2 + 1] = v1;
+              } else {
+                acc[0][h * 2] = v0;
+                acc[0][h * 2 + 1] = v1;
               }
             }
           }
@@ -470,10 +465,10 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
             if (writer && t < nrow && n < N) {
               float v;
               if (NMAT == 2) {
-                v = (p.epilogue == 2) ? swiglu_per_op(acc[0][nt][j], acc[NMAT - 1][nt][j])
-                                      : swiglu_cpu_contract(acc[0][nt][j], acc[NMAT - 1][nt][j]);
+                v = (p.epilogue == 2) ? swiglu_per_op(acc[nt][j], accu[nt][j])
+                                      : swiglu_cpu_contract(acc[nt][j], accu[nt][j]);
               } else {
-                v = acc[0][nt][j];
+                v = acc[nt][j];
               }
               const int dst = pv.row_dst[off + rc + t];
               p.out[(size_t)dst * p.ldo + n] = __float2bfloat16_rn(v);
@@ -519,7 +514,7 @@ static int launch_full(const QmmParams& p, int max_groups, cudaStream_t st) {
       return fail(ZMOE_ERR_CUDA, "qmm: shared memory of %d bytes refused: %s", lay.total, cudaGetErrorString(e));
   }
   dim3 grid((p.N + 16 * WM - 1) / (16 * WM), max_groups);
-  kern<<<grid, 32 * WK * WM, lay.total, st>>>(p);
+  kern<<<grid, 32 * WK * WM * NMAT, lay.total, st>>>(p);
   return check_launch("qmm_affine_kernel");
 }
 
