@@ -209,7 +209,7 @@ def main() -> None:
     def step_eager():
         h = x_dev
         for ly in layers:
-            h = ly.forward(x_dev)  # every layer sees the same token rows: layers are independent work units
+            h = ly.forward(h)  # layer i+1 routes and computes on layer i's output: a true dependency chain
         return h
 
     # --- distinct experts touched per step (for the algorithmic byte count), from one eager pass
@@ -240,8 +240,8 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    # launches per step: router linear, router top-k, plan, gate/up, down, combine (+3 for a shared expert)
-    launches_per_layer = 6 + (3 if cfg.n_shared else 0)
+    # launches per layer: fused router (linear + top-k + plan), gate/up, down, combine (+3 for a shared expert)
+    launches_per_layer = 4 + (3 if cfg.n_shared else 0)
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
@@ -305,7 +305,7 @@ def main() -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_step": alg_bytes_step,
-                         "note": "whole layer pass (6 kernels); per-kernel figures in profiles/"},
+                         "note": "whole layer pass (4 kernels); per-kernel figures in profiles/"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
                     "d2h_bytes_per_step": T * cfg.d_model * 2},
             "gpu_launches": launches_per_layer * L * args.steps,

@@ -113,6 +113,20 @@ int zmoe_router_sigmoid_bias_topk(const void* logits, int logits_dtype, int T, i
 int zmoe_router_logits(const void* x, const void* wr, int T, int E, int d, void* logits, int out_dtype,
                        void* stream);
 
+/*
+ * Fused router for one MoE block: router linear (T logits, as above), the family's top-k and
+ * the token-sorted expert plan over the T*K (token, slot) pairs, in ONE launch.
+ * family 0: top-k of logits then softmax (moe.py:1287-1315); 1: softmax then top-k with
+ * `renorm` as in zmoe_router_softmax_topk (moe_mlp.py:260-266); 2: sigmoid + bias with
+ * n_group / topk_group / scale as in zmoe_router_sigmoid_bias_topk.  Replaces the gate call and
+ * `_gating` of the patched block (moe_mlp.py:202-289) on the fused-layer path.
+ * logits (T, E) T is written as a by-product; plan may be NULL; counter is one int of device
+ * memory that must be zero before the first call (the kernel leaves it zero).
+ */
+int zmoe_route(const void* x, const void* wr, int T, int E, int d, int K, int family, const float* bias, int renorm,
+               int n_group, int topk_group, float scale, void* logits, float* weights, uint32_t* indices, void* plan,
+               size_t plan_bytes, int* counter, void* stream);
+
 /* --------------------------------------------------- token-sorted expert plan */
 
 /*

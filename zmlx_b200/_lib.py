@@ -39,6 +39,8 @@ SIGNATURES = {
     "zmoe_router_sigmoid_bias_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float,
                                               c_void_p, c_void_p, c_void_p]),
     "zmoe_router_logits": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "zmoe_route": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "zmoe_plan_bytes": (c_size_t, [c_int, c_int]),
     "zmoe_build_plan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "zmoe_gather_qmm_swiglu": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

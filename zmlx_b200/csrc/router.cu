@@ -5,6 +5,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "plan.cuh"
 
 namespace zmoe {
 
@@ -53,14 +54,12 @@ __device__ __forceinline__ void warp_topk_masked(float (&v)[VPL], int E, int K, 
   }
 }
 
+// One warp routes one token row (softmax family); see zmoe_router_softmax_topk.
 template <int VPL>
-__global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
-                                                           int K, int flavour, const float* __restrict__ bias,
-                                                           int renorm, float* __restrict__ weights,
-                                                           uint32_t* __restrict__ indices) {
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= T) return;
+__device__ __forceinline__ void softmax_topk_row(const void* __restrict__ logits, int dtype, int row, int E, int K,
+                                                 int flavour, const float* __restrict__ bias, int renorm,
+                                                 float* __restrict__ weights, uint32_t* __restrict__ indices,
+                                                 int lane) {
   float v[VPL];
   float mx = -CUDART_INF_F;
 #pragma unroll
@@ -117,21 +116,27 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restric
   }
 }
 
+template <int VPL>
+__global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
+                                                           int K, int flavour, const float* __restrict__ bias,
+                                                           int renorm, float* __restrict__ weights,
+                                                           uint32_t* __restrict__ indices) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= T) return;
+  softmax_topk_row<VPL>(logits, dtype, row, E, K, flavour, bias, renorm, weights, indices, lane);
+}
+
 // sigmoid + selection bias, optional group-limited selection.  Per-warp shared
 // scratch holds the E scores so that one lane per group can scan its group.
+// One warp routes one token row (sigmoid family); `sc` is E + 64 floats of scratch owned by the warp.
 template <int VPL>
-__global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
-                                                           int K, const float* __restrict__ bias, int n_group,
-                                                           int topk_group, float scale, float* __restrict__ weights,
-                                                           uint32_t* __restrict__ indices) {
-  extern __shared__ float sm[];
-  const int lane = threadIdx.x & 31;
-  const int wid = threadIdx.x >> 5;
-  const int row = blockIdx.x * (blockDim.x >> 5) + wid;
-  float* sc = sm + (size_t)wid * (E + 64);  // E scores, then 32 group scores, then 32 keep flags
+__device__ __forceinline__ void sigmoid_topk_row(const void* __restrict__ logits, int dtype, int row, int E, int K,
+                                                 const float* __restrict__ bias, int n_group, int topk_group,
+                                                 float scale, float* __restrict__ weights,
+                                                 uint32_t* __restrict__ indices, int lane, float* sc) {
   float* gsc = sc + E;
   float* gkeep = gsc + 32;
-  if (row >= T) return;
   float v[VPL];
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
@@ -201,6 +206,20 @@ __global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restric
   }
 }
 
+template <int VPL>
+__global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E,
+                                                           int K, const float* __restrict__ bias, int n_group,
+                                                           int topk_group, float scale, float* __restrict__ weights,
+                                                           uint32_t* __restrict__ indices) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + wid;
+  if (row >= T) return;
+  sigmoid_topk_row<VPL>(logits, dtype, row, E, K, bias, n_group, topk_group, scale, weights, indices, lane,
+                        sm + (size_t)wid * (E + 64));
+}
+
 // Router linear.  One warp per (expert, token tile of 8): 16-byte loads of the
 // expert's weight row, the token rows come from L1/L2.
 __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
@@ -252,6 +271,89 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16*
         reinterpret_cast<__nv_bfloat16*>(logits)[o] = __float2bfloat16_rn(s);
     }
   }
+}
+
+// Fused router: router linear for all tokens, then -- in the CTA that finishes last -- the
+// family's top-k for every token and the token-sorted expert plan.  One launch replaces the
+// router matmul, the top-k kernel and the plan kernel.  `counter` is one int of device memory
+// that is zero before the first launch; the last CTA leaves it zero again.
+struct RouteParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* wr;
+  int T, E, d, K;
+  int family;  // 0: top-k of logits then softmax; 1: softmax then top-k; 2: sigmoid + bias
+  const float* bias;
+  int renorm, n_group, topk_group;
+  float scale;
+  __nv_bfloat16* logits;  // (T, E) scratch / output
+  float* weights;
+  uint32_t* indices;
+  int* plan;
+  int* counter;
+};
+
+template <int VPL>
+__global__ void __launch_bounds__(128) route_fused_kernel(const RouteParams p) {
+  extern __shared__ int route_sm[];
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int T = p.T, E = p.E, d = p.d;
+  // ---- phase 1: one warp per expert row, token tiles of 8
+  const int e = blockIdx.x * 4 + wid;
+  if (e < E) {
+    const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
+    const int nvec = d >> 3;
+    for (int t0 = 0; t0 < T; t0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
+      for (int i = lane; i < nvec; i += 32) {
+        const uint4 wv = __ldg(wrow + i);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          if (t0 + t < T) {
+            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)(t0 + t) * d) + i);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc[t] = fmaf(bf16_bits_to_float(ww[q] & 0xffffu), bf16_bits_to_float(xw[q] & 0xffffu), acc[t]);
+              acc[t] = fmaf(bf16_bits_to_float(ww[q] >> 16), bf16_bits_to_float(xw[q] >> 16), acc[t]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float sres = warp_sum(acc[t]);
+        if (lane == 0 && t0 + t < T) p.logits[(size_t)(t0 + t) * E + e] = __float2bfloat16_rn(sres);
+      }
+    }
+  }
+  // ---- last CTA done?
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(p.counter, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // ---- phase 2: top-k of every token row (one warp per row)
+  float* scratch = reinterpret_cast<float*>(route_sm);
+  for (int row = wid; row < T; row += 4) {
+    if (p.family == 2)
+      sigmoid_topk_row<VPL>(p.logits, ZMOE_BF16, row, E, p.K, p.bias, p.n_group, p.topk_group, p.scale, p.weights,
+                            p.indices, lane, scratch + (size_t)wid * (E + 64));
+    else
+      softmax_topk_row<VPL>(p.logits, ZMOE_BF16, row, E, p.K,
+                            p.family == 0 ? ZMOE_ROUTER_TOPK_THEN_SOFTMAX : ZMOE_ROUTER_SOFTMAX_THEN_TOPK, p.bias,
+                            p.renorm, p.weights, p.indices, lane);
+  }
+  __syncthreads();
+  // ---- phase 3: plan over the (token, slot) pairs; pair p reads token row p / K
+  if (p.plan)
+    build_plan_block<128>(nullptr, p.K, reinterpret_cast<const int*>(p.indices), T * p.K, 1, E, p.plan, route_sm);
+  if (threadIdx.x == 0) *p.counter = 0;
 }
 
 template <typename F>
@@ -335,6 +437,57 @@ int zmoe_router_logits(const void* x, const void* wr, int T, int E, int d, void*
   router_logits_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wr, T,
                                                                  E, d, logits, out_dtype);
   return check_launch("zmoe_router_logits");
+}
+
+int zmoe_route(const void* x, const void* wr, int T, int E, int d, int K, int family, const float* bias, int renorm,
+               int n_group, int topk_group, float scale, void* logits, float* weights, uint32_t* indices, void* plan,
+               size_t plan_bytes, int* counter, void* stream) {
+  ZMOE_REQUIRE(x && wr && logits && weights && indices && counter, ZMOE_ERR_SHAPE, "zmoe_route: null pointer");
+  ZMOE_REQUIRE(T >= 0 && E >= 1 && d >= 8 && K >= 1 && K <= E, ZMOE_ERR_SHAPE,
+               "zmoe_route: bad sizes T=%d E=%d d=%d K=%d", T, E, d, K);
+  ZMOE_REQUIRE(d % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)wr % 16) == 0, ZMOE_ERR_ALIGN,
+               "zmoe_route: x and wr rows must be 16-byte aligned");
+  ZMOE_REQUIRE(E <= 32 * kMaxVPL && K <= kMaxK, ZMOE_ERR_UNSUPPORTED, "zmoe_route: E=%d or K=%d beyond limits", E, K);
+  ZMOE_REQUIRE(family >= 0 && family <= 2, ZMOE_ERR_UNSUPPORTED, "zmoe_route: family %d", family);
+  if (family == 2) {
+    ZMOE_REQUIRE(bias != nullptr, ZMOE_ERR_SHAPE, "zmoe_route: the sigmoid router needs a bias");
+    ZMOE_REQUIRE(n_group >= 1 && n_group <= 32 && topk_group >= 1 && topk_group <= n_group && E % n_group == 0,
+                 ZMOE_ERR_SHAPE, "zmoe_route: invalid n_group=%d / topk_group=%d", n_group, topk_group);
+  }
+  if (plan) {
+    ZMOE_REQUIRE(E <= 4096 && (long long)T * K < (1ll << 24), ZMOE_ERR_UNSUPPORTED, "zmoe_route: plan too large");
+    ZMOE_REQUIRE(plan_bytes >= zmoe_plan_bytes(T * K, E), ZMOE_ERR_WORKSPACE,
+                 "zmoe_route: plan buffer of %zu bytes, need %zu", plan_bytes, zmoe_plan_bytes(T * K, E));
+  }
+  if (T == 0) return ZMOE_OK;
+  RouteParams p;
+  p.x = (const __nv_bfloat16*)x;
+  p.wr = (const __nv_bfloat16*)wr;
+  p.T = T;
+  p.E = E;
+  p.d = d;
+  p.K = K;
+  p.family = family;
+  p.bias = bias;
+  p.renorm = renorm;
+  p.n_group = n_group;
+  p.topk_group = topk_group;
+  p.scale = scale;
+  p.logits = (__nv_bfloat16*)logits;
+  p.weights = weights;
+  p.indices = indices;
+  p.plan = (int*)plan;
+  p.counter = counter;
+  size_t smem_plan = (size_t)(2 * E + 128) * sizeof(int);
+  size_t smem_sig = 4 * (size_t)(E + 64) * sizeof(float);
+  size_t smem = smem_plan > smem_sig ? smem_plan : smem_sig;
+  dim3 grid((E + 3) / 4), block(128);
+  cudaStream_t st = (cudaStream_t)stream;
+  dispatch_vpl(E, [&](auto vpl) {
+    route_fused_kernel<decltype(vpl)::value><<<grid, block, smem, st>>>(p);
+    return 0;
+  });
+  return check_launch("zmoe_route");
 }
 
 }  // extern "C"

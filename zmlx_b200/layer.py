@@ -46,6 +46,7 @@ class MoELayer:
         self.weights = torch.empty((T, K), dtype=f32, device=dev)
         self.indices = torch.empty((T, K), dtype=i32, device=dev)
         self.plan = torch.empty(ops.plan_bytes(T * K, cfg.n_experts) // 4, dtype=i32, device=dev)
+        self.counter = torch.zeros(1, dtype=i32, device=dev)
         self.h = torch.empty((T * K, cfg.d_ff), dtype=bf, device=dev)
         self.y = torch.empty((T * K, cfg.d_model), dtype=bf, device=dev)
         self.out = torch.empty((T, cfg.d_model), dtype=bf, device=dev)
@@ -56,39 +57,51 @@ class MoELayer:
             self.sh_y = torch.empty((T, cfg.d_model), dtype=bf, device=dev)
 
     # -- steps -------------------------------------------------------------
+    def _route_args(self):
+        cfg = self.cfg
+        bias = self.p.get("expert_bias")
+        if cfg.family == "generic":
+            if bias is None and cfg.norm_topk_prob:
+                return 0, None, 0
+            return 1, bias, (1 if cfg.norm_topk_prob else 0)
+        if cfg.family == "qwen3":
+            return 1, None, (2 if cfg.norm_topk_prob else 0)
+        return 2, bias, 0
+
     def route(self, x: torch.Tensor):
-        """Router linear (bf16 logits) and the family's top-k; fills weights/indices."""
+        """Router linear (bf16 logits), the family's top-k and the expert plan, in one launch."""
         cfg = self.cfg
         T = x.shape[0]
-        lib = _lib.load()
-        st = ops._stream()
         p = ops._ptr
-        _lib.check(lib.zmoe_router_logits(p(x), p(self.p["router_w"]), T, cfg.n_experts, cfg.d_model,
-                                          p(self.logits), _lib.BF16, st))
-        if cfg.family == "generic":
-            norm = cfg.norm_topk_prob
-            bias = self.p.get("expert_bias")
-            if bias is None and norm:
-                rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
-                                                  _lib.ROUTER_TOPK_THEN_SOFTMAX, None, 0, p(self.weights),
-                                                  p(self.indices), st)
+        family, bias, renorm = self._route_args()
+        lib = _lib.load()
+        if T > 8:
+            # many rows: separate launches, one warp per token row across many CTAs
+            st = ops._stream()
+            _lib.check(lib.zmoe_router_logits(p(x), p(self.p["router_w"]), T, cfg.n_experts, cfg.d_model,
+                                              p(self.logits), _lib.BF16, st))
+            if family == 2:
+                rc = lib.zmoe_router_sigmoid_bias_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k, p(bias),
+                                                       cfg.n_group, cfg.topk_group,
+                                                       ctypes.c_float(cfg.routed_scaling_factor), p(self.weights),
+                                                       p(self.indices), st)
             else:
                 rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
-                                                  _lib.ROUTER_SOFTMAX_THEN_TOPK, p(bias), 1 if norm else 0,
+                                                  _lib.ROUTER_TOPK_THEN_SOFTMAX if family == 0
+                                                  else _lib.ROUTER_SOFTMAX_THEN_TOPK, p(bias), renorm,
                                                   p(self.weights), p(self.indices), st)
-        elif cfg.family == "qwen3":
-            rc = lib.zmoe_router_softmax_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
-                                              _lib.ROUTER_SOFTMAX_THEN_TOPK, None, 2 if cfg.norm_topk_prob else 0,
-                                              p(self.weights), p(self.indices), st)
-        else:
-            rc = lib.zmoe_router_sigmoid_bias_topk(p(self.logits), _lib.BF16, T, cfg.n_experts, cfg.top_k,
-                                                   p(self.p["expert_bias"]), cfg.n_group, cfg.topk_group,
-                                                   ctypes.c_float(cfg.routed_scaling_factor), p(self.weights),
-                                                   p(self.indices), st)
-        _lib.check(rc)
+            _lib.check(rc)
+            _lib.check(lib.zmoe_build_plan(None, cfg.top_k, p(self.indices), T * cfg.top_k, 1, cfg.n_experts,
+                                           p(self.plan), self.plan.numel() * 4, st))
+            return
+        _lib.check(lib.zmoe_route(
+            p(x), p(self.p["router_w"]), T, cfg.n_experts, cfg.d_model, cfg.top_k, family, p(bias), renorm,
+            cfg.n_group, cfg.topk_group, ctypes.c_float(cfg.routed_scaling_factor if family == 2 else 1.0),
+            p(self.logits), p(self.weights), p(self.indices), p(self.plan), self.plan.numel() * 4, p(self.counter),
+            ops._stream()))
 
     def experts(self, x: torch.Tensor):
-        """Plan, fused gate/up + SwiGLU, down projection for all (token, slot) pairs."""
+        """Fused gate/up + SwiGLU and the down projection for all (token, slot) pairs (plan from route())."""
         cfg = self.cfg
         T = x.shape[0]
         K = cfg.top_k
@@ -97,8 +110,6 @@ class MoELayer:
         p = ops._ptr
         qm = ops.qmode_code(cfg.mode)
         W = self.p
-        _lib.check(lib.zmoe_build_plan(None, K, p(self.indices), T * K, 1, cfg.n_experts, p(self.plan),
-                                       self.plan.numel() * 4, st))
         _lib.check(lib.zmoe_gather_qmm_swiglu(p(x), T, x.stride(0), p(W["gate_w"]), p(W["gate_s"]), p(W["gate_b"]),
                                               p(W["up_w"]), p(W["up_s"]), p(W["up_b"]), cfg.n_experts, cfg.d_ff,
                                               cfg.d_model, self.gs, qm, p(self.plan), T * K, T, p(self.h),
