@@ -162,7 +162,9 @@ int zmoe_gather_qmm_swiglu(const void* x, int x_rows, int ldx, const uint32_t* g
  * Replaces the third-party op at its call sites moe.py:1219-1229, 2147-2157 and
  * moe_mlp.py:571-574 (switch_mlp.down_proj).  With x_by_output_row != 0 output row r
  * reads x row r (the down projection after gather_qmm_swiglu, whose output rows are
- * already one per pair) instead of the plan's lhs row.
+ * already one per pair) instead of the plan's lhs row (bit 0).  Bit 1 of x_by_output_row
+ * declares that the plan was written before the kernel that produced x started; the call
+ * may then stream its first weights while that kernel is still running.
  */
 int zmoe_gather_qmm(const void* x, int x_rows, int ldx, const uint32_t* w, const void* scales, const void* biases,
                     int E, int N, int K, int group_size, int qmode, const void* plan, int rows, int rows_hint,

@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(kPlanThreads) build_plan_kernel(const int* __r
                                                                   const int* __restrict__ rhs, int P, int M, int E,
                                                                   int* plan_base) {
   extern __shared__ int sm[];
+  pdl_wait();
+  pdl_trigger();
   build_plan_block<kPlanThreads>(lhs, lhs_div, rhs, P, M, E, plan_base, sm);
 }
 
@@ -63,7 +65,8 @@ int zmoe_build_plan(const int32_t* lhs, int lhs_div, const int32_t* rhs, int P, 
   ZMOE_REQUIRE(plan_bytes >= zmoe_plan_bytes(P * M, E), ZMOE_ERR_WORKSPACE,
                "zmoe_build_plan: plan buffer of %zu bytes, need %zu", plan_bytes, zmoe_plan_bytes(P * M, E));
   size_t smem = (size_t)(2 * E + kPlanThreads) * sizeof(int);
-  build_plan_kernel<<<1, kPlanThreads, smem, (cudaStream_t)stream>>>(lhs, lhs_div, rhs, P, M, E, (int*)plan);
+  launch_pdl(build_plan_kernel, dim3(1), dim3(kPlanThreads), smem, (cudaStream_t)stream, lhs, lhs_div, rhs, P, M, E,
+             (int*)plan);
   return check_launch("zmoe_build_plan");
 }
 

@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const void* __restrict__ y
                                                       const void* __restrict__ w, int w_dtype, int T, int K, int D,
                                                       void* __restrict__ out, int out_t,
                                                       const __nv_bfloat16* __restrict__ residual) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.y;
   const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (d >= D) return;
@@ -91,7 +93,7 @@ int combine_launch(const void* y, int y_dtype, const void* w, int w_dtype, int T
   cudaStream_t st = (cudaStream_t)stream;
   const __nv_bfloat16* res = (const __nv_bfloat16*)residual;
 #define ZMOE_LAUNCH(M) \
-  combine_kernel<M><<<grid, block, 0, st>>>(y, y_dtype, w, w_dtype, T, K, D, out, out_t, res)
+  launch_pdl(combine_kernel<M>, grid, block, 0, st, y, y_dtype, w, w_dtype, T, K, D, out, out_t, res)
   switch (mode) {
     case ZMOE_COMBINE_FP32: ZMOE_LAUNCH(ZMOE_COMBINE_FP32); break;
     case ZMOE_COMBINE_FP32_NO_FMA: ZMOE_LAUNCH(ZMOE_COMBINE_FP32_NO_FMA); break;

@@ -52,6 +52,30 @@ inline size_t plan_words(int rows, int E) {
   return 4 + 4 * (size_t)E + (size_t)(E + 1) + (size_t)E + 2 * (size_t)rows;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// Every libzmoe kernel is launched with the programmatic-stream-serialization attribute:
+// its CTAs may start while the previous kernel of the stream drains, and it calls
+// pdl_wait() before it touches anything that kernel may have written.  pdl_trigger()
+// lets the next kernel of the stream start in the same way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------- device helpers
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t h) { return __uint_as_float(h << 16); }
 

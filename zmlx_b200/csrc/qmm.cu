@@ -41,7 +41,7 @@ struct QmmSmem {
 __host__ __device__ inline QmmSmem qmm_smem(int K, int ngroups, int rs, int rc, int nmat, int wm, int wk, int nt) {
   QmmSmem m;
   int xs_bytes = rs * qmm_xs_stride(K);
-  int red_bytes = (wk * nmat > 1) ? wk * wm * nmat * 32 * nt * 4 * (int)sizeof(float) : 0;
+  int red_bytes = (wk > 1) ? wk * wm * 32 * nmat * nt * 4 * (int)sizeof(float) : 0;
   m.xs = 0;
   int a = xs_bytes > red_bytes ? xs_bytes : red_bytes;
   a = (a + 15) & ~15;
@@ -74,26 +74,76 @@ __device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src)
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// Loads one quad (4 consecutive groups: 32 bytes of each of the lane's two rows) into registers.
-template <bool FULLQ>
-__device__ __forceinline__ void load_quad(uint2 (&buf)[4][2], const uint32_t* (&wp)[2], int G0, int ngroups) {
+// codes at bits [sh, sh+4) and [sh+16, sh+20) -> bf16x2 (128+q_lo, 128+q_hi)
+template <int SH>
+__device__ __forceinline__ uint32_t deq_imm(uint32_t word) {
+  uint32_t r;
+  if (SH == 0) {
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(word));
+  } else {
+    asm("{ .reg .b32 t; shr.b32 t, %1, %2; lop3.b32 %0, t, 0x000F000F, 0x43004300, 0xEA; }"
+        : "=r"(r)
+        : "r"(word), "n"(SH));
+  }
+  return r;
+}
+
+// Loads one quad (4 consecutive groups: 32 bytes of each of the lane's rows) into registers.
+template <int NMAT, bool FULLQ>
+__device__ __forceinline__ void load_quad(uint2 (&buf)[4][NMAT][2], const uint32_t* (&wp)[NMAT][2], int G0,
+                                          int ngroups) {
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if (FULLQ || G0 + 0 < ngroups) buf[0][h] = ldg_stream_u2<0>(wp[h]);
-    if (FULLQ || G0 + 1 < ngroups) buf[1][h] = ldg_stream_u2<32>(wp[h]);
-    if (FULLQ || G0 + 2 < ngroups) buf[2][h] = ldg_stream_u2<64>(wp[h]);
-    if (FULLQ || G0 + 3 < ngroups) buf[3][h] = ldg_stream_u2<96>(wp[h]);
+  for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (FULLQ || G0 + 0 < ngroups) buf[0][m][h] = ldg_stream_u2<0>(wp[m][h]);
+      if (FULLQ || G0 + 1 < ngroups) buf[1][m][h] = ldg_stream_u2<32>(wp[m][h]);
+      if (FULLQ || G0 + 2 < ngroups) buf[2][m][h] = ldg_stream_u2<64>(wp[m][h]);
+      if (FULLQ || G0 + 3 < ngroups) buf[3][m][h] = ldg_stream_u2<96>(wp[m][h]);
+    }
   }
 }
 
-// Warp layout of a CTA: warp = ((wm * NMAT) + mat) * WK + wk.  Each warp streams one
-// matrix (gate or up) for 16 weight rows over its share of the K quads.
+// Applies scale, bias and the 128 offset to a block of 8/TT multiplexed groups whose first
+// item in the warp's stream is gi0.  Lane (g, tig) owns columns 2*tig and 2*tig+1.
 template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
-__global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * WK * WM * NMAT) : 1)
+__device__ __forceinline__ void fixup_multi(float (&acc)[NMAT][NT][4], const float (&dg)[NMAT][NT][4],
+                                            const float* xsum, const unsigned char* sraw, int sc_stride, int wk,
+                                            int wm, int g, int tig, int gi0, int nq_w, int ngroups) {
+  constexpr int RC = 8 * NT;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int col = 2 * tig + c;
+    const int gi_c = gi0 + ((TT == 8) ? 0 : col / TT);
+    const int G_c = (wk + (gi_c >> 2) * WK) * 4 + (gi_c & 3);
+    if ((gi_c >> 2) < nq_w && (FULLQ || G_c < ngroups)) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float X = xsum[G_c * RC + ((TT == 8) ? nt * 8 + col : col % TT)];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = wm * 16 + g + 8 * h;
+            const float sv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+                sraw + ((m * 2 + 0) * 16 * WM + r) * sc_stride + G_c * 2));
+            const float bv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+                sraw + ((m * 2 + 1) * 16 * WM + r) * sc_stride + G_c * 2));
+            const float cv = fmaf(-128.0f, sv, bv);
+            acc[m][nt][h * 2 + c] = fmaf(sv, dg[m][nt][h * 2 + c], fmaf(cv, X, acc[m][nt][h * 2 + c]));
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int NMAT, int NT, int TT, int WK, int WM, bool FULLQ>
+__global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM) : 1)
     qmm_affine_kernel(const QmmParams p) {
   static_assert(NT == 1 || TT == 8, "token tiles beyond the first are full");
   constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
-  constexpr int NTH = 32 * WK * WM * NMAT;
+  constexpr int NTH = 32 * WK * WM;
   constexpr int RC = 8 * NT;
   extern __shared__ __align__(16) unsigned char smem[];
 
@@ -101,8 +151,7 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
   const int lane = tid & 31;
   const int wid = tid >> 5;
   const int wk = wid % WK;
-  const int mat = (wid / WK) % NMAT;
-  const int wm = wid / (WK * NMAT);
+  const int wm = wid / WK;
   const int g = lane >> 2;
   const int tig = lane & 3;
   // column g of the B operand is (slot g / TT, token g % TT)
@@ -119,6 +168,12 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
   unsigned char* sraw = smem + lay.sc;
   float* red = reinterpret_cast<float*>(smem + lay.xs);
 
+  // With late_wait the caller vouches that the plan was written before the previous kernel started (so it is
+  // complete whenever this grid runs) and only the token rows come from the previous kernel: the first weights
+  // are then streamed before the dependency wait.
+  if (!p.late_wait) pdl_wait();
+  pdl_trigger();
+  bool waited = !p.late_wait;
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.rows, p.E);
   const int nq = (ngroups + 3) >> 2;
   const int nq_w = (nq > wk) ? (nq - wk + WK - 1) / WK : 0;
@@ -132,10 +187,13 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
     const int n_lo = min(n_cta + wm * 16 + g, N - 1);
     const int n_hi = min(n_cta + wm * 16 + g + 8, N - 1);
 
-    const uint32_t* wmat = (NMAT == 2 && mat) ? p.w[1] : p.w[0];
-    const uint32_t* we = wmat + (size_t)e * N * K8;
-    const uint32_t* wrow0 = we + (size_t)n_lo * K8 + tig * 2 + wk * 32;
-    const uint32_t* wrow1 = we + (size_t)n_hi * K8 + tig * 2 + wk * 32;
+    const uint32_t* wrow[NMAT][2];
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+      const uint32_t* we = p.w[m] + (size_t)e * N * K8;
+      wrow[m][0] = we + (size_t)n_lo * K8 + tig * 2;
+      wrow[m][1] = we + (size_t)n_hi * K8 + tig * 2;
+    }
 
     for (int rc = 0; rc < cnt; rc += p.rs) {
       const int nrow = min(p.rs, cnt - rc);
@@ -144,14 +202,22 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
       first_pass = false;
 
       // ---- (1) prefetch the first two quads (8 groups) of packed weights into registers
-      const uint32_t* wp[2] = {wrow0, wrow1};  // this warp's next quad to fetch, per row half
-      uint2 wbuf[2][4][2];
+      const uint32_t* wp[NMAT][2];  // this warp's next quad to fetch, per matrix and row half
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
+        wp[m][0] = wrow[m][0] + wk * 32;
+        wp[m][1] = wrow[m][1] + wk * 32;
+      }
+      uint2 wbuf[2][4][NMAT][2];
 #pragma unroll
       for (int bq = 0; bq < 2; ++bq) {
         if (bq < nq_w) {
-          load_quad<FULLQ>(wbuf[bq], wp, (wk + bq * WK) * 4, ngroups);
-          wp[0] += WK * 32;
-          wp[1] += WK * 32;
+          load_quad<NMAT, FULLQ>(wbuf[bq], wp, (wk + bq * WK) * 4, ngroups);
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+            wp[m][0] += WK * 32;
+            wp[m][1] += WK * 32;
+          }
         }
       }
 
@@ -182,6 +248,10 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
         }
       }
 
+      if (!waited) {
+        pdl_wait();
+        waited = true;
+      }
       // ---- (3) stage the token rows: 8-element blocks permuted to (0,4,1,5,2,6,3,7), plus group sums
       for (int t = 0; t < nrow; ++t) {
         const int src = p.x_by_dst ? pv.row_dst[off + rc + t] : pv.row_src[off + rc + t];
@@ -217,23 +287,21 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
       cp_async_wait_all();
       __syncthreads();
 
-      // ---- (4) main loop over this warp's quads
-      float acc[NT][4];
-      float dg[NT][4];
+      // ---- (4) main loop over this warp's groups
+      float acc[NMAT][NT][4];
+      float dg[NMAT][NT][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+      for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[m][nt][j] = 0.0f;
 
       // per-lane shared-memory bases: token row (or the zero page) and the scale rows
       const int xlane = lay.xs + ((TT == 8) ? g : tok_g) * xs_stride + tig * 32;  // byte offsets into smem
       const int zpage = lay.zero;
       const bool tok_ok = ((TT == 8) ? g : tok_g) < nrow;
-      const unsigned char* srow = sraw + ((mat * 2 + 0) * 16 * WM + wm * 16 + g) * sc_stride;
-      const unsigned char* brow = sraw + ((mat * 2 + 1) * 16 * WM + wm * 16 + g) * sc_stride;
 
-      uint32_t kMask, kMagic;  // opaque to the compiler: keeps them in registers
-      asm volatile("mov.b32 %0, 0x000F000F; mov.b32 %1, 0x43004300;" : "=r"(kMask), "=r"(kMagic));
       for (int qi = 0; qi < nq_w; qi += 2) {
 #pragma unroll
         for (int bq = 0; bq < 2; ++bq) {
@@ -246,9 +314,11 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
               const int G = quad * 4 + j;
               if (slot == 0) {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+                for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-                  for (int jj = 0; jj < 4; ++jj) dg[nt][jj] = 0.0f;
+                  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) dg[m][nt][jj] = 0.0f;
               }
               if (FULLQ || G < ngroups) {
                 uint4 xb[NT][2];
@@ -259,108 +329,101 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
                   xb[nt][0] = *reinterpret_cast<const uint4*>(smem + xo);
                   xb[nt][1] = *reinterpret_cast<const uint4*>(smem + xo + 16);
                 }
-                const uint2 wa = wbuf[bq][j][0];
-                const uint2 wb = wbuf[bq][j][1];
-                {
-                  const uint32_t a0 = deq_pair<0>(wa.x, kMask, kMagic), a1 = deq_pair<0>(wb.x, kMask, kMagic);
-                  const uint32_t a2 = deq_pair<4>(wa.x, kMask, kMagic), a3 = deq_pair<4>(wb.x, kMask, kMagic);
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
-                }
-                {
-                  const uint32_t a0 = deq_pair<8>(wa.x, kMask, kMagic), a1 = deq_pair<8>(wb.x, kMask, kMagic);
-                  const uint32_t a2 = deq_pair<12>(wa.x, kMask, kMagic), a3 = deq_pair<12>(wb.x, kMask, kMagic);
+                for (int m = 0; m < NMAT; ++m) {
+                  const uint2 wa = wbuf[bq][j][m][0];
+                  const uint2 wb = wbuf[bq][j][m][1];
+                  {
+                    const uint32_t a0 = deq_imm<0>(wa.x), a1 = deq_imm<0>(wb.x);
+                    const uint32_t a2 = deq_imm<4>(wa.x), a3 = deq_imm<4>(wb.x);
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
-                }
-                {
-                  const uint32_t a0 = deq_pair<0>(wa.y, kMask, kMagic), a1 = deq_pair<0>(wb.y, kMask, kMagic);
-                  const uint32_t a2 = deq_pair<4>(wa.y, kMask, kMagic), a3 = deq_pair<4>(wb.y, kMask, kMagic);
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].x, xb[nt][0].y);
+                  }
+                  {
+                    const uint32_t a0 = deq_imm<8>(wa.x), a1 = deq_imm<8>(wb.x);
+                    const uint32_t a2 = deq_imm<12>(wa.x), a3 = deq_imm<12>(wb.x);
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
-                }
-                {
-                  const uint32_t a0 = deq_pair<8>(wa.y, kMask, kMagic), a1 = deq_pair<8>(wb.y, kMask, kMagic);
-                  const uint32_t a2 = deq_pair<12>(wa.y, kMask, kMagic), a3 = deq_pair<12>(wb.y, kMask, kMagic);
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][0].z, xb[nt][0].w);
+                  }
+                  {
+                    const uint32_t a0 = deq_imm<0>(wa.y), a1 = deq_imm<0>(wb.y);
+                    const uint32_t a2 = deq_imm<4>(wa.y), a3 = deq_imm<4>(wb.y);
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) mma_bf16_m16n8k16(dg[nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].x, xb[nt][1].y);
+                  }
+                  {
+                    const uint32_t a0 = deq_imm<8>(wa.y), a1 = deq_imm<8>(wb.y);
+                    const uint32_t a2 = deq_imm<12>(wa.y), a3 = deq_imm<12>(wb.y);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_bf16_m16n8k16(dg[m][nt], a0, a1, a2, a3, xb[nt][1].z, xb[nt][1].w);
+                  }
                 }
               }
               if (GPB <= 4 && slot == GPB - 1)
-                fixup_block<NT, TT, WK, FULLQ>(acc, dg, xsum, srow, brow, sc_stride, wk, tig,
-                                               (qi + bq) * 4 + j - (GPB - 1), nq_w, ngroups);
+                fixup_multi<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig,
+                                                         (qi + bq) * 4 + j - (GPB - 1), nq_w, ngroups);
             }
             // refill this pipeline slot with the quad two steps ahead
             if (qi + bq + 2 < nq_w) {
-              load_quad<FULLQ>(wbuf[bq], wp, (quad + 2 * WK) * 4, ngroups);
-              wp[0] += WK * 32;
-              wp[1] += WK * 32;
+              load_quad<NMAT, FULLQ>(wbuf[bq], wp, (quad + 2 * WK) * 4, ngroups);
+#pragma unroll
+              for (int m = 0; m < NMAT; ++m) {
+                wp[m][0] += WK * 32;
+                wp[m][1] += WK * 32;
+              }
             }
           }
         }
         if (GPB == 8)
-          fixup_block<NT, TT, WK, FULLQ>(acc, dg, xsum, srow, brow, sc_stride, wk, tig, qi * 4, nq_w, ngroups);
+          fixup_multi<NMAT, NT, TT, WK, WM, FULLQ>(acc, dg, xsum, sraw, sc_stride, wk, wm, g, tig, qi * 4, nq_w,
+                                                   ngroups);
       }
 
-      // ---- (5) gather the K-split and the two matrices in the first warp of each row tile (fixed order)
-      float accu[NT][4];  // the second matrix (up) when NMAT == 2
-      if (WK * NMAT > 1) {
+      // ---- (5) reduce the K-split across warps (fixed order)
+      if (WK > 1) {
         __syncthreads();  // every warp is done reading the staged rows; reuse their space
-        float* mine = red + (wid * 32 + lane) * (NT * 4);
+        float* mine = red + ((wm * WK + wk) * 32 + lane) * (NMAT * NT * 4);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) mine[nt * 4 + j] = acc[nt][j];
-        __syncthreads();
-        if (wk == 0 && mat == 0) {
+        for (int m = 0; m < NMAT; ++m)
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) accu[nt][j] = 0.0f;
+            for (int j = 0; j < 4; ++j) mine[(m * NT + nt) * 4 + j] = acc[m][nt][j];
+        __syncthreads();
+        if (wk == 0) {
 #pragma unroll
-          for (int mm = 0; mm < NMAT; ++mm) {
+          for (int o = 1; o < WK; ++o) {
+            const float* other = red + ((wm * WK + o) * 32 + lane) * (NMAT * NT * 4);
 #pragma unroll
-            for (int o = 0; o < WK; ++o) {
-              if (mm == 0 && o == 0) continue;
-              const float* other = red + ((((wm * NMAT) + mm) * WK + o) * 32 + lane) * (NT * 4);
+            for (int m = 0; m < NMAT; ++m)
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (mm == 0)
-                    acc[nt][j] += other[nt * 4 + j];
-                  else
-                    accu[nt][j] += other[nt * 4 + j];
-                }
-            }
+                for (int j = 0; j < 4; ++j) acc[m][nt][j] += other[(m * NT + nt) * 4 + j];
           }
         }
       }
-      if (wk == 0 && mat == 0) {
+      if (wk == 0) {
         // ---- (6) fold the multiplexed columns back onto their tokens (fixed order), then the epilogue
         if (TT < 8) {
 #pragma unroll
-          for (int mm = 0; mm < NMAT; ++mm) {
+          for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              float v0 = mm ? accu[0][h * 2] : acc[0][h * 2];
-              float v1 = mm ? accu[0][h * 2 + 1] : acc[0][h * 2 + 1];
               if (TT == 1) {
-                v0 += v1;
-                v1 = 0.0f;
+                acc[m][0][h * 2] += acc[m][0][h * 2 + 1];
+                acc[m][0][h * 2 + 1] = 0.0f;
               }
-              if (TT <= 2) v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
-              v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
-              if (TT > 1) {
-                if (TT <= 2) v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-                v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-              }
-              if (mm) {
-                accu[0][h * 2] = v0;
-                accu[0][h * 2 + 1] = v1;
-              } else {
-                acc[0][h * 2] = v0;
-                acc[0][h * 2 + 1] = v1;
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                float v = acc[m][0][h * 2 + c];
+                if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                acc[m][0][h * 2 + c] = v;
               }
             }
           }
@@ -376,10 +439,10 @@ __global__ void __launch_bounds__(32 * WK * WM * NMAT, (NT == 1) ? 1024 / (32 * 
             if (writer && t < nrow && n < N) {
               float v;
               if (NMAT == 2) {
-                v = (p.epilogue == 2) ? swiglu_per_op(acc[nt][j], accu[nt][j])
-                                      : swiglu_cpu_contract(acc[nt][j], accu[nt][j]);
+                v = (p.epilogue == 2) ? swiglu_per_op(acc[0][nt][j], acc[NMAT - 1][nt][j])
+                                      : swiglu_cpu_contract(acc[0][nt][j], acc[NMAT - 1][nt][j]);
               } else {
-                v = acc[nt][j];
+                v = acc[0][nt][j];
               }
               const int dst = pv.row_dst[off + rc + t];
               p.out[(size_t)dst * p.ldo + n] = __float2bfloat16_rn(v);
@@ -425,7 +488,7 @@ static int launch_full(const QmmParams& p, int max_groups, cudaStream_t st) {
       return fail(ZMOE_ERR_CUDA, "qmm: shared memory of %d bytes refused: %s", lay.total, cudaGetErrorString(e));
   }
   dim3 grid((p.N + 16 * WM - 1) / (16 * WM), max_groups);
-  kern<<<grid, 32 * WK * WM * NMAT, lay.total, st>>>(p);
+  launch_pdl(kern, grid, dim3(32 * WK * WM), (size_t)lay.total, st, p);
   return check_launch("qmm_affine_kernel");
 }
 
@@ -496,10 +559,13 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
   p.K = K;
   p.ngroups = K / 64;
   p.epilogue = epilogue;
-  p.x_by_dst = x_by_dst;
+  p.x_by_dst = x_by_dst & 1;
+  p.late_wait = (x_by_dst & 2) ? 1 : 0;
 
-  static const bool no_stream = getenv("ZMOE_NO_STREAM") != nullptr;
-  if (!no_stream) {
+  // The shared-memory pipelined kernel is opt-in (ZMOE_STREAM=1): the register-pipelined kernel below is
+  // as fast or faster at decode sizes.
+  static const bool use_stream = getenv("ZMOE_STREAM") != nullptr && atoi(getenv("ZMOE_STREAM")) != 0;
+  if (use_stream) {
     p.rs = 0;
     const int rc = qmm_stream_launch(p, nmat, rows_hint, (cudaStream_t)stream);
     if (rc != 1) return rc;  // 1: shape outside the pipelined kernel's fast path
@@ -550,7 +616,7 @@ int zmoe_gather_qmm(const void* x, int x_rows, int ldx, const uint32_t* w_, cons
   const void* s[2] = {scales, nullptr};
   const void* b[2] = {biases, nullptr};
   return qmm_launch(1, x, x_rows, ldx, w, s, b, E, N, K, group_size, qmode, plan, rows, rows_hint, out, 0,
-                    x_by_output_row != 0, stream, "zmoe_gather_qmm");
+                    x_by_output_row, stream, "zmoe_gather_qmm");
 }
 
 }  // extern "C"

@@ -19,6 +19,7 @@ struct QmmParams {
   int rs;        // token rows staged per pass (<= TT*NT)
   int epilogue;  // 0: store T; 1: SwiGLU CPU contract; 2: SwiGLU per-op contract
   int x_by_dst;  // token row r of the output reads x row r instead of the plan's source row
+  int late_wait;  // the plan predates the previous kernel: stream the first weights before the dependency wait
 };
 
 __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

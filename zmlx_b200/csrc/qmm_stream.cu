@@ -20,16 +20,20 @@
 // Every wait is bounded: after kSpinLimit failed polls a thread records the fact in a
 // status word, sets a CTA-wide abort flag and stops waiting (results are then
 // meaningless, but the kernel terminates and the context stays usable).
+#include <cstdlib>
+
 #include "qmm_common.cuh"
 
 namespace zmoe {
 
 constexpr int kMaxStages = 8;
 constexpr int kCW = 8;                   // consumer warps
-constexpr int kThreads = 32 * (kCW + 1);  // + one producer warp
+constexpr int kPW = 4;                   // producer warps: a warp's bulk copies are accepted one by one,
+                                         // so several warps issue the stages round-robin
+constexpr int kThreads = 32 * (kCW + kPW);
 constexpr int kCQ = 4;                   // quads (of 4 groups) per weight stage: 512 bytes per row
 constexpr int kRowStride = kCQ * 128 + 32;  // == 32 (mod 128): conflict-free 8-byte fragment loads
-constexpr int kSpinLimit = 1 << 22;
+constexpr int kSpinLimit = 1 << 20;  // non-blocking polls (~20 ms) before a wait gives up
 
 __device__ int g_stream_status = 0;
 
@@ -84,7 +88,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_try(uint32_t bar, int parity) {
   uint32_t ok;
   asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
@@ -165,7 +169,7 @@ __device__ __forceinline__ void fixup_fp8(float (&acc)[NT][4], const float (&dg)
 }
 
 template <int NMAT, int NT, int TT>
-__global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams p, int n_tiles, int nstages) {
+__global__ void __launch_bounds__(kThreads, 1) qmm_stream_kernel(const QmmParams p, int n_tiles, int nstages, int dbg) {
   static_assert(NT == 1 || TT == 8, "token tiles beyond the first are full");
   constexpr int WM = (NMAT == 2) ? 1 : 2;
   constexpr int GPB = 8 / TT;
@@ -174,6 +178,8 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
   constexpr int NCH = (NT == 1) ? 4 : 2;  // accumulation chains: hides the latency of dependent mmas
   extern __shared__ __align__(128) unsigned char smem[];
 
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int wid = tid >> 5;
@@ -218,8 +224,9 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
 
   int n_stage = 0, n_sc = 0, n_x = 0;  // running use counts of the three rings
 
-  if (wid == kCW) {
-    // ------------------------------------------------------------------ producer warp
+  if (wid >= kCW) {
+    // ------------------------------------------------------------------ producer warps
+    const int pw = wid - kCW;
     for (int a = a_first; a * n_tiles < it1; ++a) {
       const int4 task = __ldg(reinterpret_cast<const int4*>(pv.tasks) + a);
       const int e = task.x, off = task.y, cnt = task.z;
@@ -227,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
       const int nt_hi = min(it1, (a + 1) * n_tiles) - a * n_tiles;
       for (int rc = 0; rc < cnt; rc += p.rs) {
         const int nrow = min(p.rs, cnt - rc);
-        {  // token rows of this (task, pass)
+        if (pw == 0) {  // token rows of this (task, pass)
           const int xb = n_x & 1;
           if (n_x >= 2) mbar_wait(bar_xempty + xb * 8, ((n_x >> 1) - 1) & 1, abort_flag);
           if (lane == 0) mbar_expect_tx(bar_xfull + xb * 8, nrow * K * 2);
@@ -237,10 +244,10 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
             bulk_g2s(smem_u32(smem + lay.x + xb * lay.x_bytes + t * xs_stride), p.x + (size_t)src * p.ldx, K * 2,
                      bar_xfull + xb * 8);
           }
-          ++n_x;
         }
+        ++n_x;
         for (int nt = nt_lo; nt < nt_hi; ++nt) {
-          {  // scales and biases of the item: one contiguous block per array
+          if (pw == 0) {  // scales and biases of the item: one contiguous block per array
             const int sb = n_sc & 1;
             if (n_sc >= 2) mbar_wait(bar_scempty + sb * 8, ((n_sc >> 1) - 1) & 1, abort_flag);
             const int arr_bytes = 16 * WM * ngroups * 2;
@@ -251,13 +258,14 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
               bulk_g2s(smem_u32(smem + lay.sc + sb * lay.sc_bytes + lane * arr_bytes),
                        base + ((size_t)e * N + (size_t)nt * 16 * WM) * ngroups, arr_bytes, bar_scfull + sb * 8);
             }
-            ++n_sc;
           }
+          ++n_sc;
           // weight stages: lane r copies row r of the 32-row stage
           const int rs_idx = lane >> 4;  // gate/up (NMAT == 2) or row tile (NMAT == 1)
           const uint32_t* wsrc = ((NMAT == 2 && rs_idx) ? p.w[1] : p.w[0]) +
                                  ((size_t)e * N + (size_t)nt * 16 * WM + (NMAT == 2 ? 0 : rs_idx * 16) + (lane & 15)) * K8;
-          for (int ch = 0; ch < nchunks; ++ch) {
+          for (int ch = 0; ch < nchunks; ++ch, ++n_stage) {
+            if ((n_stage % kPW) != pw) continue;
             const int s = n_stage % nstages;
             const int round = n_stage / nstages;
             if (round > 0) mbar_wait(bar_empty + s * 8, (round - 1) & 1, abort_flag);
@@ -266,7 +274,6 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
             __syncwarp();
             bulk_g2s(smem_u32(smem + lay.stages + s * lay.stage_bytes + lane * kRowStride), wsrc + ch * (kCQ * 32),
                      qn * 128, bar_full + s * 8);
-            ++n_stage;
           }
         }
       }
@@ -394,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
           const int s = n_stage % nstages;
           mbar_wait(bar_full + s * 8, (n_stage / nstages) & 1, abort_flag);
           const int quad = ch * kCQ + wk;
-          if (quad < nq) {
+          if (quad < nq && !(dbg & 1)) {
             const unsigned char* wlane =
                 smem + lay.stages + s * lay.stage_bytes + (rs_idx * 16 + g) * kRowStride + wk * 128 + tig * 8;
 #pragma unroll
@@ -467,6 +474,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmm_stream_kernel(const QmmParams
         if (lane == 0) mbar_arrive(bar_scempty + sb * 8);
         ++n_sc;
 
+        if (dbg & 4) continue;
         // ---- gather the K split (and the second matrix) in the first warp of each row block, fixed order
         consumer_sync();  // the previous item's readers are done with the buffer
         float* mine_red = red + (wid * 32 + lane) * (NT * 4);
@@ -573,10 +581,11 @@ static int launch_stream(const QmmParams& p, int n_tiles, int max_items, int nst
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "qmm_stream: shared memory of %d bytes refused: %s", smem_bytes, cudaGetErrorString(e));
-  const int per_sm = (smem_bytes <= 113 * 1024) ? 2 : 1;
+  const int per_sm = 1;
   int grid = sms * per_sm;
   if (grid > max_items) grid = max_items;
-  kern<<<grid, kThreads, smem_bytes, st>>>(p, n_tiles, nstages);
+  static const int dbg = getenv("ZMOE_STREAM_DBG") ? atoi(getenv("ZMOE_STREAM_DBG")) : 0;
+  launch_pdl(kern, dim3(grid), dim3(kThreads), (size_t)smem_bytes, st, p, n_tiles, nstages, dbg);
   return check_launch("qmm_stream_kernel");
 }
 

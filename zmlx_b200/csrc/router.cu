@@ -121,6 +121,8 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restric
                                                            int K, int flavour, const float* __restrict__ bias,
                                                            int renorm, float* __restrict__ weights,
                                                            uint32_t* __restrict__ indices) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T) return;
@@ -212,6 +214,8 @@ __global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restric
                                                            int topk_group, float scale, float* __restrict__ weights,
                                                            uint32_t* __restrict__ indices) {
   extern __shared__ float sm[];
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + wid;
@@ -225,6 +229,8 @@ __global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restric
 __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ wr, int T, int E,
                                                             int d, void* __restrict__ logits, int out_dtype) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
@@ -295,6 +301,8 @@ struct RouteParams {
 template <int VPL>
 __global__ void __launch_bounds__(128) route_fused_kernel(const RouteParams p) {
   extern __shared__ int route_sm[];
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int T = p.T, E = p.E, d = p.d;
@@ -307,6 +315,7 @@ __global__ void __launch_bounds__(128) route_fused_kernel(const RouteParams p) {
       float acc[8];
 #pragma unroll
       for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
+#pragma unroll 8
       for (int i = lane; i < nvec; i += 32) {
         const uint4 wv = __ldg(wrow + i);
         const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -388,8 +397,8 @@ int zmoe_router_softmax_topk(const void* logits, int logits_dtype, int T, int E,
   dim3 grid((T + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
   dispatch_vpl(E, [&](auto vpl) {
-    softmax_topk_kernel<decltype(vpl)::value>
-        <<<grid, block, 0, st>>>(logits, logits_dtype, T, E, K, flavour, bias, renorm, weights, indices);
+    launch_pdl(softmax_topk_kernel<decltype(vpl)::value>, grid, block, 0, st, logits, logits_dtype, T, E, K, flavour,
+               bias, renorm, weights, indices);
     return 0;
   });
   return check_launch("zmoe_router_softmax_topk");
@@ -416,8 +425,8 @@ int zmoe_router_sigmoid_bias_topk(const void* logits, int logits_dtype, int T, i
   size_t smem = 4 * (size_t)(E + 64) * sizeof(float);
   cudaStream_t st = (cudaStream_t)stream;
   dispatch_vpl(E, [&](auto vpl) {
-    sigmoid_topk_kernel<decltype(vpl)::value><<<grid, block, smem, st>>>(logits, logits_dtype, T, E, K, bias, n_group,
-                                                                        topk_group, scale, weights, indices);
+    launch_pdl(sigmoid_topk_kernel<decltype(vpl)::value>, grid, block, smem, st, logits, logits_dtype, T, E, K, bias,
+               n_group, topk_group, scale, weights, indices);
     return 0;
   });
   return check_launch("zmoe_router_sigmoid_bias_topk");
@@ -434,8 +443,8 @@ int zmoe_router_logits(const void* x, const void* wr, int T, int E, int d, void*
                out_dtype);
   if (T == 0) return ZMOE_OK;
   dim3 grid((E + 3) / 4, (T + 7) / 8), block(128);
-  router_logits_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wr, T,
-                                                                 E, d, logits, out_dtype);
+  launch_pdl(router_logits_kernel, grid, block, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x,
+             (const __nv_bfloat16*)wr, T, E, d, logits, out_dtype);
   return check_launch("zmoe_router_logits");
 }
 
@@ -484,7 +493,7 @@ int zmoe_route(const void* x, const void* wr, int T, int E, int d, int K, int fa
   dim3 grid((E + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
   dispatch_vpl(E, [&](auto vpl) {
-    route_fused_kernel<decltype(vpl)::value><<<grid, block, smem, st>>>(p);
+    launch_pdl(route_fused_kernel<decltype(vpl)::value>, grid, block, smem, st, p);
     return 0;
   });
   return check_launch("zmoe_route");

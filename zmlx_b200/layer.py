@@ -115,7 +115,7 @@ class MoELayer:
                                               cfg.d_model, self.gs, qm, p(self.plan), T * K, T, p(self.h),
                                               self.swiglu, st))
         _lib.check(lib.zmoe_gather_qmm(p(self.h), T * K, cfg.d_ff, p(W["down_w"]), p(W["down_s"]), p(W["down_b"]),
-                                       cfg.n_experts, cfg.d_model, cfg.d_ff, self.gs, qm, p(self.plan), T * K, T, 1,
+                                       cfg.n_experts, cfg.d_model, cfg.d_ff, self.gs, qm, p(self.plan), T * K, T, 3,
                                        p(self.y), st))
 
     def shared(self, x: torch.Tensor):
