@@ -17,40 +17,47 @@ __device__ __forceinline__ float load_logit(const void* p, int dtype, size_t i) 
   return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
-// K rounds of arg-max over the lane-strided values v[j] (expert id = lane + 32*j);
-// all lanes end with the same winners in sel_val/sel_idx.  A lane keeps a bit
-// mask of the ids it has given away, so that genuine -inf scores cannot be
-// confused with retired entries.
+// Top-k of the lane-strided values v[j] (expert id = lane + 32*j) by ranking: every value
+// counts how many others beat it under the canonical order (value descending, id ascending);
+// the ranks are a permutation, so the entries ranked below K write themselves straight into
+// slot order.  `scratch` is E + 2 * kMaxK floats owned by the warp.  All lanes end with the
+// winners in sel_val/sel_idx.
 template <int VPL>
 __device__ __forceinline__ void warp_topk_masked(float (&v)[VPL], int E, int K, int lane, float* sel_val,
-                                                 int* sel_idx) {
-  uint32_t taken = 0;
-  for (int r = 0; r < K; ++r) {
-    float best = -CUDART_INF_F;
-    int bidx = 0x7fffffff;
+                                                 int* sel_idx, float* scratch) {
+  float* vals = scratch;
+  float* out_v = scratch + E;
+  int* out_i = reinterpret_cast<int*>(scratch + E + kMaxK);
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int idx = lane + 32 * j;
+    if (idx < E) vals[idx] = v[j];
+  }
+  __syncwarp();
+  int rank[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) rank[j] = 0;
+  for (int o = 0; o < E; ++o) {
+    const float ov = vals[o];  // broadcast read
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-      int idx = lane + 32 * j;
-      bool avail = idx < E && !((taken >> j) & 1u);
-      if (avail && (bidx == 0x7fffffff || v[j] > best)) {
-        best = v[j];
-        bidx = idx;
-      }
+      const int idx = lane + 32 * j;
+      rank[j] += (ov > v[j]) || (ov == v[j] && o < idx);
     }
+  }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
-      bool other_valid = oi != 0x7fffffff;
-      bool mine_valid = bidx != 0x7fffffff;
-      if (other_valid && (!mine_valid || ov > best || (ov == best && oi < bidx))) {
-        best = ov;
-        bidx = oi;
-      }
+  for (int j = 0; j < VPL; ++j) {
+    const int idx = lane + 32 * j;
+    if (idx < E && rank[j] < K) {
+      out_v[rank[j]] = v[j];
+      out_i[rank[j]] = idx;
     }
-    sel_val[r] = best;
-    sel_idx[r] = bidx;
-    if (bidx != 0x7fffffff && (bidx & 31) == lane) taken |= 1u << (bidx >> 5);
+  }
+  __syncwarp();
+  for (int r = 0; r < K; ++r) {
+    sel_val[r] = out_v[r];
+    sel_idx[r] = out_i[r];
   }
 }
 
@@ -59,7 +66,7 @@ template <int VPL>
 __device__ __forceinline__ void softmax_topk_row(const void* __restrict__ logits, int dtype, int row, int E, int K,
                                                  int flavour, const float* __restrict__ bias, int renorm,
                                                  float* __restrict__ weights, uint32_t* __restrict__ indices,
-                                                 int lane) {
+                                                 int lane, float* scratch) {
   float v[VPL];
   float mx = -CUDART_INF_F;
 #pragma unroll
@@ -71,7 +78,7 @@ __device__ __forceinline__ void softmax_topk_row(const void* __restrict__ logits
   float sel_val[kMaxK];
   int sel_idx[kMaxK];
   if (flavour == ZMOE_ROUTER_TOPK_THEN_SOFTMAX) {
-    warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+    warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx, scratch);
     if (lane == 0) {
       float m = sel_val[0];
       float s = 0.0f;
@@ -101,7 +108,7 @@ __device__ __forceinline__ void softmax_topk_row(const void* __restrict__ logits
       if (bias) v[j] += bias[idx];
     }
   }
-  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx, scratch);
   if (lane == 0) {
     float denom = 1.0f;
     if (renorm) {
@@ -123,15 +130,17 @@ __global__ void __launch_bounds__(128) softmax_topk_kernel(const void* __restric
                                                            uint32_t* __restrict__ indices) {
   pdl_wait();
   pdl_trigger();
+  extern __shared__ float topk_sm[];
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T) return;
-  softmax_topk_row<VPL>(logits, dtype, row, E, K, flavour, bias, renorm, weights, indices, lane);
+  softmax_topk_row<VPL>(logits, dtype, row, E, K, flavour, bias, renorm, weights, indices, lane,
+                        topk_sm + (size_t)(threadIdx.x >> 5) * (E + 2 * kMaxK));
 }
 
-// sigmoid + selection bias, optional group-limited selection.  Per-warp shared
-// scratch holds the E scores so that one lane per group can scan its group.
-// One warp routes one token row (sigmoid family); `sc` is E + 64 floats of scratch owned by the warp.
+// sigmoid + selection bias, optional group-limited selection.  One warp routes one token row;
+// `sc` is 2 * E + 64 + 2 * kMaxK floats of scratch owned by the warp (scores, group scores and
+// keep flags, then the top-k scratch).
 template <int VPL>
 __device__ __forceinline__ void sigmoid_topk_row(const void* __restrict__ logits, int dtype, int row, int E, int K,
                                                  const float* __restrict__ bias, int n_group, int topk_group,
@@ -190,7 +199,7 @@ __device__ __forceinline__ void sigmoid_topk_row(const void* __restrict__ logits
   }
   float sel_val[kMaxK];
   int sel_idx[kMaxK];
-  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx);
+  warp_topk_masked<VPL>(v, E, K, lane, sel_val, sel_idx, sc + E + 64);
   if (lane == 0) {
     float aff[kMaxK];
     float sum = 0.0f;
@@ -221,7 +230,7 @@ __global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restric
   const int row = blockIdx.x * (blockDim.x >> 5) + wid;
   if (row >= T) return;
   sigmoid_topk_row<VPL>(logits, dtype, row, E, K, bias, n_group, topk_group, scale, weights, indices, lane,
-                        sm + (size_t)wid * (E + 64));
+                        sm + (size_t)wid * (2 * E + 64 + 2 * kMaxK));
 }
 
 // Router linear.  One warp per (expert, token tile of 8): 16-byte loads of the
@@ -352,11 +361,11 @@ __global__ void __launch_bounds__(128) route_fused_kernel(const RouteParams p) {
   for (int row = wid; row < T; row += 4) {
     if (p.family == 2)
       sigmoid_topk_row<VPL>(p.logits, ZMOE_BF16, row, E, p.K, p.bias, p.n_group, p.topk_group, p.scale, p.weights,
-                            p.indices, lane, scratch + (size_t)wid * (E + 64));
+                            p.indices, lane, scratch + (size_t)wid * (2 * E + 64 + 2 * kMaxK));
     else
       softmax_topk_row<VPL>(p.logits, ZMOE_BF16, row, E, p.K,
                             p.family == 0 ? ZMOE_ROUTER_TOPK_THEN_SOFTMAX : ZMOE_ROUTER_SOFTMAX_THEN_TOPK, p.bias,
-                            p.renorm, p.weights, p.indices, lane);
+                            p.renorm, p.weights, p.indices, lane, scratch + (size_t)wid * (2 * E + 64 + 2 * kMaxK));
   }
   __syncthreads();
   // ---- phase 3: plan over the (token, slot) pairs; pair p reads token row p / K
@@ -397,7 +406,7 @@ int zmoe_router_softmax_topk(const void* logits, int logits_dtype, int T, int E,
   dim3 grid((T + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
   dispatch_vpl(E, [&](auto vpl) {
-    launch_pdl(softmax_topk_kernel<decltype(vpl)::value>, grid, block, 0, st, logits, logits_dtype, T, E, K, flavour,
+    launch_pdl(softmax_topk_kernel<decltype(vpl)::value>, grid, block, 4 * (size_t)(E + 2 * kMaxK) * sizeof(float), st, logits, logits_dtype, T, E, K, flavour,
                bias, renorm, weights, indices);
     return 0;
   });
@@ -422,7 +431,7 @@ int zmoe_router_sigmoid_bias_topk(const void* logits, int logits_dtype, int T, i
                "zmoe_router_sigmoid_bias_topk: logits dtype %d", logits_dtype);
   if (T == 0) return ZMOE_OK;
   dim3 grid((T + 3) / 4), block(128);
-  size_t smem = 4 * (size_t)(E + 64) * sizeof(float);
+  size_t smem = 4 * (size_t)(2 * E + 64 + 2 * kMaxK) * sizeof(float);
   cudaStream_t st = (cudaStream_t)stream;
   dispatch_vpl(E, [&](auto vpl) {
     launch_pdl(sigmoid_topk_kernel<decltype(vpl)::value>, grid, block, smem, st, logits, logits_dtype, T, E, K, bias,
@@ -488,7 +497,7 @@ int zmoe_route(const void* x, const void* wr, int T, int E, int d, int K, int fa
   p.plan = (int*)plan;
   p.counter = counter;
   size_t smem_plan = (size_t)(2 * E + 128) * sizeof(int);
-  size_t smem_sig = 4 * (size_t)(E + 64) * sizeof(float);
+  size_t smem_sig = 4 * (size_t)(2 * E + 64 + 2 * kMaxK) * sizeof(float);
   size_t smem = smem_plan > smem_sig ? smem_plan : smem_sig;
   dim3 grid((E + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
