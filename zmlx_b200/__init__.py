@@ -11,5 +11,7 @@ __version__ = "0.1.0"
 
 from . import kernels  # noqa: F401,E402
 from .kernels import fused_moe, moe  # noqa: F401,E402
+from . import patch as _patch_module  # noqa: F401,E402
+from .patch import patch, unpatch  # noqa: F401,E402
 
-__all__ = ["kernels", "moe", "fused_moe", "__version__"]
+__all__ = ["kernels", "moe", "fused_moe", "patch", "unpatch", "__version__"]
