@@ -75,7 +75,7 @@ def _oracle_layer(cfg, params, x, logits, idx_gpu):
 
 
 @pytest.mark.parametrize("name,T", [("c1", 1), ("c1", 5), ("c2", 1), ("c2", 4), ("c2", 16), ("c2", 64),
-                                    ("c5", 1), ("c5", 9)])
+                                    ("c3", 1), ("c3", 3), ("c3", 16), ("c5", 1), ("c5", 9)])
 def test_layer_matches_oracle(name, T):
     cfg, params = _layer(name)
     layer = MoELayer(cfg, params, max_tokens=64)

@@ -161,3 +161,33 @@ def test_bad_arguments_raise():
     with pytest.raises(ValueError):
         fused_moe.gather_qmm_swiglu(x, *_to(DEV, *gate), *_to(DEV, *up),
                                     rhs_indices=torch.zeros((1,), device=DEV))  # float indices
+
+
+@pytest.mark.parametrize("T,K_,d,f", [(1, 4, 2048, 1536), (5, 2, 512, 256), (12, 3, 256, 768), (40, 2, 256, 256)])
+def test_mxfp4_swiglu_and_down(T, K_, d, f):
+    """mxfp4 expert banks (e2m1 codes, e8m0 scale per 32): fused gate/up + SwiGLU (per-op contract) and down."""
+    E = 8
+    g = torch.Generator().manual_seed(100 + T)
+    banks = []
+    for n_out, n_in in ((f, d), (f, d), (d, f)):
+        w = torch.randn((E, n_out, n_in), generator=g) * 0.02
+        banks.append(quant.quantize_mxfp4(w))
+    x = torch.randn((T, 1, 1, d), generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K_] for _ in range(T)]).to(torch.int32)
+    (gw, gs), (uw, us), (dw, ds) = banks
+    h = fused_moe.gather_qmm_swiglu(x.to(DEV), gw.to(DEV), gs.to(DEV), None, uw.to(DEV), us.to(DEV), None,
+                                    rhs_indices=idx.to(DEV), mode="mxfp4", group_size=32, swiglu_contract="per_op")
+    assert h.shape == (T, K_, 1, f)
+    lhs = np.repeat(np.arange(T, dtype=np.int32), K_)
+    rhs = t2n(idx).reshape(-1)
+    gg = F.gather_qmm_rows(t2n(x).reshape(T, d), t2n(gw), t2n(gs), None, lhs, rhs, mode="mxfp4")
+    uu = F.gather_qmm_rows(t2n(x).reshape(T, d), t2n(uw), t2n(us), None, lhs, rhs, mode="mxfp4")
+    ref_h = S.swiglu_per_op(gg, uu)
+    assert_close_rel(t2n(h).reshape(T * K_, f), ref_h, REL, "mxfp4 swiglu")
+    gate = torch.rand((T, K_), generator=g)
+    out = moe.gather_qmm_combine_quantized(h.reshape(T, K_, f), dw.to(DEV), ds.to(DEV), None, gate.to(DEV),
+                                           idx.to(DEV).view(torch.uint32), group_size=32, mode="mxfp4",
+                                           output_dtype=torch.float32, no_fma=True)
+    ref = S.gather_qmm_combine_quantized(t2n(h).reshape(T, K_, f), t2n(dw), t2n(ds), None, t2n(gate), t2n(idx),
+                                         mode="mxfp4", combine="fp32_no_fma")
+    assert_close_rel(t2n(out), ref, REL, "mxfp4 down + combine")

@@ -29,6 +29,8 @@ namespace zmoe {
 
 // Persistent bulk-copy pipelined variant (qmm_stream.cu); returns 1 when the shape is outside its fast path.
 int qmm_stream_launch(const QmmParams& p, int nmat, int rows_hint, cudaStream_t st);
+// mxfp4 weights (qmm_mxfp4.cu).
+int qmm_mxfp4_launch(QmmParams p, int nmat, int rows_hint, int max_groups, cudaStream_t st, const char* who);
 
 
 __host__ __device__ inline int qmm_xs_stride(int K) { return K * 2 + 16; }
@@ -528,15 +530,17 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
     ZMOE_REQUIRE(w[m] && s[m], ZMOE_ERR_SHAPE, "%s: null weight or scale pointer", who);
   ZMOE_REQUIRE(E >= 1 && N >= 1 && K >= 1 && rows >= 0 && x_rows >= 0, ZMOE_ERR_SHAPE,
                "%s: bad sizes E=%d N=%d K=%d rows=%d", who, E, N, K, rows);
-  ZMOE_REQUIRE(qmode == ZMOE_Q_AFFINE4, ZMOE_ERR_UNSUPPORTED, "%s: quantisation mode %d is not supported", who,
-               qmode);
-  ZMOE_REQUIRE(group_size == 64, ZMOE_ERR_UNSUPPORTED, "%s: group_size=%d (only 64 is supported)", who, group_size);
+  ZMOE_REQUIRE(qmode == ZMOE_Q_AFFINE4 || qmode == ZMOE_Q_MXFP4, ZMOE_ERR_UNSUPPORTED,
+               "%s: quantisation mode %d is not supported", who, qmode);
+  const bool mx = (qmode == ZMOE_Q_MXFP4);
+  ZMOE_REQUIRE(group_size == (mx ? 32 : 64), ZMOE_ERR_UNSUPPORTED, "%s: group_size=%d (affine: 64, mxfp4: 32)", who,
+               group_size);
   ZMOE_REQUIRE(K % 64 == 0, ZMOE_ERR_SHAPE, "%s: K=%d must be a multiple of 64", who, K);
-  for (int m = 0; m < nmat; ++m) ZMOE_REQUIRE(b[m], ZMOE_ERR_SHAPE, "%s: affine mode needs biases", who);
+  for (int m = 0; m < nmat; ++m) ZMOE_REQUIRE(mx || b[m], ZMOE_ERR_SHAPE, "%s: affine mode needs biases", who);
   ZMOE_REQUIRE(ldx >= K && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0, ZMOE_ERR_ALIGN,
                "%s: x rows must be 16-byte aligned (ldx=%d)", who, ldx);
   for (int m = 0; m < nmat; ++m)
-    ZMOE_REQUIRE(((uintptr_t)w[m] % 8) == 0 && ((uintptr_t)s[m] % 8) == 0 && ((uintptr_t)b[m] % 8) == 0,
+    ZMOE_REQUIRE(((uintptr_t)w[m] % 8) == 0 && ((uintptr_t)s[m] % 8) == 0 && (mx || ((uintptr_t)b[m] % 8) == 0),
                  ZMOE_ERR_ALIGN, "%s: packed weights, scales and biases must be 8-byte aligned", who);
   if (rows == 0) return ZMOE_OK;
   if (rows_hint <= 0 || rows_hint > rows) rows_hint = rows;
@@ -562,6 +566,11 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
   p.x_by_dst = x_by_dst & 1;
   p.late_wait = (x_by_dst & 2) ? 1 : 0;
 
+  if (mx) {
+    int mg = rows < E ? rows : E;
+    if (mg > 65535) mg = 65535;
+    return qmm_mxfp4_launch(p, nmat, rows_hint, mg, (cudaStream_t)stream, who);
+  }
   // The shared-memory pipelined kernel is opt-in (ZMOE_STREAM=1): the register-pipelined kernel below is
   // as fast or faster at decode sizes.
   static const bool use_stream = getenv("ZMOE_STREAM") != nullptr && atoi(getenv("ZMOE_STREAM")) != 0;
