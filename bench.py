@@ -8,9 +8,11 @@ times over.  ``value`` = layer-tokens per second = T * L * n_gpus / step time, i
 resident in HBM; ``e2e`` is the same metric through the public Python call with the
 token rows starting in pinned host memory and the result read back every step.
 
-Multi-GPU (--gpus N under torchrun): the path shards by independent layers/experts
-with no data-path collective in this build; every rank runs the same workload on its
-own weights (weak scaling) and the step time is the max over ranks.
+Multi-GPU (--gpus N under torchrun): expert parallel.  Rank r owns E/N experts of every
+layer and brings its own T tokens; per layer the token rows are all-gathered, routed on
+every rank, the local experts run, and the per-slot rows are reduce-scattered back for the
+ordered combine (zmlx_b200/ep.py).  Per-GPU tokens are fixed as N grows (weak scaling);
+the step time is the max over ranks.  ``--replicas`` runs N independent copies instead.
 
 ``--impl reference`` times the CPU restatement of the reference's path (the compiled
 oracle, all host threads) on a bounded sample of the same workload.
@@ -45,6 +47,8 @@ def _args():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallel")
+    ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
 
 
@@ -199,12 +203,43 @@ def main() -> None:
 
     cfg = synthetic.CONFIGS[args.config]
     T, L = args.tokens, args.layers
-    layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T)
-              for i in range(L)]
+    use_ep = world > 1 and not args.replicas
+    if use_ep:
+        from zmlx_b200 import ep
+
+        layers = []
+        for i in range(L):
+            full = synthetic.make_layer(cfg, layer=i, device=dev)  # same seed on every rank: one model
+            lo, hi = ep.expert_range(cfg.n_experts, world, rank)
+            layers.append(ep.EPMoELayer(cfg, ep.shard_params(full, lo, hi), rank=rank, world=world, max_tokens=T,
+                                        sharded=True))
+            if args.check and i == 0:
+                ref_layer = MoELayer(cfg, full, max_tokens=T)
+            else:
+                del full
+        torch.cuda.empty_cache()
+    else:
+        layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T)
+                  for i in range(L)]
     x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
     x_dev = x_host.to(dev)
     out_host = torch.empty((T, cfg.d_model), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.Stream(device=dev)
+    if use_ep and args.check:
+        with torch.cuda.stream(stream):
+            got = layers[0].forward(x_dev).clone()
+            want = ref_layer.forward(x_dev).clone()
+        stream.synchronize()
+        diff = (got.float() - want.float()).abs().max().item()
+        scale = want.float().abs().max().item()
+        rec = {"max_abs_diff": diff, "max_abs": scale, "equal_frac": (got == want).float().mean().item(),
+               "indices_equal": bool(torch.equal(layers[0].inner.indices[rank * T:(rank + 1) * T],
+                                                 ref_layer.indices[:T]))}
+        flags = [None] * world
+        dist.all_gather_object(flags, rec)
+        if rank == 0:
+            print(json.dumps({"check": "expert-parallel layer 0 vs the 1-GPU layer on each rank's own tokens",
+                              "ranks": flags}), file=sys.stderr)
 
     def step_eager():
         h = x_dev
@@ -216,8 +251,17 @@ def main() -> None:
     with torch.cuda.stream(stream):
         step_eager()
     stream.synchronize()
-    distinct = [int(torch.unique(ly.indices[:T]).numel()) for ly in layers]
-    alg_bytes_step = sum(cfg.algorithmic_bytes(dn, T) for dn in distinct)
+    if use_ep:
+        distinct = []
+        for ly in layers:
+            idx = ly.inner.indices[:T * world].reshape(-1)
+            distinct.append(int(torch.unique(idx[(idx >= ly.lo) & (idx < ly.hi)]).numel()))
+        # bytes this rank must move: its local experts, the replicated router over all gathered tokens, rows in/out
+        alg_bytes_step = sum(dn * cfg.expert_bytes + cfg.n_shared * cfg.expert_bytes + cfg.router_bytes
+                             + 4 * T * world * cfg.d_model for dn in distinct)
+    else:
+        distinct = [int(torch.unique(ly.indices[:T]).numel()) for ly in layers]
+        alg_bytes_step = sum(cfg.algorithmic_bytes(dn, T) for dn in distinct)
 
     graph = None
     if not args.no_graph:
@@ -225,9 +269,15 @@ def main() -> None:
             for _ in range(2):
                 step_eager()
         stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step_eager()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_eager()
+        except Exception as exc:  # e.g. a collective that cannot be captured: time eager launches instead
+            if rank == 0:
+                print(f"[bench] CUDA-graph capture failed ({type(exc).__name__}); timing eager launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize(dev)
 
     def run_step():
         if graph is not None:
@@ -240,8 +290,9 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    # launches per layer: fused router (linear + top-k + plan), gate/up, down, combine (+3 for a shared expert)
-    launches_per_layer = 4 + (3 if cfg.n_shared else 0)
+    # launches per layer: fused router (linear + top-k + plan), gate/up, down, combine (+3 for a shared expert);
+    # expert parallel adds the local plan kernel (the NCCL and torch kernels are not counted)
+    launches_per_layer = 4 + (3 if cfg.n_shared else 0) + (1 if use_ep else 0)
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
@@ -301,11 +352,14 @@ def main() -> None:
                                    f"L={L} independent layers",
                        "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
-                       "cuda_graph": graph is not None, "parallelism": f"replicated layers x{world}"},
+                       "cuda_graph": graph is not None,
+                       "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
+                                       "reduce-scattered (NCCL)") if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_step": alg_bytes_step,
-                         "note": "whole layer pass (4 kernels); per-kernel figures in profiles/"},
+                         "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
+                                  "whole layer pass (4 kernels); per-kernel figures in profiles/")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
                     "d2h_bytes_per_step": T * cfg.d_model * 2},
             "gpu_launches": launches_per_layer * L * args.steps,

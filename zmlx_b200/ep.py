@@ -1,0 +1,150 @@
+"""Expert-parallel MoE layer across the GPUs of one node (one process per GPU, NCCL).
+
+The reference has no distributed code at all (SURVEY: no collectives anywhere in the tree); this is the sharding
+its operator surface allows: experts are independent, so rank r owns experts [r*E/R, (r+1)*E/R) and the router
+weight and shared experts are replicated.  Every rank brings its own T decode tokens (data-parallel attention
+side); one layer pass is
+
+    all-gather token rows  ->  route all R*T tokens (replicated, identical on every rank)
+    -> gate/up + SwiGLU and down projection for the (token, slot) pairs whose expert is local
+    -> reduce-scatter of the per-slot rows  ->  ordered combine of the rank's own T tokens.
+
+The per-slot rows of non-local pairs are zero, so the reduce-scatter adds exactly one non-zero bf16 value per
+element and zeros: the sum is exact in any order and the combine sees the same rows, in the same slot order, as
+the single-GPU layer.  The exchange and the combine thus add no rounding of their own; what can differ from a
+1-GPU run is the fp32 summation grouping inside the matmul kernel, which depends on how many rows an expert
+receives in one launch (a last-bit effect on a few bf16 outputs).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+from .layer import MoELayer
+from .synthetic import MoEConfig
+
+
+def expert_range(n_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """[lo, hi) of the experts rank ``rank`` owns; ``world`` must divide the expert count."""
+    if n_experts % world != 0:
+        raise ValueError(f"{n_experts} experts do not split evenly over {world} ranks")
+    per = n_experts // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_params(params: dict, lo: int, hi: int) -> dict:
+    """The expert banks restricted to experts [lo, hi); router weight, bias and shared experts stay whole."""
+    out = dict(params)
+    for k in ("gate", "up", "down"):
+        for suffix in ("w", "s", "b"):
+            t = params.get(f"{k}_{suffix}")
+            if t is None:
+                out[f"{k}_{suffix}"] = None
+            elif t.dtype == torch.uint32:
+                out[f"{k}_{suffix}"] = t.view(torch.int32)[lo:hi].contiguous().view(torch.uint32)
+            else:
+                out[f"{k}_{suffix}"] = t[lo:hi].contiguous()
+    return out
+
+
+def localize_indices(indices: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+    """Expert ids relative to the local shard; ids outside [lo, hi) become -1 (the plan builder drops them)."""
+    idx = indices.to(torch.int32)
+    local = idx - lo
+    return torch.where((idx >= lo) & (idx < hi), local, torch.full_like(local, -1))
+
+
+def exchange_slot_rows(y_all: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """Reduce-scatter of the (R*T*K, d) per-slot rows: rank r receives rows [r*T*K, (r+1)*T*K) summed over
+    ranks.  Exactly one rank holds a non-zero value per element, so the sum is exact."""
+    if world == 1:
+        return y_all
+    rows = y_all.shape[0] // world
+    out = torch.empty((rows, y_all.shape[1]), dtype=y_all.dtype, device=y_all.device)
+    if y_all.is_cuda:
+        dist.reduce_scatter_tensor(out, y_all, op=dist.ReduceOp.SUM, group=group)
+    else:  # gloo has no reduce_scatter: all-reduce and slice (host-logic tests only)
+        tmp = y_all.to(torch.float32)
+        dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
+        r = dist.get_rank(group)
+        out.copy_(tmp[r * rows:(r + 1) * rows].to(y_all.dtype))
+    return out
+
+
+def gather_tokens(x: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """All-gather of the ranks' (T, d) token rows into (R*T, d), rank-major."""
+    if world == 1:
+        return x
+    out = torch.empty((world * x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    if x.is_cuda:
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+    else:
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        out.copy_(torch.cat(parts))
+    return out
+
+
+class EPMoELayer:
+    """One expert-parallel MoE layer; ``params`` are the FULL layer's tensors on this rank's GPU or already the
+    shard (``sharded=True``)."""
+
+    def __init__(self, cfg: MoEConfig, params: dict, *, rank: int, world: int, max_tokens: int = 16, group=None,
+                 sharded: bool = False):
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
+        self.lo, self.hi = expert_range(cfg.n_experts, world, rank)
+        local = params if sharded else shard_params(params, self.lo, self.hi)
+        self.n_local = self.hi - self.lo
+        # the single-GPU layer object provides buffers and the replicated router on all R*T tokens
+        self.inner = MoELayer(cfg, local, max_tokens=max_tokens * world)
+        dev = self.inner.device
+        TK = max_tokens * world * cfg.top_k
+        self.local_idx = torch.empty((TK,), dtype=torch.int32, device=dev)
+        self.local_plan = torch.empty(ops.plan_bytes(TK, self.n_local) // 4, dtype=torch.int32, device=dev)
+        self.out = torch.empty((max_tokens, cfg.d_model), dtype=torch.bfloat16, device=dev)
+        self.max_tokens = max_tokens
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        cfg, inner, R = self.cfg, self.inner, self.world
+        T = x.shape[0]
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens exceed max_tokens={self.max_tokens}")
+        K = cfg.top_k
+        lib = _lib.load()
+        p = ops._ptr
+        with torch.cuda.device(inner.device):
+            x_all = gather_tokens(x, R, self.group)  # (R*T, d)
+            TA = x_all.shape[0]
+            inner.route(x_all)  # replicated: weights/indices of all R*T tokens (the full-E plan is unused)
+            li = self.local_idx[:TA * K]
+            torch.sub(inner.indices[:TA].reshape(-1), self.lo, out=li)  # ids outside [0, n_local) are dropped
+            st = ops._stream()
+            _lib.check(lib.zmoe_build_plan(None, K, p(li), TA * K, 1, self.n_local, p(self.local_plan),
+                                           self.local_plan.numel() * 4, st))
+            qm = ops.qmode_code(cfg.mode)
+            W = inner.p
+            y = inner.y[:TA * K]
+            y.zero_()
+            _lib.check(lib.zmoe_gather_qmm_swiglu(p(x_all), TA, x_all.stride(0), p(W["gate_w"]), p(W["gate_s"]),
+                                                  p(W["gate_b"]), p(W["up_w"]), p(W["up_s"]), p(W["up_b"]),
+                                                  self.n_local, cfg.d_ff, cfg.d_model, inner.gs, qm,
+                                                  p(self.local_plan), TA * K, TA, p(inner.h), inner.swiglu, st))
+            _lib.check(lib.zmoe_gather_qmm(p(inner.h), TA * K, cfg.d_ff, p(W["down_w"]), p(W["down_s"]),
+                                           p(W["down_b"]), self.n_local, cfg.d_model, cfg.d_ff, inner.gs, qm,
+                                           p(self.local_plan), TA * K, TA, 1, p(y), st))
+            y_mine = exchange_slot_rows(y, R, self.group)  # (T*K, d): complete rows of this rank's tokens
+            w_mine = inner.weights[self.rank * T:(self.rank + 1) * T] if R > 1 else inner.weights[:T]
+            residual = None
+            if cfg.n_shared:
+                inner.shared(x)
+                residual = inner.sh_y
+            _lib.check(lib.zmoe_moe_combine(p(y_mine), _lib.BF16, p(w_mine.contiguous()), _lib.F32, T, K, cfg.d_model,
+                                            inner.combine_mode, p(self.out), 3 if cfg.family == "generic" else 1,
+                                            p(residual), ops._stream()))
+        return self.out[:T]
+
+    __call__ = forward
