@@ -197,6 +197,25 @@ int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w, const v
                             const void* gate, int gate_dtype, int mode, void* scratch, void* out, int out_t,
                             void* stream);
 
+/*
+ * The same operation as zmoe_gather_qmm_combine for callers that have no scratch buffer to give and
+ * must not allocate one: code running inside a CUDA-graph capture or a real-time serving loop where
+ * cudaMalloc (a device-wide synchronising call) is off limits, and hosts that bind this library from a
+ * runtime whose allocator they cannot reach.  It has no counterpart in the reference.
+ *
+ * The T*K*N projected rows live in a 4 MiB array inside the library image (every GPU that loads the
+ * library holds it until the process exits), so T*K*N must not exceed 2,097,152; larger calls fail
+ * with ZMOE_ERR_WORKSPACE and a message.  The call allocates nothing.  The first call on each device
+ * looks up the array's device address (a one-time, non-stream runtime query): make that first call
+ * outside any stream capture.  All calls on a device share the array: two calls that may overlap on the
+ * GPU (different streams) race with each other; calls on one stream are safe.  The used part of the
+ * array is zeroed at the start of every call.
+ */
+int zmoe_gather_qmm_combine_noalloc(const void* act, int ldx, const uint32_t* w, const void* scales,
+                                    const void* biases, int E, int N, int Kin, int group_size, int qmode,
+                                    const void* plan, int T, int K, const void* gate, int gate_dtype, int mode,
+                                    void* out, int out_t, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,9 @@ SIGNATURES = {
     "zmoe_gather_qmm_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                         c_int, c_void_p]),
+    "zmoe_gather_qmm_combine_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                                                c_void_p]),
 }
 
 

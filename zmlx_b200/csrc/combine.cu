@@ -1,5 +1,7 @@
 // Weighted combine over the K expert slots under the reference's rounding
 // contracts, plus the fused down-projection + combine entry point.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace zmoe {
@@ -106,6 +108,37 @@ int combine_launch(const void* y, int y_dtype, const void* w, int w_dtype, int T
   return check_launch(who);
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for zmoe_gather_qmm_combine_noalloc: lives in the library image, one copy per GPU that
+// loads the library, for the life of the process.
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB = 2,097,152 projected values in T
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mutex;
+static void* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the array on the CURRENT device.  In host code the symbol itself is only a
+// stand-in; the real address comes from cudaGetSymbolAddress, asked once per device.
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine_noalloc: cudaGetDevice: %s",
+                                    cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(ZMOE_ERR_UNSUPPORTED, "zmoe_gather_qmm_combine_noalloc: device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return ZMOE_OK;
+}
+
 }  // namespace zmoe
 
 using namespace zmoe;
@@ -131,6 +164,30 @@ int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w_, const 
   if (rc != ZMOE_OK) return rc;
   return combine_launch(scratch, ZMOE_BF16, gate, gate_dtype, T, K, N, mode, out, out_t, nullptr, stream,
                         "zmoe_gather_qmm_combine");
+}
+
+int zmoe_gather_qmm_combine_noalloc(const void* act, int ldx, const uint32_t* w_, const void* scales,
+                                    const void* biases, int E, int N, int Kin, int group_size, int qmode,
+                                    const void* plan, int T, int K, const void* gate, int gate_dtype, int mode,
+                                    void* out, int out_t, void* stream) {
+  ZMOE_REQUIRE(T >= 0 && K >= 1 && N >= 1, ZMOE_ERR_SHAPE, "zmoe_gather_qmm_combine_noalloc: bad sizes T=%d K=%d N=%d",
+               T, K, N);
+  const size_t need = (size_t)T * K * N * 2;
+  ZMOE_REQUIRE(need <= kStaticScratchBytes, ZMOE_ERR_WORKSPACE,
+               "zmoe_gather_qmm_combine_noalloc: T*K*N = %zu projected values need %zu bytes, the built-in scratch "
+               "holds %zu (use zmoe_gather_qmm_combine with caller scratch for larger calls)",
+               (size_t)T * K * N, need, (size_t)kStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != ZMOE_OK) return rc;
+  if (T == 0) return ZMOE_OK;
+  // the array keeps the previous call's rows: rows whose expert id the plan dropped are never written by the
+  // projection, so start the used part from zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, need, (cudaStream_t)stream);
+  if (e != cudaSuccess)
+    return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return zmoe_gather_qmm_combine(act, ldx, w_, scales, biases, E, N, Kin, group_size, qmode, plan, T, K, gate,
+                                 gate_dtype, mode, scratch, out, out_t, stream);
 }
 
 }  // extern "C"
