@@ -47,6 +47,8 @@ def _args():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-fused", action="store_true",
+                    help="run every block as separate kernels even where the one-launch decode kernel covers it")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallel")
     ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
@@ -219,7 +221,8 @@ def main() -> None:
                 del full
         torch.cuda.empty_cache()
     else:
-        layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T)
+        layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T,
+                           fused=not args.no_fused)
                   for i in range(L)]
     x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
     x_dev = x_host.to(dev)
@@ -296,6 +299,9 @@ def main() -> None:
     # launches per layer: fused router (linear + top-k + plan), gate/up, down, combine (+3 for a shared expert);
     # expert parallel adds the local plan kernel (the NCCL and torch kernels are not counted)
     launches_per_layer = 4 + (3 if cfg.n_shared else 0) + (1 if use_ep else 0)
+    one_launch = (not use_ep) and layers[0].fused and layers[0].fused_workspace_bytes(T) > 0
+    if one_launch:
+        launches_per_layer = 1  # zmoe_layer_decode: the whole block, shared expert included
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
@@ -355,13 +361,14 @@ def main() -> None:
                                    f"L={L} independent layers",
                        "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
-                       "cuda_graph": graph is not None,
+                       "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
                        "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
                                        "reduce-scattered (NCCL)") if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
+                                  "whole block in one cooperative launch (zmoe_layer_decode)" if one_launch else
                                   "whole layer pass (4 kernels); per-kernel figures in profiles/")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
                     "d2h_bytes_per_step": T * cfg.d_model * 2},

@@ -216,6 +216,63 @@ int zmoe_gather_qmm_combine_noalloc(const void* act, int ldx, const uint32_t* w,
                                     const void* plan, int T, int K, const void* gate, int gate_dtype, int mode,
                                     void* out, int out_t, void* stream);
 
+/* --------------------------------------------------------- one-launch decode block */
+
+/* Packed tensors of one expert bank: (E, N, K/8) uint32 weights, (E, N, K/64) T scales and biases. */
+typedef struct zmoe_expert_bank {
+  const uint32_t* gate_w;
+  const void* gate_scales;
+  const void* gate_biases;
+  const uint32_t* up_w;
+  const void* up_scales;
+  const void* up_biases;
+  const uint32_t* down_w;
+  const void* down_scales;
+  const void* down_biases;
+} zmoe_expert_bank;
+
+/*
+ * One MoE block as the patched module sees it (attribute contract of
+ * src/zmlx/patch/patterns/moe_mlp.py:392-409,778-809 and deepseek_router.py:58-69).
+ * router_family / router_bias / renorm / n_group / topk_group / routed_scale as in zmoe_route;
+ * combine_mode and out_flags as `mode` and `out_t` of zmoe_moe_combine; n_shared is 0 or 1 and
+ * the shared expert has the routed experts' d_ff.
+ */
+typedef struct zmoe_layer_desc {
+  int32_t E, d_model, d_ff, top_k;
+  int32_t group_size, qmode;
+  int32_t router_family, renorm, n_group, topk_group;
+  float routed_scale;
+  int32_t n_shared;
+  int32_t swiglu_mode, shared_swiglu_mode;
+  int32_t combine_mode, out_flags;
+  const void* router_w;     /* (E, d_model) T */
+  const float* router_bias; /* (E) or NULL */
+  zmoe_expert_bank routed;
+  zmoe_expert_bank shared;  /* ignored when n_shared == 0 */
+} zmoe_layer_desc;
+
+/*
+ * The whole patched block forward for a few decode tokens (src/zmlx/patch/patterns/moe_mlp.py:883-1063:
+ * gate -> experts -> combine -> + shared_experts(x)) in ONE cooperative launch: router linear, the family's
+ * top-k, gather_qmm_swiglu, the down projection, the ordered combine and the shared expert.  Same
+ * arithmetic contracts as the separate entry points above.  Covers 4-bit affine weights with group
+ * size 64, 1..8 tokens, top_k <= 8, E <= 256, d_model and d_ff multiples of 256; other shapes fail with
+ * ZMOE_ERR_UNSUPPORTED (zmoe_layer_decode_workspace_bytes returns 0 for them) and take the separate calls.
+ *
+ * workspace: zmoe_layer_decode_workspace_bytes(L, T) bytes, 256-byte aligned.  Its first 256 bytes are a
+ * header that starts with four ints {barrier, barrier, exit count, status}; the header must be zero
+ * before the first call and the kernel
+ * leaves the first three zero.  The CTAs of the launch meet at two grid-wide barriers; each wait is
+ * bounded, and a wait that runs out sets status to 1 and ends the launch with `out` undefined.  One
+ * workspace serves one stream at a time.  x (T, d_model) T with row stride ldx; out (T, d_model) T
+ * (float for the FP32 combine modes without out_flags bit 0); weights (T, top_k) float and indices
+ * (T, top_k) uint32 receive the routing when not NULL.
+ */
+size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T);
+int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
+                      size_t workspace_bytes, float* weights, uint32_t* indices, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,14 +74,21 @@ def _oracle_layer(cfg, params, x, logits, idx_gpu):
     return out, w
 
 
-@pytest.mark.parametrize("name,T", [("c1", 1), ("c1", 5), ("c2", 1), ("c2", 4), ("c2", 16), ("c2", 64),
-                                    ("c3", 1), ("c3", 3), ("c3", 16), ("c5", 1), ("c5", 9)])
-def test_layer_matches_oracle(name, T):
+# fused: the one-launch path (zmoe_layer_decode) takes the block; otherwise the separate kernels do
+@pytest.mark.parametrize("name,T,fused", [("c1", 1, False), ("c1", 5, False), ("c2", 1, False), ("c2", 4, False),
+                                          ("c2", 16, False), ("c2", 64, False), ("c3", 1, False), ("c3", 3, False),
+                                          ("c3", 16, False), ("c5", 1, False), ("c5", 9, False),
+                                          ("c1", 1, True), ("c1", 2, True), ("c1", 5, True), ("c1", 8, True),
+                                          ("c2", 1, True), ("c2", 2, True), ("c2", 3, True), ("c2", 4, True),
+                                          ("c2", 7, True), ("c2", 8, True), ("c5", 1, True), ("c5", 2, True)])
+def test_layer_matches_oracle(name, T, fused):
     cfg, params = _layer(name)
-    layer = MoELayer(cfg, params, max_tokens=64)
+    layer = MoELayer(cfg, params, max_tokens=64, fused=fused)
+    assert (layer.fused_workspace_bytes(T) > 0) or not fused
     x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
     out = layer(x).clone()
-    ref, w_ref = _oracle_layer(cfg, params, x, layer.logits[:T], layer.indices[:T])
+    assert layer.fused_status(T) == 0
+    ref, w_ref = _oracle_layer(cfg, params, x, layer.router_logits(T), layer.indices[:T])
     w_gpu = t2n(layer.weights[:T])
     if cfg.family == "generic":  # the block casts the weights to T before combining (moe_mlp.py:288)
         w_gpu = S.bf16(w_gpu)
@@ -91,11 +98,45 @@ def test_layer_matches_oracle(name, T):
     assert torch.equal(layer(x), out)
 
 
+@pytest.mark.parametrize("name,T", [("c1", 1), ("c1", 6), ("c2", 1), ("c2", 2), ("c2", 4), ("c2", 8), ("c5", 1),
+                                    ("c5", 2)])
+def test_one_launch_block_agrees_with_the_separate_kernels(name, T):
+    """Same routing bit for bit; outputs differ by the summation order of the K split only."""
+    cfg, params = _layer(name)
+    one = MoELayer(cfg, params, max_tokens=8, fused=True)
+    sep = MoELayer(cfg, params, max_tokens=8, fused=False)
+    x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
+    a = one(x).clone()
+    b = sep(x).clone()
+    assert one.fused_status(T) == 0
+    assert torch.equal(one.router_logits(T), sep.router_logits(T))
+    assert torch.equal(one.indices[:T], sep.indices[:T])
+    assert torch.equal(one.weights[:T], sep.weights[:T])
+    assert_close_rel(t2n(a), t2n(b), 2e-2, f"{name} T={T} one-launch vs separate")
+    # repeated launches reuse the self-resetting barrier words
+    for _ in range(3):
+        assert torch.equal(one(x), a)
+    assert one.fused_status(T) == 0
+
+
+def test_one_launch_block_rejects_what_it_does_not_cover():
+    cfg, params = _layer("c3")  # mxfp4
+    layer = MoELayer(cfg, params, max_tokens=8)
+    assert layer.fused_workspace_bytes(1) == 0
+    cfg2, params2 = _layer("c2")
+    layer2 = MoELayer(cfg2, params2, max_tokens=16)
+    assert layer2.fused_workspace_bytes(9) == 0 and layer2.fused_workspace_bytes(8) > 0
+    cfg5, params5 = _layer("c5")  # four tokens of h rows no longer fit in shared memory
+    layer5 = MoELayer(cfg5, params5, max_tokens=8)
+    assert layer5.fused_workspace_bytes(4) == 0 and layer5.fused_workspace_bytes(2) > 0
+    assert torch.isfinite(layer5(synthetic.make_tokens(cfg5, 4, device="cpu").to(DEV)).float()).all()
+
+
 def test_router_logits_match_a_float64_matmul():
     cfg, params = _layer("c2")
     layer = MoELayer(cfg, params, max_tokens=16)
     x = synthetic.make_tokens(cfg, 16, device="cpu").to(DEV)
     layer(x)
     ref = (x.double() @ params["router_w"].double().T).cpu().numpy()
-    got = t2n(layer.logits[:16])
+    got = t2n(layer.router_logits(16))
     assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6

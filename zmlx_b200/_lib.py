@@ -30,6 +30,26 @@ COMBINE_MODES = {
     "stream_t": COMBINE_STREAM_T,
 }
 
+
+
+class ExpertBank(ctypes.Structure):
+    """``zmoe_expert_bank``: device pointers of one bank's packed gate/up/down tensors."""
+
+    _fields_ = [(n, c_void_p) for n in ("gate_w", "gate_scales", "gate_biases", "up_w", "up_scales", "up_biases",
+                                        "down_w", "down_scales", "down_biases")]
+
+
+class LayerDesc(ctypes.Structure):
+    """``zmoe_layer_desc``: one MoE block for ``zmoe_layer_decode``."""
+
+    _fields_ = ([(n, ctypes.c_int32) for n in ("E", "d_model", "d_ff", "top_k", "group_size", "qmode",
+                                               "router_family", "renorm", "n_group", "topk_group")]
+                + [("routed_scale", c_float)]
+                + [(n, ctypes.c_int32) for n in ("n_shared", "swiglu_mode", "shared_swiglu_mode", "combine_mode",
+                                                 "out_flags")]
+                + [("router_w", c_void_p), ("router_bias", c_void_p), ("routed", ExpertBank), ("shared", ExpertBank)])
+
+
 # name -> (restype, argtypes); must list every symbol include/zmoe.h declares.
 SIGNATURES = {
     "zmoe_abi_version": (c_int, []),
@@ -56,6 +76,9 @@ SIGNATURES = {
     "zmoe_gather_qmm_combine_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                 c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
                                                 c_void_p]),
+    "zmoe_layer_decode_workspace_bytes": (c_size_t, [ctypes.POINTER(LayerDesc), c_int]),
+    "zmoe_layer_decode": (c_int, [ctypes.POINTER(LayerDesc), c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p,
+                                  c_void_p, c_void_p, c_void_p]),
 }
 
 

@@ -1,0 +1,1134 @@
+// One MoE block for a handful of decode tokens in ONE launch: router linear, top-k,
+// fused gate/up + SwiGLU, down projection, ordered weighted combine, shared expert.
+//
+// The separate-kernel path pays four dependent launches per block; at one token each of
+// them is a few microseconds of launch and pipeline-fill latency around ~1 us of memory
+// traffic.  Here a persistent grid of one 512-thread CTA per SM walks the three phases
+// and meets at two grid-wide barriers (cooperative launch, so every CTA is resident):
+//
+//   phase 0  every CTA stages the T token rows in shared memory (they feed both the
+//            router and every gate/up tile);
+//   phase 1  router linear, one warp per expert row across the whole grid -> logits in
+//            global scratch;                                              [barrier 1]
+//   phase 2  every CTA repeats the top-k of the T rows (cheap, avoids a third barrier)
+//            and derives the task list (distinct experts and their rows) in shared
+//            memory; gate/up + SwiGLU tiles (task, 16 rows) are dealt to groups of four
+//            warps across the grid; h rows go to global scratch.  Before the second
+//            barrier each warp already streams the first packed down-projection weights
+//            into registers: they depend on the routing only.           [barrier 2]
+//   phase 3  every CTA stages all h rows, owns 16 output columns at a time, computes
+//            them for every task (warps split tasks and K) and combines the K slots of
+//            each token in slot order under the requested rounding contract.
+//
+// The matmul core is the one of qmm.cu: packed codes go from HBM to registers with
+// 8-byte streaming loads, become bf16 (128 + q) with a shift and a lop3, and meet the
+// token rows on the tensor cores (mma.sync m16n8k16, weights are the A operand); scale,
+// bias and the 128 offset are applied per group in fp32; spare mma columns carry other
+// groups (column multiplexing).  Every wait on another CTA is bounded: when the limit
+// is hit the CTA records it in the status word and leaves.
+#include <mutex>
+
+#include "qmm_common.cuh"
+#include "router_rows.cuh"
+
+namespace zmoe {
+
+constexpr int kLdThreads = 512;
+constexpr int kLdWarps = kLdThreads / 32;
+constexpr int kLdMaxT = 8;
+constexpr int kLdMaxK = 8;
+constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;      // (token, slot) rows
+constexpr int kLdMaxRows = kLdMaxRouted + kLdMaxT;   // + one shared-expert row per token
+constexpr int kLdMaxTasks = kLdMaxRouted + 1;
+constexpr int kLdDownPD = 2;  // quads of packed weights a warp keeps in flight in the down projection
+constexpr int kLdSpinLimit = 1 << 21;  // polls of the barrier counter before a CTA gives up (~1 s)
+
+struct LdBank {
+  const uint32_t* w[2];
+  const __nv_bfloat16* s[2];
+  const __nv_bfloat16* b[2];
+};
+
+struct LdParams {
+  const __nv_bfloat16* x;
+  int ldx, T;
+  const __nv_bfloat16* wr;
+  const float* rbias;
+  int family, renorm, n_group, topk_group;
+  float scale;
+  int E, d, f, K;
+  LdBank gu, dn, sgu, sdn;  // routed gate/up, routed down, shared gate/up, shared down
+  int n_shared;
+  int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
+  int combine_mode, out_flags;
+  int* sync;  // {barrier 1, barrier 2, exit count, status}
+  __nv_bfloat16* logits;
+  __nv_bfloat16* h;
+  float* weights;
+  uint32_t* indices;
+  void* out;
+};
+
+struct LdMeta {
+  int n_tasks, n_routed;
+  int idx[kLdMaxRouted];
+  float w[kLdMaxRouted];
+  int rank[kLdMaxRouted];
+  int task_expert[kLdMaxTasks];
+  int task_cnt[kLdMaxTasks];
+  unsigned char task_rows[kLdMaxTasks][kLdMaxT];
+};
+
+struct LdSmem {
+  int xs, xsum, sc, red, ybuf, route, meta, zero, total;
+};
+
+__host__ __device__ inline int ld_align16(int a) { return (a + 15) & ~15; }
+
+__host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int n_shared) {
+  LdSmem m;
+  const int rtot = T * K + (n_shared ? T : 0);
+  const int ngd = d / 64, ngf = f / 64;
+  int a = 0;
+  m.xs = a;
+  const int xs1 = T * qmm_xs_stride(d), xs2 = rtot * qmm_xs_stride(f);
+  a += ld_align16(xs1 > xs2 ? xs1 : xs2);
+  m.xsum = a;
+  const int su1 = ngd * T, su2 = ngf * rtot;
+  a += ld_align16((su1 > su2 ? su1 : su2) * 4);
+  m.sc = a;
+  const int sc1 = 4 * 4 * 16 * qmm_sc_stride(ngd);        // gate/up: 4 groups x {gate,up} x {scale,bias} x 16 rows
+  const int sc2 = kLdWarps * 2 * 16 * qmm_sc_stride(ngf);  // down: up to 16 groups x {scale,bias} x 16 rows
+  a += ld_align16(sc1 > sc2 ? sc1 : sc2);
+  m.red = a;
+  a += kLdWarps * 32 * 8 * 4;
+  m.ybuf = a;
+  a += ld_align16(rtot * 16 * 4);
+  m.route = a;
+  a += ld_align16(T * E * 2) + ld_align16(T * (E + 64 + 2 * kLdMaxK) * 4);  // logits, scores, group scratch, winners
+  m.meta = a;
+  a += ld_align16((int)sizeof(LdMeta));
+  m.zero = a;
+  a += 32;
+  m.total = a;
+  return m;
+}
+
+// ------------------------------------------------------------------ grid barrier
+__device__ __forceinline__ int ld_acquire_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_inc(int* p) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p) : "memory");
+}
+
+// All CTAs of the (co-resident) grid meet here.  Returns false when the wait ran out.
+__device__ __forceinline__ bool ld_grid_barrier(int* ctr, int* status, int nblocks, int* ok_s) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    __threadfence();
+    red_release_inc(ctr);
+    int spins = 0;
+    while (ld_acquire_s32(ctr) < nblocks) {
+      if (++spins > kLdSpinLimit) {
+        ok = 0;
+        atomicExch(status, 1);
+        break;
+      }
+    }
+    __threadfence();
+    *ok_s = ok;
+  }
+  __syncthreads();
+  return *ok_s != 0;
+}
+
+__device__ __forceinline__ void ld_group_sync(int gid, int wk_count) {
+  if (wk_count == 1)
+    __syncwarp();
+  else
+    asm volatile("bar.sync %0, %1;" ::"r"(gid + 1), "r"(wk_count * 32) : "memory");
+}
+
+// ------------------------------------------------------------------ staging of token rows
+// Rows go to shared memory with every 8-element block permuted to (0,4,1,5,2,6,3,7) -- the order in
+// which a lane's two 16-byte reads give the B fragments of four k16 steps -- plus per-group sums.
+template <bool COHERENT>
+__device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float* xsum, int xsum_stride,
+                                              const __nv_bfloat16* src, int ld, int nrows, int K8) {
+  const int total = nrows * K8;
+  const int lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int base = (int)(threadIdx.x & ~31u); base < total; base += kLdThreads) {
+    const int i = base + lane;
+    const bool ok = i < total;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    int t = 0, blk = 0;
+    if (ok) {
+      t = i / K8;
+      blk = i - t * K8;
+      const uint4* src4 = reinterpret_cast<const uint4*>(src + (size_t)t * ld) + blk;
+      v = COHERENT ? __ldcg(src4) : __ldg(src4);
+      uint4 o;
+      o.x = __byte_perm(v.x, v.z, 0x5410);
+      o.y = __byte_perm(v.x, v.z, 0x7632);
+      o.z = __byte_perm(v.y, v.w, 0x5410);
+      o.w = __byte_perm(v.y, v.w, 0x7632);
+      *reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16) = o;
+    }
+    float part = ((bf16_bits_to_float(v.x & 0xffffu) + bf16_bits_to_float(v.x >> 16)) +
+                  (bf16_bits_to_float(v.y & 0xffffu) + bf16_bits_to_float(v.y >> 16))) +
+                 ((bf16_bits_to_float(v.z & 0xffffu) + bf16_bits_to_float(v.z >> 16)) +
+                  (bf16_bits_to_float(v.w & 0xffffu) + bf16_bits_to_float(v.w >> 16)));
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    if (ok && (lane & 7) == 0) xsum[(blk >> 3) * xsum_stride + t] = part;
+  }
+}
+
+// ------------------------------------------------------------------ top-k of the T rows, whole CTA
+// Same arithmetic as the per-row router functions (softmax_topk_row / sigmoid_topk_row: the order of every
+// floating-point sum is kept, so scores, indices and weights are bit-identical), but the selection -- ranking
+// every score against every other one -- is spread over all threads instead of one warp per row.
+//
+// Step 1, one warp per row: the row's selection scores -> vals[t][E].
+__device__ __forceinline__ void ld_scores_row(const __nv_bfloat16* g_logits, __nv_bfloat16* s_logits, int row, int E,
+                                              int family, const float* bias, int n_group, int topk_group,
+                                              float* vals, float* gsc /* 64 floats */, int lane) {
+  constexpr int NJ = 8;  // values per lane: E <= 256
+  __nv_bfloat16* lg = s_logits + (size_t)row * E;
+  float v[NJ];
+  {  // the row's logits were written by other CTAs before the barrier: read them through L2, all at once
+    const unsigned short* gl = reinterpret_cast<const unsigned short*>(g_logits) + (size_t)row * E;
+    unsigned short raw[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) raw[j] = (lane + 32 * j < E) ? __ldcg(gl + lane + 32 * j) : (unsigned short)0;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      if (lane + 32 * j < E) reinterpret_cast<unsigned short*>(lg)[lane + 32 * j] = raw[j];
+      v[j] = bf16_bits_to_float(raw[j]);
+    }
+  }
+  if (family == 0) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < E) vals[lane + 32 * j] = v[j];
+    return;
+  }
+  if (family == 1) {
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < E) mx = fmaxf(mx, v[j]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      v[j] = (lane + 32 * j < E) ? expf(v[j] - mx) : 0.0f;
+      sum += v[j];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int idx = lane + 32 * j;
+      if (idx < E) {
+        float q = v[j] / sum;
+        if (bias) q += bias[idx];
+        vals[idx] = q;
+      }
+    }
+    return;
+  }
+  // sigmoid + selection bias, optional group-limited selection
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int idx = lane + 32 * j;
+    if (idx < E) {
+      v[j] = sigmoid_stable(v[j]) + bias[idx];
+      vals[idx] = v[j];
+    }
+  }
+  if (n_group > 1) {
+    float* gkeep = gsc + 32;
+    __syncwarp();
+    const int per = E / n_group;
+    if (lane < n_group) {
+      float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+#pragma unroll 8
+      for (int j = 0; j < per; ++j) {
+        const float x = vals[lane * per + j];
+        if (x > t1) {
+          t2 = t1;
+          t1 = x;
+        } else if (x > t2) {
+          t2 = x;
+        }
+      }
+      gsc[lane] = t1 + t2;
+    }
+    __syncwarp();
+    if (lane < n_group) {
+      const float mine = gsc[lane];
+      int rank = 0;
+      for (int h = 0; h < n_group; ++h) {
+        const float o = gsc[h];
+        rank += (o > mine) || (o == mine && h < lane);
+      }
+      gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int idx = lane + 32 * j;
+      if (idx < E && gkeep[idx / per] == 0.0f) vals[idx] = 0.0f;
+    }
+  }
+}
+
+// Step 2, all threads: rank of every score under (score descending, expert id ascending); the ranks of a row
+// are a permutation, so the entries ranked below K write themselves into slot order.
+__device__ __forceinline__ void ld_rank_select(const float* vals, int T, int E, int K, float* sel_val, int* sel_idx) {
+  const int pairs = T * E;
+  int P = 1;  // threads that share one score's scan
+  while (P < 32 && P * 2 * pairs <= kLdThreads) P *= 2;
+  const int per_pass = kLdThreads / P;
+  const int part = threadIdx.x & (P - 1);
+  for (int base = 0; base < pairs; base += per_pass) {
+    const int pair = base + (threadIdx.x / P);
+    const bool ok = pair < pairs;
+    const int t = ok ? pair / E : 0;
+    const int i = ok ? pair - t * E : 0;
+    const float* row = vals + (size_t)t * E;
+    const float v = row[i];
+    int rank = 0;
+#pragma unroll 4
+    for (int j = part; j < E; j += P) {
+      const float ov = row[j];
+      rank += (ov > v) || (ov == v && j < i);
+    }
+    for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+    if (ok && part == 0 && rank < K) {
+      sel_val[t * K + rank] = v;
+      sel_idx[t * K + rank] = i;
+    }
+  }
+}
+
+// Step 3, one warp per row: the weights of the selected experts.  Lane i < K owns slot i; sums run over the
+// slots in order 0..K-1 (every lane repeats them), as in the per-row router functions.
+__device__ __forceinline__ void ld_finish_row(const __nv_bfloat16* s_logits, int row, int E, int K, int family,
+                                              int renorm, float scale, const float* sel_val, const int* sel_idx,
+                                              float* w_out, int* idx_out, int lane) {
+  const int li = lane < K ? lane : 0;
+  const float sv = sel_val[row * K + li];
+  const int si = sel_idx[row * K + li];
+  float mine;  // the slot's term of the normalising sum
+  if (family == 0)
+    mine = expf(sv - sel_val[row * K]);
+  else if (family == 1)
+    mine = sv;
+  else
+    mine = sigmoid_stable(__bfloat162float(s_logits[(size_t)row * E + si]));
+  float sum = 0.0f;
+  for (int i = 0; i < K; ++i) sum += __shfl_sync(0xffffffffu, mine, i);
+  float w;
+  if (family == 0) {
+    w = mine / sum;
+  } else if (family == 1) {
+    const float denom = (renorm == 1) ? sum + 1e-20f : sum;
+    w = renorm ? sv / denom : sv;
+  } else {
+    const float inv = 1.0f / sum;
+    w = mine * inv;
+    if (scale != 1.0f) w = w * scale;
+  }
+  if (lane < K) {
+    w_out[row * K + lane] = w;
+    idx_out[row * K + lane] = si;
+  }
+}
+
+// ------------------------------------------------------------------ matmul core (one warp)
+template <int NMAT>
+__device__ __forceinline__ void ld_load_quad(uint2 (&buf)[4][NMAT][2], const uint32_t* (&wp)[NMAT][2]) {
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      buf[0][m][h] = ldg_stream_u2<0>(wp[m][h]);
+      buf[1][m][h] = ldg_stream_u2<32>(wp[m][h]);
+      buf[2][m][h] = ldg_stream_u2<64>(wp[m][h]);
+      buf[3][m][h] = ldg_stream_u2<96>(wp[m][h]);
+    }
+  }
+}
+
+// Starts one (expert, 16-row tile) item: the first PD quads of this warp's share of K go to registers ...
+template <int NMAT, int PD>
+__device__ __forceinline__ void ld_issue_w(uint2 (&wbuf)[PD][4][NMAT][2], const uint32_t* (&wp)[NMAT][2],
+                                           const LdBank& bank, int e, int N, int K8, int n0, int g, int tig, int wk,
+                                           int wk_count, int nq_w) {
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+    const uint32_t* we = bank.w[m] + ((size_t)e * N + n0) * K8 + tig * 2 + wk * 32;
+    wp[m][0] = we + (size_t)g * K8;
+    wp[m][1] = we + (size_t)(g + 8) * K8;
+  }
+#pragma unroll
+  for (int bq = 0; bq < PD; ++bq) {
+    if (bq < nq_w) {
+      ld_load_quad<NMAT>(wbuf[bq], wp);
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
+        wp[m][0] += wk_count * 32;
+        wp[m][1] += wk_count * 32;
+      }
+    }
+  }
+}
+
+// ... and the tile's scales and biases to the group's shared-memory area (asynchronous copies, raw T values).
+template <int NMAT>
+__device__ __forceinline__ void ld_issue_sc(const LdBank& bank, int e, int N, int ngroups, int n0, unsigned char* sraw,
+                                            int sc_stride, int gtid, int gsize) {
+  const int cpr = ngroups >> 2;  // 8-byte chunks per row
+#pragma unroll
+  for (int arr = 0; arr < NMAT * 2; ++arr) {
+    const __nv_bfloat16* base = ((arr & 1) ? bank.b[arr >> 1] : bank.s[arr >> 1]) + ((size_t)e * N + n0) * ngroups;
+    unsigned char* dst = sraw + arr * 16 * sc_stride;
+    for (int i = gtid; i < 16 * cpr; i += gsize) {
+      const int r = i / cpr;
+      const int c = i - r * cpr;
+      cp_async_8(dst + r * sc_stride + c * 8, base + (size_t)r * ngroups + c * 4);
+    }
+  }
+}
+
+// Picks the routed or the shared bank field by field (keeps the kernel parameters out of local memory).
+__device__ __forceinline__ LdBank ld_pick(const LdBank& a, const LdBank& b, bool second) {
+  LdBank r;
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    r.w[m] = second ? b.w[m] : a.w[m];
+    r.s[m] = second ? b.s[m] : a.s[m];
+    r.b[m] = second ? b.b[m] : a.b[m];
+  }
+  return r;
+}
+
+// Scale, bias and the 128 offset for a block of 8/TT multiplexed groups whose first item in the warp's stream
+// is gi0.  Lane (g, tig) owns columns 2*tig and 2*tig+1; srow_c[c] is the staged row of column c's token (-1: none).
+template <int NMAT, int TT>
+__device__ __forceinline__ void ld_fixup(float (&acc)[NMAT][4], const float (&dg)[NMAT][4], const float* xsum,
+                                         int xsum_stride, const int (&srow_c)[2], const unsigned char* sraw,
+                                         int sc_stride, int wk, int wk_count, int g, int tig, int gi0, int nq_w) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int col = 2 * tig + c;
+    const int gi_c = gi0 + ((TT == 8) ? 0 : col / TT);
+    const int G_c = (wk + (gi_c >> 2) * wk_count) * 4 + (gi_c & 3);
+    if ((gi_c >> 2) < nq_w) {
+      const float X = (srow_c[c] >= 0) ? xsum[G_c * xsum_stride + srow_c[c]] : 0.0f;
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = g + 8 * h;
+          const float sv = __bfloat162float(
+              *reinterpret_cast<const __nv_bfloat16*>(sraw + ((m * 2 + 0) * 16 + r) * sc_stride + G_c * 2));
+          const float bv = __bfloat162float(
+              *reinterpret_cast<const __nv_bfloat16*>(sraw + ((m * 2 + 1) * 16 + r) * sc_stride + G_c * 2));
+          const float cv = fmaf(-128.0f, sv, bv);
+          acc[m][h * 2 + c] = fmaf(sv, dg[m][h * 2 + c], fmaf(cv, X, acc[m][h * 2 + c]));
+        }
+      }
+    }
+  }
+}
+
+// This warp's share of K for one item.  xoff is the byte offset (in shared memory) of the lane's token row
+// plus tig*32; lanes whose column carries no token of this item read the zero page.  The four k16 steps of a
+// group go to NACC independent accumulators (summed in a fixed order at the fix-up): a chain of dependent
+// mma.sync on one accumulator costs its full latency per step, and at decode sizes nothing else hides it.
+template <int NMAT, int PD, int TT, int NACC>
+__device__ __forceinline__ void ld_mainloop(float (&acc)[NMAT][4], uint2 (&wbuf)[PD][4][NMAT][2],
+                                            const uint32_t* (&wp)[NMAT][2], const unsigned char* smem, int xoff,
+                                            bool tok_ok, int zpage, int slot_g, const float* xsum, int xsum_stride,
+                                            const int (&srow_c)[2], const unsigned char* sraw, int sc_stride, int wk,
+                                            int wk_count, int nq_w, int g, int tig) {
+  static_assert(NACC == 1 || NACC == 2 || NACC == 4, "accumulators per matrix");
+  constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
+  float dg[NMAT][NACC][4];
+  float dsum[NMAT][4];
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
+#pragma unroll
+    for (int n = 0; n < NACC; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dg[m][n][j] = 0.0f;
+  }
+  auto fold = [&]() {
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (NACC == 1) dsum[m][j] = dg[m][0][j];
+        if (NACC == 2) dsum[m][j] = dg[m][0][j] + dg[m][NACC - 1][j];
+        if (NACC == 4) dsum[m][j] = (dg[m][0][j] + dg[m][1 % NACC][j]) + (dg[m][2 % NACC][j] + dg[m][3 % NACC][j]);
+      }
+  };
+  for (int qi = 0; qi < nq_w; qi += PD) {
+#pragma unroll
+    for (int bq = 0; bq < PD; ++bq) {
+      const int quad = wk + (qi + bq) * wk_count;
+      if (qi + bq < nq_w) {  // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int slot = (bq * 4 + j) % GPB;
+          if (slot == 0) {
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+              for (int n = 0; n < NACC; ++n)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) dg[m][n][jj] = 0.0f;
+          }
+          const bool mine = tok_ok && (TT == 8 || slot_g == slot);
+          const int xo = mine ? (xoff + quad * 512 + j * 128) : zpage;
+          const uint4 xb0 = *reinterpret_cast<const uint4*>(smem + xo);
+          const uint4 xb1 = *reinterpret_cast<const uint4*>(smem + xo + 16);
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+            const uint2 wa = wbuf[bq][j][m][0];
+            const uint2 wb = wbuf[bq][j][m][1];
+            mma_bf16_m16n8k16(dg[m][0], deq_imm<0>(wa.x), deq_imm<0>(wb.x), deq_imm<4>(wa.x), deq_imm<4>(wb.x), xb0.x,
+                              xb0.y);
+            mma_bf16_m16n8k16(dg[m][1 % NACC], deq_imm<8>(wa.x), deq_imm<8>(wb.x), deq_imm<12>(wa.x),
+                              deq_imm<12>(wb.x), xb0.z, xb0.w);
+            mma_bf16_m16n8k16(dg[m][2 % NACC], deq_imm<0>(wa.y), deq_imm<0>(wb.y), deq_imm<4>(wa.y), deq_imm<4>(wb.y),
+                              xb1.x, xb1.y);
+            mma_bf16_m16n8k16(dg[m][3 % NACC], deq_imm<8>(wa.y), deq_imm<8>(wb.y), deq_imm<12>(wa.y),
+                              deq_imm<12>(wb.y), xb1.z, xb1.w);
+          }
+          if (slot == GPB - 1) {
+            fold();
+            ld_fixup<NMAT, TT>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig,
+                               (qi + bq) * 4 + j - (GPB - 1), nq_w);
+          }
+        }
+        if (qi + bq + PD < nq_w) {  // refill this pipeline slot with the quad PD steps ahead
+          ld_load_quad<NMAT>(wbuf[bq], wp);
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+            wp[m][0] += wk_count * 32;
+            wp[m][1] += wk_count * 32;
+          }
+        }
+      }
+    }
+  }
+  // an odd number of quads leaves half a block of eight multiplexed groups without its fix-up
+  if (GPB == 8 && (nq_w & 1)) {
+    fold();
+    ld_fixup<NMAT, TT>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig, (nq_w - 1) * 4,
+                       nq_w);
+  }
+}
+
+// Sums the K-split partial results of a group's warps in warp order (result in the group's first warp), then
+// folds the multiplexed columns back onto their tokens: afterwards column c < TT of the first warp holds token c.
+template <int NMAT, int TT>
+__device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red, int gid, int wk, int wk_count,
+                                               int lane) {
+  const int wid = threadIdx.x >> 5;
+  if (wk_count > 1) {
+    float* mine = red + (wid * 32 + lane) * 8;
+    if (wk != 0) {
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mine[m * 4 + j] = acc[m][j];
+    }
+    ld_group_sync(gid, wk_count);
+    if (wk == 0) {
+      for (int o = 1; o < wk_count; ++o) {
+        const float* other = red + ((wid + o) * 32 + lane) * 8;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[m][j] += other[m * 4 + j];
+      }
+    }
+  }
+  if (wk == 0 && TT < 8) {
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (TT == 1) {
+          acc[m][h * 2] += acc[m][h * 2 + 1];
+          acc[m][h * 2 + 1] = 0.0f;
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float v = acc[m][h * 2 + c];
+          if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          acc[m][h * 2 + c] = v;
+        }
+      }
+    }
+  }
+}
+
+// Debug builds (-DZMOE_LD_TIMING) record CTA 0's cycle counter at the phase boundaries in the workspace
+// header (8-byte slots from byte 64).
+#ifdef ZMOE_LD_TIMING
+#define LD_STAMP(i)                                                                     \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && threadIdx.x == 0)                                            \
+      reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.sync) + 64)[i] = clock64(); \
+  } while (0)
+#else
+#define LD_STAMP(i) \
+  do {              \
+  } while (0)
+#endif
+
+// ------------------------------------------------------------------ the kernel
+template <int TT>
+__global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int barrier_ok;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int wid = tid >> 5;
+  const int g = lane >> 2;
+  const int tig = lane & 3;
+  const int slot_g = g / TT;
+  const int tok_g = g % TT;
+
+  const int T = p.T, K = p.K, E = p.E, d = p.d, f = p.f;
+  const int R = T * K;
+  const int rtot = R + (p.n_shared ? T : 0);
+  const int ngd = d >> 6, ngf = f >> 6;
+  const LdSmem lay = ld_smem(T, K, E, d, f, p.n_shared);
+  unsigned char* xs = smem + lay.xs;
+  float* xsum = reinterpret_cast<float*>(smem + lay.xsum);
+  float* red = reinterpret_cast<float*>(smem + lay.red);
+  float* ybuf = reinterpret_cast<float*>(smem + lay.ybuf);
+  __nv_bfloat16* s_logits = reinterpret_cast<__nv_bfloat16*>(smem + lay.route);
+  float* vals = reinterpret_cast<float*>(smem + lay.route + ld_align16(T * E * 2));
+  float* gsc = vals + T * E;
+  float* sel_val = gsc + T * 64;
+  int* sel_idx = reinterpret_cast<int*>(sel_val + T * kLdMaxK);
+  LdMeta* meta = reinterpret_cast<LdMeta*>(smem + lay.meta);
+  const int zpage = lay.zero;
+  const int nblocks = gridDim.x;
+  bool alive = true;
+
+  LD_STAMP(0);
+  // ---- phase 0: token rows -> shared memory (permuted, with group sums)
+  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, p.x, p.ldx, T, d >> 3);
+  if (tid < 8) reinterpret_cast<uint32_t*>(smem + zpage)[tid] = 0u;
+  for (int i = tid; i < kLdMaxTasks; i += kLdThreads) meta->task_cnt[i] = 0;
+
+  LD_STAMP(1);
+  // ---- phase 1: router linear, one warp per expert row over the whole grid.  A lane's eight 16-byte pieces of
+  // the row are requested before anything is consumed (one memory round trip); the sum runs over i ascending
+  // per lane and then over the lanes, as in the stand-alone router kernels.
+  {
+    const int nvec = d >> 3;
+    for (int e = blockIdx.x + nblocks * wid; e < E; e += nblocks * kLdWarps) {
+      const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
+#pragma unroll 1
+      for (int t = 0; t < T; ++t) {
+        const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx);
+        float acc = 0.0f;
+#pragma unroll 1
+        for (int i0 = lane; i0 < nvec; i0 += 256) {
+          uint4 wv[8], xv[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            wv[u] = (i0 + 32 * u < nvec) ? __ldg(wrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            xv[u] = (i0 + 32 * u < nvec) ? __ldg(xrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+            const uint32_t xw[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc = fmaf(bf16_bits_to_float(ww[q] & 0xffffu), bf16_bits_to_float(xw[q] & 0xffffu), acc);
+              acc = fmaf(bf16_bits_to_float(ww[q] >> 16), bf16_bits_to_float(xw[q] >> 16), acc);
+            }
+          }
+        }
+        const float sres = warp_sum(acc);
+        if (lane == 0) p.logits[(size_t)t * E + e] = __float2bfloat16_rn(sres);
+      }
+    }
+  }
+  LD_STAMP(2);
+  alive = ld_grid_barrier(p.sync + 0, p.sync + 3, nblocks, &barrier_ok);
+  LD_STAMP(3);
+
+  if (alive) {
+    // ---- phase 2a: top-k of every row, repeated by every CTA
+    if (wid < T)
+      ld_scores_row(p.logits, s_logits, wid, E, p.family, p.rbias, p.n_group, p.topk_group, vals + wid * E,
+                    gsc + wid * 64, lane);
+    __syncthreads();
+    LD_STAMP(20);
+    ld_rank_select(vals, T, E, K, sel_val, sel_idx);
+    __syncthreads();
+    LD_STAMP(21);
+    if (wid < T)
+      ld_finish_row(s_logits, wid, E, K, p.family, p.renorm, p.scale, sel_val, sel_idx, meta->w, meta->idx, lane);
+    if (T == 1) {
+      // one token: its K experts are distinct, so slot a is task a
+      if (tid < K) {
+        meta->task_expert[tid] = sel_idx[tid];
+        meta->task_cnt[tid] = 1;
+        meta->task_rows[tid][0] = (unsigned char)tid;
+      }
+      if (tid == 0) {
+        meta->n_routed = K;
+        meta->n_tasks = K + (p.n_shared ? 1 : 0);
+        if (p.n_shared) {
+          meta->task_expert[K] = 0;
+          meta->task_cnt[K] = 1;
+          meta->task_rows[K][0] = (unsigned char)R;
+        }
+      }
+    }
+    __syncthreads();
+    LD_STAMP(4);
+    if (blockIdx.x == 0 && tid < R) {
+      if (p.weights) p.weights[tid] = meta->w[tid];
+      if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
+    }
+    if (T > 1) {
+      // ---- phase 2b: tasks = distinct experts in order of first use; a task's rows in row order
+      if (tid < R) {
+        const int e = meta->idx[tid];
+        int rk = 0;
+        for (int r = 0; r < tid; ++r) rk += (meta->idx[r] == e);
+        meta->rank[tid] = rk;
+      }
+      __syncthreads();
+      if (tid < R) {
+        const int e = meta->idx[tid];
+        int r0 = 0;
+        while (meta->idx[r0] != e) ++r0;  // first row of this expert (r0 <= tid)
+        int tk = 0;
+        for (int r = 0; r < r0; ++r) tk += (meta->rank[r] == 0);
+        const int rk = meta->rank[tid];
+        if (rk == 0) meta->task_expert[tk] = e;
+        if (rk < kLdMaxT) meta->task_rows[tk][rk] = (unsigned char)tid;
+        atomicAdd(&meta->task_cnt[tk], 1);
+      }
+      if (tid == 0) {
+        int n = 0;
+        for (int r = 0; r < R; ++r) n += (meta->rank[r] == 0);
+        meta->n_routed = n;
+        meta->n_tasks = n + (p.n_shared ? 1 : 0);
+        if (p.n_shared) {
+          meta->task_expert[n] = 0;
+          meta->task_cnt[n] = T;
+          for (int t = 0; t < T; ++t) meta->task_rows[n][t] = (unsigned char)(R + t);
+        }
+      }
+      __syncthreads();
+    }
+    const int n_tasks = meta->n_tasks;
+    const int n_routed = meta->n_routed;
+    LD_STAMP(5);
+
+    // ---- phase 2c: gate/up + SwiGLU; items (task, 16-row tile) dealt to groups of four warps over the grid
+    {
+      constexpr int WK = 4;
+      const int gid = wid >> 2, wk = wid & 3;
+      const int nq = ngd >> 2;
+      const int nq_w = (nq > wk) ? (nq - wk + WK - 1) / WK : 0;
+      const int ntiles = f >> 4;
+      const int nitems = n_tasks * ntiles;
+      const int sc_stride = qmm_sc_stride(ngd);
+      unsigned char* sraw = smem + lay.sc + gid * (4 * 16 * sc_stride);
+      const int xs_stride = qmm_xs_stride(d);
+      for (int it = gid * nblocks + blockIdx.x; it < nitems; it += nblocks * 4) {
+        const int a = it / ntiles;
+        const int n0 = (it - a * ntiles) << 4;
+        const bool is_sh = a >= n_routed;
+        const LdBank bank = ld_pick(p.gu, p.sgu, is_sh);
+        const int e = meta->task_expert[a];
+        const int cnt = meta->task_cnt[a];
+        uint2 wbuf[2][4][2][2];
+        const uint32_t* wp[2][2];
+        ld_issue_w<2, 2>(wbuf, wp, bank, e, f, d >> 3, n0, g, tig, wk, WK, nq_w);
+        ld_group_sync(gid, WK);  // the previous item is done with the group's scale area
+        ld_issue_sc<2>(bank, e, f, ngd, n0, sraw, sc_stride, tid & 127, 128);
+        // token of a task row: routed row r belongs to token r / K, shared row R + t to token t
+        const bool tok_ok = tok_g < cnt;
+        int trow = 0;
+        if (tok_ok) {
+          const int r = meta->task_rows[a][tok_g];
+          trow = is_sh ? r - R : r / K;
+        }
+        int srow_c[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int sl = (2 * tig + c) % TT;
+          srow_c[c] = -1;
+          if (sl < cnt) {
+            const int r = meta->task_rows[a][sl];
+            srow_c[c] = is_sh ? r - R : r / K;
+          }
+        }
+        LD_STAMP(11);
+        cp_async_wait_all();
+        ld_group_sync(gid, WK);
+        LD_STAMP(12);
+        float acc[2][4];
+        ld_mainloop<2, 2, TT, 2>(acc, wbuf, wp, smem, lay.xs + trow * xs_stride + tig * 32, tok_ok, zpage, slot_g, xsum,
+                              T, srow_c, sraw, sc_stride, wk, WK, nq_w, g, tig);
+        LD_STAMP(13);
+        ld_reduce_fold<2, TT>(acc, red, gid, wk, WK, lane);
+        LD_STAMP(14);
+        if (wk == 0) {
+          const int epi = is_sh ? p.sepi : p.epi;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = 2 * tig + (j & 1);
+            const bool writer = (TT == 8) || (col < TT);
+            if (writer && col < cnt) {
+              const float v = (epi == 2) ? swiglu_per_op(acc[0][j], acc[1][j]) : swiglu_cpu_contract(acc[0][j], acc[1][j]);
+              const int dst = meta->task_rows[a][col];
+              p.h[(size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0)] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+    }
+
+    LD_STAMP(6);
+    // ---- phase 3 set-up: how the 16 warps split tasks and K for one 16-column output tile
+    const int nqf = ngf >> 2;
+    int wkc = 1;
+    {
+      int best = 1 << 30;
+      for (int c = 4; c >= 1; c >>= 1) {  // ties go to the smaller split (fewer partial sums)
+        if (c > nqf) continue;
+        const int groups = kLdWarps / c;
+        const int cost = ((n_tasks + groups - 1) / groups) * ((nqf + c - 1) / c);
+        if (cost <= best) {
+          best = cost;
+          wkc = c;
+        }
+      }
+    }
+    const int ngrp = kLdWarps / wkc;
+    const int gid = wid / wkc, wk = wid % wkc;
+    const int nq_w = (nqf > wk) ? (nqf - wk + wkc - 1) / wkc : 0;
+    const int sc_stride = qmm_sc_stride(ngf);
+    unsigned char* sraw = smem + lay.sc + gid * (2 * 16 * sc_stride);
+    const int ntiles_d = d >> 4;
+    const int gtid = tid - gid * wkc * 32;
+
+    uint2 wbuf[kLdDownPD][4][1][2];
+    const uint32_t* wp[1][2];
+    // the first item's packed weights and scales depend on the routing only: stream them before the barrier
+    const bool pre = (int)blockIdx.x < ntiles_d && gid < n_tasks;
+    if (pre)
+      ld_issue_w<1, kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, f >> 3,
+                       blockIdx.x << 4, g, tig, wk, wkc, nq_w);
+    __syncthreads();  // every group of this CTA is done with the gate/up scale areas, which the next copies reuse
+    if (pre)
+      ld_issue_sc<1>(ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, ngf, blockIdx.x << 4, sraw,
+                     sc_stride, gtid, wkc * 32);
+    LD_STAMP(7);
+    alive = ld_grid_barrier(p.sync + 1, p.sync + 3, nblocks, &barrier_ok);
+    LD_STAMP(8);
+    if (alive) {
+      // ---- phase 3: stage every h row, then 16 output columns at a time: all tasks, then the combine
+      const int xs_stride = qmm_xs_stride(f);
+      ld_stage_rows<true>(xs, xs_stride, xsum, rtot, p.h, f, rtot, f >> 3);
+      __syncthreads();
+      LD_STAMP(9);
+      for (int tile = blockIdx.x; tile < ntiles_d; tile += nblocks) {
+        const int n0 = tile << 4;
+        for (int a = gid; a < n_tasks; a += ngrp) {
+          const bool is_sh = a >= n_routed;
+          const int cnt = meta->task_cnt[a];
+          if (!(pre && tile == (int)blockIdx.x && a == gid)) {
+            const LdBank bank = ld_pick(p.dn, p.sdn, is_sh);
+            ld_issue_w<1, kLdDownPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc, nq_w);
+            ld_group_sync(gid, wkc);  // the previous item is done with the group's scale area
+            ld_issue_sc<1>(bank, meta->task_expert[a], d, ngf, n0, sraw, sc_stride, gtid, wkc * 32);
+          }
+          const bool tok_ok = tok_g < cnt;
+          const int srow = tok_ok ? meta->task_rows[a][tok_g] : 0;
+          int srow_c[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int sl = (2 * tig + c) % TT;
+            srow_c[c] = (sl < cnt) ? (int)meta->task_rows[a][sl] : -1;
+          }
+          LD_STAMP(15);
+          cp_async_wait_all();
+          ld_group_sync(gid, wkc);
+          LD_STAMP(16);
+          float acc[1][4];
+          ld_mainloop<1, kLdDownPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok, zpage, slot_g, xsum,
+                                rtot, srow_c, sraw, sc_stride, wk, wkc, nq_w, g, tig);
+          LD_STAMP(17);
+          ld_reduce_fold<1, TT>(acc, red, gid, wk, wkc, lane);
+          LD_STAMP(18);
+          if (wk == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = 2 * tig + (j & 1);
+              const bool writer = (TT == 8) || (col < TT);
+              if (writer && col < cnt) ybuf[(int)meta->task_rows[a][col] * 16 + g + ((j >> 1) ? 8 : 0)] = acc[0][j];
+            }
+          }
+        }
+        __syncthreads();
+        LD_STAMP(19);
+        // ordered combine: thread (token, column) walks the K slots; projected values are rounded to T first,
+        // as the separate-kernel path stores them
+        if (tid < T * 16) {
+          const int t = tid >> 4, n = tid & 15;
+          const int mode = p.combine_mode;
+          float a0 = 0.0f;
+          for (int i = 0; i < K; ++i) {
+            float wi = meta->w[t * K + i];
+            if (p.out_flags & 2) wi = round_bf16(wi);
+            const float v0 = round_bf16(ybuf[(t * K + i) * 16 + n]);
+            if (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_T) {
+              a0 = fmaf(wi, v0, a0);
+            } else if (mode == ZMOE_COMBINE_FP32_NO_FMA || mode == ZMOE_COMBINE_NO_FMA) {
+              a0 = __fadd_rn(a0, __fmul_rn(wi, v0));
+            } else if (mode == ZMOE_COMBINE_EXACT) {
+              wi = round_bf16(wi);
+              a0 = round_bf16(__fadd_rn(a0, round_bf16(__fmul_rn(wi, v0))));
+            } else {
+              a0 = round_bf16(__fadd_rn(a0, __fmul_rn(wi, v0)));
+            }
+          }
+          const size_t oo = (size_t)t * d + n0 + n;
+          const bool fp32_mode = (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_FP32_NO_FMA);
+          if (fp32_mode && !(p.out_flags & 1)) {
+            reinterpret_cast<float*>(p.out)[oo] = a0;
+          } else {
+            a0 = round_bf16(a0);
+            if (p.n_shared) a0 = __fadd_rn(a0, round_bf16(ybuf[(R + t) * 16 + n]));
+            reinterpret_cast<__nv_bfloat16*>(p.out)[oo] = __float2bfloat16_rn(a0);
+          }
+        }
+        __syncthreads();
+      }
+    }
+  }
+
+  // ---- exit: the last CTA to leave puts the barrier counters back to zero for the next launch
+  __syncthreads();
+  LD_STAMP(10);
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(p.sync + 2, 1) == nblocks - 1) {
+      p.sync[0] = 0;
+      p.sync[1] = 0;
+      __threadfence();
+      p.sync[2] = 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+constexpr int kLdMaxDevices = 64;
+static std::mutex g_ld_mutex;
+static int g_ld_sms[kLdMaxDevices] = {};
+
+static int ld_sm_count(int* out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kLdMaxDevices)
+    return fail(ZMOE_ERR_UNSUPPORTED, "zmoe_layer_decode: device ordinal %d beyond %d", dev, kLdMaxDevices);
+  std::lock_guard<std::mutex> lock(g_ld_mutex);
+  if (g_ld_sms[dev] == 0) {
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || n <= 0)
+      return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: SM count query failed: %s", cudaGetErrorString(e));
+    g_ld_sms[dev] = n;
+  }
+  *out = g_ld_sms[dev];
+  return ZMOE_OK;
+}
+
+// Why a block shape cannot take the one-launch path (nullptr: it can).
+static const char* ld_unsupported(const zmoe_layer_desc* L, int T) {
+  if (L->qmode != ZMOE_Q_AFFINE4 || L->group_size != 64) return "needs 4-bit affine weights with group size 64";
+  if (T < 1 || T > kLdMaxT) return "takes 1..8 tokens";
+  if (L->top_k < 1 || L->top_k > kLdMaxK) return "takes top_k <= 8";
+  if (L->E < L->top_k || L->E > 256) return "takes at most 256 experts";
+  if (L->d_model % 256 != 0 || L->d_ff % 256 != 0) return "needs d_model and d_ff to be multiples of 256";
+  if (L->n_shared < 0 || L->n_shared > 1) return "takes at most one shared expert";
+  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared);
+  if (lay.total > 220 * 1024) return "needs more shared memory than an SM has";
+  return nullptr;
+}
+
+static size_t ld_ws_logits_off() { return 256; }
+static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
+  return (ld_ws_logits_off() + (size_t)T * L->E * 2 + 255) & ~(size_t)255;
+}
+
+template <int TT>
+static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_t st) {
+  auto kern = layer_decode_kernel<TT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (e != cudaSuccess)
+    return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
+                cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kLdThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // every CTA resident at once: the barriers rely on it
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, p);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: launch failed: %s", cudaGetErrorString(e));
+  return check_launch("layer_decode_kernel");
+}
+
+}  // namespace zmoe
+
+using namespace zmoe;
+
+extern "C" {
+
+size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T) {
+  if (!L || ld_unsupported(L, T)) return 0;
+  const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
+  return ld_ws_h_off(L, T) + rows * L->d_ff * 2;
+}
+
+int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
+                      size_t workspace_bytes, float* weights, uint32_t* indices, void* out, void* stream) {
+  ZMOE_REQUIRE(L && x && workspace && out, ZMOE_ERR_SHAPE, "zmoe_layer_decode: null pointer");
+  const char* why = ld_unsupported(L, T);
+  ZMOE_REQUIRE(why == nullptr, ZMOE_ERR_UNSUPPORTED, "zmoe_layer_decode: the one-launch path %s", why);
+  ZMOE_REQUIRE(L->router_w && L->routed.gate_w && L->routed.gate_scales && L->routed.gate_biases && L->routed.up_w &&
+                   L->routed.up_scales && L->routed.up_biases && L->routed.down_w && L->routed.down_scales &&
+                   L->routed.down_biases,
+               ZMOE_ERR_SHAPE, "zmoe_layer_decode: null router or expert tensor");
+  if (L->n_shared)
+    ZMOE_REQUIRE(L->shared.gate_w && L->shared.gate_scales && L->shared.gate_biases && L->shared.up_w &&
+                     L->shared.up_scales && L->shared.up_biases && L->shared.down_w && L->shared.down_scales &&
+                     L->shared.down_biases,
+                 ZMOE_ERR_SHAPE, "zmoe_layer_decode: null shared-expert tensor");
+  ZMOE_REQUIRE(L->router_family >= 0 && L->router_family <= 2, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: router family %d", L->router_family);
+  if (L->router_family == 2) {
+    ZMOE_REQUIRE(L->router_bias != nullptr, ZMOE_ERR_SHAPE, "zmoe_layer_decode: the sigmoid router needs a bias");
+    ZMOE_REQUIRE(L->n_group >= 1 && L->n_group <= 32 && L->topk_group >= 1 && L->topk_group <= L->n_group &&
+                     L->E % L->n_group == 0,
+                 ZMOE_ERR_SHAPE, "zmoe_layer_decode: invalid n_group=%d / topk_group=%d", L->n_group, L->topk_group);
+  }
+  ZMOE_REQUIRE(!(L->router_family == 0 && L->router_bias), ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: a bias needs the softmax-then-top-k family");
+  ZMOE_REQUIRE(L->swiglu_mode == ZMOE_SWIGLU_CPU || L->swiglu_mode == ZMOE_SWIGLU_PER_OP, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: swiglu_mode %d", L->swiglu_mode);
+  ZMOE_REQUIRE(!L->n_shared || L->shared_swiglu_mode == ZMOE_SWIGLU_CPU || L->shared_swiglu_mode == ZMOE_SWIGLU_PER_OP,
+               ZMOE_ERR_UNSUPPORTED, "zmoe_layer_decode: shared_swiglu_mode %d", L->shared_swiglu_mode);
+  ZMOE_REQUIRE(L->combine_mode >= ZMOE_COMBINE_FP32 && L->combine_mode <= ZMOE_COMBINE_STREAM_T, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: combine mode %d", L->combine_mode);
+  const bool fp32_out = (L->combine_mode == ZMOE_COMBINE_FP32 || L->combine_mode == ZMOE_COMBINE_FP32_NO_FMA) &&
+                        !(L->out_flags & 1);
+  ZMOE_REQUIRE(!(L->n_shared && fp32_out), ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: a shared expert needs an output in T");
+  ZMOE_REQUIRE(ldx >= L->d_model && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0, ZMOE_ERR_ALIGN,
+               "zmoe_layer_decode: x rows must be 16-byte aligned (ldx=%d)", ldx);
+  ZMOE_REQUIRE(((uintptr_t)L->router_w % 16) == 0 && ((uintptr_t)workspace % 256) == 0, ZMOE_ERR_ALIGN,
+               "zmoe_layer_decode: router_w must be 16-byte and the workspace 256-byte aligned");
+  const zmoe_expert_bank* banks[2] = {&L->routed, L->n_shared ? &L->shared : nullptr};
+  for (int i = 0; i < 2; ++i) {
+    if (!banks[i]) continue;
+    const void* ptrs[9] = {banks[i]->gate_w,    banks[i]->gate_scales, banks[i]->gate_biases,
+                           banks[i]->up_w,      banks[i]->up_scales,   banks[i]->up_biases,
+                           banks[i]->down_w,    banks[i]->down_scales, banks[i]->down_biases};
+    for (int j = 0; j < 9; ++j)
+      ZMOE_REQUIRE(((uintptr_t)ptrs[j] % 8) == 0, ZMOE_ERR_ALIGN,
+                   "zmoe_layer_decode: packed weights, scales and biases must be 8-byte aligned");
+  }
+  const size_t need = zmoe_layer_decode_workspace_bytes(L, T);
+  ZMOE_REQUIRE(workspace_bytes >= need, ZMOE_ERR_WORKSPACE, "zmoe_layer_decode: workspace of %zu bytes, need %zu",
+               workspace_bytes, need);
+
+  LdParams p;
+  p.x = (const __nv_bfloat16*)x;
+  p.ldx = ldx;
+  p.T = T;
+  p.wr = (const __nv_bfloat16*)L->router_w;
+  p.rbias = L->router_bias;
+  p.family = L->router_family;
+  p.renorm = L->renorm;
+  p.n_group = L->n_group;
+  p.topk_group = L->topk_group;
+  p.scale = (L->router_family == 2) ? L->routed_scale : 1.0f;
+  p.E = L->E;
+  p.d = L->d_model;
+  p.f = L->d_ff;
+  p.K = L->top_k;
+  auto fill = [](LdBank& gu, LdBank& dn, const zmoe_expert_bank& b) {
+    gu.w[0] = b.gate_w;
+    gu.w[1] = b.up_w;
+    gu.s[0] = (const __nv_bfloat16*)b.gate_scales;
+    gu.s[1] = (const __nv_bfloat16*)b.up_scales;
+    gu.b[0] = (const __nv_bfloat16*)b.gate_biases;
+    gu.b[1] = (const __nv_bfloat16*)b.up_biases;
+    dn.w[0] = dn.w[1] = b.down_w;
+    dn.s[0] = dn.s[1] = (const __nv_bfloat16*)b.down_scales;
+    dn.b[0] = dn.b[1] = (const __nv_bfloat16*)b.down_biases;
+  };
+  fill(p.gu, p.dn, L->routed);
+  fill(p.sgu, p.sdn, L->n_shared ? L->shared : L->routed);
+  p.n_shared = L->n_shared;
+  p.epi = L->swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : 2;
+  p.sepi = L->shared_swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : 2;
+  p.combine_mode = L->combine_mode;
+  p.out_flags = L->out_flags;
+  unsigned char* ws = (unsigned char*)workspace;
+  p.sync = (int*)ws;
+  p.logits = (__nv_bfloat16*)(ws + ld_ws_logits_off());
+  p.h = (__nv_bfloat16*)(ws + ld_ws_h_off(L, T));
+  p.weights = weights;
+  p.indices = indices;
+  p.out = out;
+
+  int sms = 0;
+  int rc = ld_sm_count(&sms);
+  if (rc != ZMOE_OK) return rc;
+  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (T <= 1) return ld_launch<1>(p, sms, lay.total, st);
+  if (T <= 2) return ld_launch<2>(p, sms, lay.total, st);
+  if (T <= 4) return ld_launch<4>(p, sms, lay.total, st);
+  return ld_launch<8>(p, sms, lay.total, st);
+}
+
+}  // extern "C"

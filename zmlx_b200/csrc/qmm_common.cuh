@@ -46,6 +46,40 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t word, uint32_t mask, uint3
   return r;
 }
 
+__host__ __device__ inline int qmm_xs_stride(int K) { return K * 2 + 16; }
+__host__ __device__ inline int qmm_sc_stride(int ngroups) { return ((ngroups + 3) & ~3) * 2 + 8; }
+
+// 8-byte streaming load at a compile-time byte offset from a register base: the offset
+// lives in the instruction, so a quad of groups costs no address arithmetic.
+template <int OFF>
+__device__ __forceinline__ uint2 ldg_stream_u2(const uint32_t* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2+%3];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p), "n"(OFF));
+  return v;
+}
+
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// codes at bits [sh, sh+4) and [sh+16, sh+20) -> bf16x2 (128+q_lo, 128+q_hi)
+template <int SH>
+__device__ __forceinline__ uint32_t deq_imm(uint32_t word) {
+  uint32_t r;
+  if (SH == 0) {
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(word));
+  } else {
+    asm("{ .reg .b32 t; shr.b32 t, %1, %2; lop3.b32 %0, t, 0x000F000F, 0x43004300, 0xEA; }"
+        : "=r"(r)
+        : "r"(word), "n"(SH));
+  }
+  return r;
+}
+
 __device__ __forceinline__ float swiglu_cpu_contract(float g, float u) {
   g = round_bf16(g);
   u = round_bf16(u);

@@ -100,7 +100,7 @@ class EPMoELayer:
         local = params if sharded else shard_params(params, self.lo, self.hi)
         self.n_local = self.hi - self.lo
         # the single-GPU layer object provides buffers and the replicated router on all R*T tokens
-        self.inner = MoELayer(cfg, local, max_tokens=max_tokens * world)
+        self.inner = MoELayer(cfg, local, max_tokens=max_tokens * world, fused=False)
         dev = self.inner.device
         TK = max_tokens * world * cfg.top_k
         self.local_idx = torch.empty((TK,), dtype=torch.int32, device=dev)

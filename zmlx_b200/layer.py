@@ -23,7 +23,7 @@ class MoELayer:
     """Packed weights of one MoE layer plus the buffers of its forward pass."""
 
     def __init__(self, cfg: MoEConfig, params: dict, *, max_tokens: int = 64, combine: str | None = None,
-                 swiglu: str | None = None):
+                 swiglu: str | None = None, fused: bool = True):
         self.cfg = cfg
         self.p = params
         dev = params["gate_w"].device
@@ -36,6 +36,74 @@ class MoELayer:
         self.swiglu = _lib.SWIGLU_CPU if sw == "cpu" else _lib.SWIGLU_PER_OP
         self.gs = 32 if cfg.mode == "mxfp4" else cfg.group_size
         self._alloc(max_tokens)
+        self.fused = bool(fused)
+        self._desc = self._describe()
+        self._fused_ws: dict[int, torch.Tensor] = {}
+
+    # -- one-launch decode path ---------------------------------------------
+    FUSED_MAX_TOKENS = 8
+
+    def _describe(self) -> _lib.LayerDesc:
+        """The block as a ``zmoe_layer_desc`` (pointers into this layer's tensors, which it keeps alive)."""
+        cfg, W = self.cfg, self.p
+        family, bias, renorm = self._route_args()
+        d = _lib.LayerDesc()
+        d.E, d.d_model, d.d_ff, d.top_k = cfg.n_experts, cfg.d_model, cfg.d_ff, cfg.top_k
+        d.group_size, d.qmode = self.gs, ops.qmode_code(cfg.mode)
+        d.router_family, d.renorm, d.n_group, d.topk_group = family, renorm, cfg.n_group, cfg.topk_group
+        d.routed_scale = float(cfg.routed_scaling_factor) if family == 2 else 1.0
+        d.n_shared = int(cfg.n_shared)
+        d.swiglu_mode, d.shared_swiglu_mode = self.swiglu, _lib.SWIGLU_PER_OP
+        d.combine_mode = self.combine_mode
+        d.out_flags = 3 if cfg.family == "generic" else 1
+        d.router_w = W["router_w"].data_ptr()
+        d.router_bias = bias.data_ptr() if bias is not None else None
+
+        def bank(dst, src):
+            for proj in ("gate", "up", "down"):
+                setattr(dst, f"{proj}_w", src[f"{proj}_w"].data_ptr())
+                setattr(dst, f"{proj}_scales", src[f"{proj}_s"].data_ptr())
+                b = src.get(f"{proj}_b")
+                setattr(dst, f"{proj}_biases", b.data_ptr() if b is not None else None)
+
+        bank(d.routed, W)
+        if cfg.n_shared:
+            bank(d.shared, W["shared"])
+        return d
+
+    def fused_workspace_bytes(self, T: int) -> int:
+        """Bytes of workspace the one-launch path needs for T tokens; 0 when the block's shape is outside it."""
+        if T < 1 or T > self.FUSED_MAX_TOKENS:
+            return 0
+        return int(_lib.load().zmoe_layer_decode_workspace_bytes(ctypes.byref(self._desc), T))
+
+    def forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        """The whole block in one cooperative launch (``zmoe_layer_decode``); raises if the shape is outside it."""
+        T = x.shape[0]
+        ws = self._fused_ws.get(T)
+        if ws is None:
+            need = self.fused_workspace_bytes(T)
+            if need == 0:
+                raise _lib.ZmoeError(_lib.ERR_UNSUPPORTED, f"no one-launch path for this block at T={T}")
+            ws = torch.zeros(need, dtype=torch.uint8, device=self.device)  # the sync words start at zero
+            self._fused_ws[T] = ws
+        p = ops._ptr
+        _lib.check(_lib.load().zmoe_layer_decode(ctypes.byref(self._desc), p(x), x.stride(0), T, p(ws), ws.numel(),
+                                                 p(self.weights), p(self.indices), p(self.out), ops._stream()))
+        return self.out[:T]
+
+    def router_logits(self, T: int) -> torch.Tensor:
+        """The (T, E) bf16 router logits of the last forward pass over T tokens (whichever path ran it)."""
+        ws = self._fused_ws.get(T) if self.fused else None
+        if ws is None:
+            return self.logits[:T]
+        E = self.cfg.n_experts
+        return ws[256:256 + T * E * 2].view(torch.bfloat16).view(T, E)
+
+    def fused_status(self, T: int) -> int:
+        """The status word of the T-token workspace: non-zero after a bounded grid-barrier wait ran out."""
+        ws = self._fused_ws.get(T)
+        return 0 if ws is None else int(ws[:16].view(torch.int32)[3].item())
 
     def _alloc(self, T: int) -> None:
         cfg, dev = self.cfg, self.device
@@ -151,6 +219,8 @@ class MoELayer:
         if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
             x = x.contiguous()
         with torch.cuda.device(self.device):
+            if self.fused and (T in self._fused_ws or self.fused_workspace_bytes(T) > 0):
+                return self.forward_fused(x)
             self.route(x)
             self.experts(x)
             residual = None
