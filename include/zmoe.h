@@ -260,14 +260,15 @@ typedef struct zmoe_layer_desc {
  * size 64, 1..8 tokens, top_k <= 8, E <= 256, d_model and d_ff multiples of 256; other shapes fail with
  * ZMOE_ERR_UNSUPPORTED (zmoe_layer_decode_workspace_bytes returns 0 for them) and take the separate calls.
  *
- * workspace: zmoe_layer_decode_workspace_bytes(L, T) bytes, 256-byte aligned.  Its first 256 bytes are a
- * header that starts with four ints {barrier, barrier, exit count, status}; the header must be zero
- * before the first call and the kernel
- * leaves the first three zero.  The CTAs of the launch meet at two grid-wide barriers; each wait is
- * bounded, and a wait that runs out sets status to 1 and ends the launch with `out` undefined.  One
- * workspace serves one stream at a time.  x (T, d_model) T with row stride ldx; out (T, d_model) T
- * (float for the FP32 combine modes without out_flags bit 0); weights (T, top_k) float and indices
- * (T, top_k) uint32 receive the routing when not NULL.
+ * workspace: zmoe_layer_decode_workspace_bytes(L, T) bytes, 256-byte aligned, ALL ZERO before the first
+ * call, then left to the library and used with the same T (zero it again before changing T).  It starts
+ * with five ints {-, -, exit count, status, launch count}.  CTAs hand the router logits and the
+ * activated rows to each other through the workspace as tagged 32-bit words and re-read a word until it
+ * carries the current launch's tag; every such wait is bounded, and one that runs out sets status to 1
+ * and ends the launch with `out` undefined.  One workspace serves one stream at a time.
+ * x (T, d_model) T with row stride ldx; out (T, d_model) T (float for the FP32 combine modes without
+ * out_flags bit 0); weights (T, top_k) float and indices (T, top_k) uint32 receive the routing when not
+ * NULL.
  */
 size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T);
 int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,

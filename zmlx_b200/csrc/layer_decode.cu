@@ -61,9 +61,9 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
-  int* sync;  // {barrier 1, barrier 2, exit count, status}
-  __nv_bfloat16* logits;
-  __nv_bfloat16* h;
+  int* sync;         // {-, -, exit count, status, launch count}
+  uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
+  uint32_t* h;       // (rows, f) hand-over words
   float* weights;
   uint32_t* indices;
   void* out;
@@ -105,7 +105,7 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   m.ybuf = a;
   a += ld_align16(rtot * 16 * 4);
   m.route = a;
-  a += ld_align16(T * E * 2) + ld_align16(T * (E + 64 + 2 * kLdMaxK) * 4);  // logits, scores, group scratch, winners
+  a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);  // per row: scores, logits, sort keys, group scratch, winners
   m.meta = a;
   a += ld_align16((int)sizeof(LdMeta));
   m.zero = a;
@@ -114,38 +114,7 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   return m;
 }
 
-// ------------------------------------------------------------------ grid barrier
-__device__ __forceinline__ int ld_acquire_s32(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_inc(int* p) {
-  asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p) : "memory");
-}
-
-// All CTAs of the (co-resident) grid meet here.  Returns false when the wait ran out.
-__device__ __forceinline__ bool ld_grid_barrier(int* ctr, int* status, int nblocks, int* ok_s) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    __threadfence();
-    red_release_inc(ctr);
-    int spins = 0;
-    while (ld_acquire_s32(ctr) < nblocks) {
-      if (++spins > kLdSpinLimit) {
-        ok = 0;
-        atomicExch(status, 1);
-        break;
-      }
-    }
-    __threadfence();
-    *ok_s = ok;
-  }
-  __syncthreads();
-  return *ok_s != 0;
-}
-
+// ------------------------------------------------------------------ warp-group barrier
 __device__ __forceinline__ void ld_group_sync(int gid, int wk_count) {
   if (wk_count == 1)
     __syncwarp();
@@ -153,14 +122,45 @@ __device__ __forceinline__ void ld_group_sync(int gid, int wk_count) {
     asm volatile("bar.sync %0, %1;" ::"r"(gid + 1), "r"(wk_count * 32) : "memory");
 }
 
+// ------------------------------------------------------------------ hand-over words
+// Values that one CTA produces and others consume (router logits, h rows) travel as 32-bit words
+// {launch tag : 16 | bfloat16 : 16}.  A consumer re-reads a word until its tag is the current launch's, so
+// the value and its "ready" flag arrive in one relaxed access and no grid-wide barrier is needed.  The tag
+// is 1 + (launch count mod 65535): never zero, so a zeroed workspace holds no valid word.
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Order-preserving map float -> uint32 (for finite values and infinities; -0 must be folded into +0 first).
+__device__ __forceinline__ uint32_t ld_order_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 // ------------------------------------------------------------------ staging of token rows
 // Rows go to shared memory with every 8-element block permuted to (0,4,1,5,2,6,3,7) -- the order in
 // which a lane's two 16-byte reads give the B fragments of four k16 steps -- plus per-group sums.
-template <bool COHERENT>
-__device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float* xsum, int xsum_stride,
-                                              const __nv_bfloat16* src, int ld, int nrows, int K8) {
+// TAGGED: the source holds hand-over words (see below); a block is re-read until its eight tags are the
+// current launch's.  Returns false when such a wait ran out.
+template <bool TAGGED>
+__device__ __forceinline__ bool ld_stage_rows(unsigned char* xs, int xs_stride, float* xsum, int xsum_stride,
+                                              const void* src, int ld, int nrows, int K8, uint32_t tag) {
   const int total = nrows * K8;
   const int lane = threadIdx.x & 31;
+  bool good = true;
 #pragma unroll 1
   for (int base = (int)(threadIdx.x & ~31u); base < total; base += kLdThreads) {
     const int i = base + lane;
@@ -170,8 +170,28 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
     if (ok) {
       t = i / K8;
       blk = i - t * K8;
-      const uint4* src4 = reinterpret_cast<const uint4*>(src + (size_t)t * ld) + blk;
-      v = COHERENT ? __ldcg(src4) : __ldg(src4);
+      if (TAGGED) {
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)t * ld + blk * 8;
+        uint4 a, b;
+        int spins = 0;
+        for (;;) {
+          a = ld_relaxed_v4(w32);
+          b = ld_relaxed_v4(w32 + 4);
+          const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
+                                (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
+          if (bad == 0u) break;
+          if (++spins >= kLdSpinLimit) {
+            good = false;
+            break;
+          }
+        }
+        v.x = (a.x & 0xffffu) | (a.y << 16);
+        v.y = (a.z & 0xffffu) | (a.w << 16);
+        v.z = (b.x & 0xffffu) | (b.y << 16);
+        v.w = (b.z & 0xffffu) | (b.w << 16);
+      } else {
+        v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + (size_t)t * ld) + blk);
+      }
       uint4 o;
       o.x = __byte_perm(v.x, v.z, 0x5410);
       o.y = __byte_perm(v.x, v.z, 0x7632);
@@ -188,151 +208,165 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
     part += __shfl_xor_sync(0xffffffffu, part, 4);
     if (ok && (lane & 7) == 0) xsum[(blk >> 3) * xsum_stride + t] = part;
   }
+  return good;
 }
 
-// ------------------------------------------------------------------ top-k of the T rows, whole CTA
+// ------------------------------------------------------------------ routing of the T token rows
 // Same arithmetic as the per-row router functions (softmax_topk_row / sigmoid_topk_row: the order of every
-// floating-point sum is kept, so scores, indices and weights are bit-identical), but the selection -- ranking
-// every score against every other one -- is spread over all threads instead of one warp per row.
+// floating-point sum is kept, so scores, indices and weights are bit-identical).  A single warp is slow at
+// long dependent instruction sequences, so only what must be is done by one warp per row (waiting for the
+// logits, the softmax / sigmoid scores, the weights of the winners); the selection itself -- ranking every
+// score against every other one -- is spread over all threads of the CTA.
 //
-// Step 1, one warp per row: the row's selection scores -> vals[t][E].
-__device__ __forceinline__ void ld_scores_row(const __nv_bfloat16* g_logits, __nv_bfloat16* s_logits, int row, int E,
-                                              int family, const float* bias, int n_group, int topk_group,
-                                              float* vals, float* gsc /* 64 floats */, int lane) {
-  constexpr int NJ = 8;  // values per lane: E <= 256
-  __nv_bfloat16* lg = s_logits + (size_t)row * E;
-  float v[NJ];
-  {  // the row's logits were written by other CTAs before the barrier: read them through L2, all at once
-    const unsigned short* gl = reinterpret_cast<const unsigned short*>(g_logits) + (size_t)row * E;
-    unsigned short raw[NJ];
+// Step 1, one warp per row: wait for the row's logits (hand-over words written by the router warps of all
+// CTAs), compute the selection scores and leave, per expert, the score, the logit and a 64-bit sort key
+// {order-preserving score : 32 | ~expert id : 32} in shared memory.  Returns false when the wait ran out.
+template <int NJ>
+__device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32_t tag, int E, int family,
+                                                const float* bias, int n_group, int topk_group, float* vals,
+                                                float* lgs, uint2* keys, float* gsc /* 64 floats */, int lane,
+                                                long long* dbg = nullptr) {
+  float lg[NJ], v[NJ];
+  {
+    uint32_t raw[NJ];
+    int spins = 0;
+    bool ok;
+    do {
+      ok = true;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) raw[j] = (lane + 32 * j < E) ? __ldcg(gl + lane + 32 * j) : (unsigned short)0;
+      for (int j = 0; j < NJ; ++j) {
+        raw[j] = tag;
+        if (lane + 32 * j < E) raw[j] = ld_relaxed_u32(g_logits + (size_t)(lane + 32 * j) * 8);
+        ok = ok && ((raw[j] & 0xffff0000u) == tag);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+    } while (!ok && ++spins < kLdSpinLimit);
+    if (!ok) return false;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      if (lane + 32 * j < E) reinterpret_cast<unsigned short*>(lg)[lane + 32 * j] = raw[j];
-      v[j] = bf16_bits_to_float(raw[j]);
+    for (int j = 0; j < NJ; ++j) lg[j] = bf16_bits_to_float(raw[j] & 0xffffu);
+    if (dbg && lane == 0) {
+      dbg[22] = clock64();
+      dbg[23] = spins;
     }
   }
   if (family == 0) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < E) vals[lane + 32 * j] = v[j];
-    return;
-  }
-  if (family == 1) {
+    for (int j = 0; j < NJ; ++j) v[j] = lg[j];
+  } else if (family == 1) {
     float mx = -CUDART_INF_F;
 #pragma unroll
     for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < E) mx = fmaxf(mx, v[j]);
+      if (lane + 32 * j < E) mx = fmaxf(mx, lg[j]);
     mx = warp_max(mx);
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
-      v[j] = (lane + 32 * j < E) ? expf(v[j] - mx) : 0.0f;
+      v[j] = (lane + 32 * j < E) ? expf(lg[j] - mx) : 0.0f;
       sum += v[j];
     }
     sum = warp_sum(sum);
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
+      v[j] = v[j] / sum;
+      if (bias && lane + 32 * j < E) v[j] += bias[lane + 32 * j];
+    }
+  } else {
+    // sigmoid + selection bias, optional group-limited selection
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
       const int idx = lane + 32 * j;
+      v[j] = 0.0f;
       if (idx < E) {
-        float q = v[j] / sum;
-        if (bias) q += bias[idx];
-        vals[idx] = q;
+        v[j] = sigmoid_stable(lg[j]) + bias[idx];
+        vals[idx] = v[j];
       }
     }
-    return;
+    if (n_group > 1) {
+      float* gkeep = gsc + 32;
+      __syncwarp();
+      const int per = E / n_group;
+      if (lane < n_group) {
+        float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+#pragma unroll 4
+        for (int j = 0; j < per; ++j) {
+          const float x = vals[lane * per + j];
+          if (x > t1) {
+            t2 = t1;
+            t1 = x;
+          } else if (x > t2) {
+            t2 = x;
+          }
+        }
+        gsc[lane] = t1 + t2;
+      }
+      __syncwarp();
+      if (lane < n_group) {
+        const float mine = gsc[lane];
+        int rank = 0;
+        for (int h = 0; h < n_group; ++h) {
+          const float o = gsc[h];
+          rank += (o > mine) || (o == mine && h < lane);
+        }
+        gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int idx = lane + 32 * j;
+        if (idx < E && gkeep[idx / per] == 0.0f) v[j] = 0.0f;
+      }
+    }
   }
-  // sigmoid + selection bias, optional group-limited selection
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
     const int idx = lane + 32 * j;
     if (idx < E) {
-      v[j] = sigmoid_stable(v[j]) + bias[idx];
       vals[idx] = v[j];
+      lgs[idx] = lg[j];
+      keys[idx] = make_uint2(~(uint32_t)idx, ld_order_key(v[j] + 0.0f));  // .y is the high half
     }
   }
-  if (n_group > 1) {
-    float* gkeep = gsc + 32;
-    __syncwarp();
-    const int per = E / n_group;
-    if (lane < n_group) {
-      float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
-#pragma unroll 8
-      for (int j = 0; j < per; ++j) {
-        const float x = vals[lane * per + j];
-        if (x > t1) {
-          t2 = t1;
-          t1 = x;
-        } else if (x > t2) {
-          t2 = x;
-        }
-      }
-      gsc[lane] = t1 + t2;
-    }
-    __syncwarp();
-    if (lane < n_group) {
-      const float mine = gsc[lane];
-      int rank = 0;
-      for (int h = 0; h < n_group; ++h) {
-        const float o = gsc[h];
-        rank += (o > mine) || (o == mine && h < lane);
-      }
-      gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
-    }
-    __syncwarp();
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int idx = lane + 32 * j;
-      if (idx < E && gkeep[idx / per] == 0.0f) vals[idx] = 0.0f;
-    }
-  }
+  return true;
 }
 
-// Step 2, all threads: rank of every score under (score descending, expert id ascending); the ranks of a row
-// are a permutation, so the entries ranked below K write themselves into slot order.
-__device__ __forceinline__ void ld_rank_select(const float* vals, int T, int E, int K, float* sel_val, int* sel_idx) {
+// Step 2, all threads: rank of every score under (score descending, expert id ascending) -- one unsigned
+// 64-bit comparison of the sort keys.  The ranks of a row are a permutation, so the experts ranked below K
+// write themselves into slot order.
+__device__ __forceinline__ void ld_rank_select(const uint2* keys, int T, int E, int K, int* sel_idx) {
   const int pairs = T * E;
   int P = 1;  // threads that share one score's scan
   while (P < 32 && P * 2 * pairs <= kLdThreads) P *= 2;
-  const int per_pass = kLdThreads / P;
+  const int lp = 31 - __clz(P);
+  const int per_pass = kLdThreads >> lp;
   const int part = threadIdx.x & (P - 1);
   for (int base = 0; base < pairs; base += per_pass) {
-    const int pair = base + (threadIdx.x / P);
+    const int pair = base + (threadIdx.x >> lp);
     const bool ok = pair < pairs;
     const int t = ok ? pair / E : 0;
     const int i = ok ? pair - t * E : 0;
-    const float* row = vals + (size_t)t * E;
-    const float v = row[i];
+    const unsigned long long* row = reinterpret_cast<const unsigned long long*>(keys + (size_t)t * E);
+    const unsigned long long mine = row[i];
     int rank = 0;
 #pragma unroll 4
-    for (int j = part; j < E; j += P) {
-      const float ov = row[j];
-      rank += (ov > v) || (ov == v && j < i);
-    }
+    for (int j = part; j < E; j += P) rank += (row[j] > mine);
     for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-    if (ok && part == 0 && rank < K) {
-      sel_val[t * K + rank] = v;
-      sel_idx[t * K + rank] = i;
-    }
+    if (ok && part == 0 && rank < K) sel_idx[t * K + rank] = i;
   }
 }
 
 // Step 3, one warp per row: the weights of the selected experts.  Lane i < K owns slot i; sums run over the
 // slots in order 0..K-1 (every lane repeats them), as in the per-row router functions.
-__device__ __forceinline__ void ld_finish_row(const __nv_bfloat16* s_logits, int row, int E, int K, int family,
-                                              int renorm, float scale, const float* sel_val, const int* sel_idx,
-                                              float* w_out, int* idx_out, int lane) {
-  const int li = lane < K ? lane : 0;
-  const float sv = sel_val[row * K + li];
-  const int si = sel_idx[row * K + li];
+__device__ __forceinline__ void ld_finish_row(const float* vals, const float* lgs, int K, int family, int renorm,
+                                              float scale, const int* sel_idx, float* w_out, int* idx_out, int lane) {
+  const int si = sel_idx[lane < K ? lane : 0];
+  const float sv = vals[si];
   float mine;  // the slot's term of the normalising sum
   if (family == 0)
-    mine = expf(sv - sel_val[row * K]);
+    mine = expf(sv - vals[sel_idx[0]]);
   else if (family == 1)
     mine = sv;
   else
-    mine = sigmoid_stable(__bfloat162float(s_logits[(size_t)row * E + si]));
+    mine = sigmoid_stable(lgs[si]);
   float sum = 0.0f;
   for (int i = 0; i < K; ++i) sum += __shfl_sync(0xffffffffu, mine, i);
   float w;
@@ -347,8 +381,8 @@ __device__ __forceinline__ void ld_finish_row(const __nv_bfloat16* s_logits, int
     if (scale != 1.0f) w = w * scale;
   }
   if (lane < K) {
-    w_out[row * K + lane] = w;
-    idx_out[row * K + lane] = si;
+    w_out[lane] = w;
+    idx_out[lane] = si;
   }
 }
 
@@ -590,12 +624,15 @@ __device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red
 // Debug builds (-DZMOE_LD_TIMING) record CTA 0's cycle counter at the phase boundaries in the workspace
 // header (8-byte slots from byte 64).
 #ifdef ZMOE_LD_TIMING
+#define LD_DBG_PTR \
+  ((blockIdx.x == 0 && wid == 0) ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.sync) + 64) : nullptr)
 #define LD_STAMP(i)                                                                     \
   do {                                                                                  \
     if (blockIdx.x == 0 && threadIdx.x == 0)                                            \
       reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.sync) + 64)[i] = clock64(); \
   } while (0)
 #else
+#define LD_DBG_PTR nullptr
 #define LD_STAMP(i) \
   do {              \
   } while (0)
@@ -605,7 +642,7 @@ __device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red
 template <int TT>
 __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ int barrier_ok;
+  __shared__ int wait_failed;  // a bounded wait on another CTA's words ran out somewhere in this CTA
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int wid = tid >> 5;
@@ -623,19 +660,23 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   float* xsum = reinterpret_cast<float*>(smem + lay.xsum);
   float* red = reinterpret_cast<float*>(smem + lay.red);
   float* ybuf = reinterpret_cast<float*>(smem + lay.ybuf);
-  __nv_bfloat16* s_logits = reinterpret_cast<__nv_bfloat16*>(smem + lay.route);
-  float* vals = reinterpret_cast<float*>(smem + lay.route + ld_align16(T * E * 2));
-  float* gsc = vals + T * E;
-  float* sel_val = gsc + T * 64;
-  int* sel_idx = reinterpret_cast<int*>(sel_val + T * kLdMaxK);
+  uint2* keys = reinterpret_cast<uint2*>(smem + lay.route);  // 8-byte aligned: the region starts 16-byte aligned
+  float* vals = reinterpret_cast<float*>(keys + T * E);
+  float* lgs = vals + T * E;
+  float* gsc = lgs + T * E;
+  int* sel_idx = reinterpret_cast<int*>(gsc + T * 64);
   LdMeta* meta = reinterpret_cast<LdMeta*>(smem + lay.meta);
   const int zpage = lay.zero;
   const int nblocks = gridDim.x;
   bool alive = true;
+  // launch count: stable while this launch runs (the last CTA to leave bumps it); tag of this launch's words
+  const int epoch = __ldcg(p.sync + 4);
+  const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
+  if (tid == 0) wait_failed = 0;
 
   LD_STAMP(0);
   // ---- phase 0: token rows -> shared memory (permuted, with group sums)
-  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, p.x, p.ldx, T, d >> 3);
+  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, p.x, p.ldx, T, d >> 3, 0u);
   if (tid < 8) reinterpret_cast<uint32_t*>(smem + zpage)[tid] = 0u;
   for (int i = tid; i < kLdMaxTasks; i += kLdThreads) meta->task_cnt[i] = 0;
 
@@ -672,30 +713,44 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
           }
         }
         const float sres = warp_sum(acc);
-        if (lane == 0) p.logits[(size_t)t * E + e] = __float2bfloat16_rn(sres);
+        // eight copies = one full 32-byte sector: L2 holds it whole and never has to merge it with a stale
+        // copy from HBM when the other CTAs read it
+        if (lane < 8) st_relaxed_u32(p.logits + ((size_t)t * E + e) * 8 + lane, tag | float_to_bf16_bits(sres));
       }
     }
   }
   LD_STAMP(2);
-  alive = ld_grid_barrier(p.sync + 0, p.sync + 3, nblocks, &barrier_ok);
-  LD_STAMP(3);
+  __syncthreads();  // wait_failed, the zero page and the cleared task counts are in place
 
-  if (alive) {
-    // ---- phase 2a: top-k of every row, repeated by every CTA
-    if (wid < T)
-      ld_scores_row(p.logits, s_logits, wid, E, p.family, p.rbias, p.n_group, p.topk_group, vals + wid * E,
-                    gsc + wid * 64, lane);
+  {
+    // ---- phase 2a: routing of every row, repeated by every CTA (one warp per row); the logits arrive as
+    // hand-over words, so this is also where the CTA waits for the router warps of the other CTAs
+    if (wid < T) {
+      bool ok;
+      if (E <= 128)
+        ok = ld_route_scores<4>(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
+                                vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane, LD_DBG_PTR);
+      else
+        ok = ld_route_scores<8>(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
+                                vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane);
+      if (!ok && lane == 0) {
+        wait_failed = 1;
+        atomicExch(p.sync + 3, 1);
+      }
+    }
     __syncthreads();
     LD_STAMP(20);
-    ld_rank_select(vals, T, E, K, sel_val, sel_idx);
+    if (wait_failed == 0) ld_rank_select(keys, T, E, K, sel_idx);
     __syncthreads();
     LD_STAMP(21);
-    if (wid < T)
-      ld_finish_row(s_logits, wid, E, K, p.family, p.renorm, p.scale, sel_val, sel_idx, meta->w, meta->idx, lane);
+    if (wid < T && wait_failed == 0)
+      ld_finish_row(vals + wid * E, lgs + wid * E, K, p.family, p.renorm, p.scale, sel_idx + wid * K,
+                    meta->w + wid * K, meta->idx + wid * K, lane);
+    LD_STAMP(3);
     if (T == 1) {
       // one token: its K experts are distinct, so slot a is task a
-      if (tid < K) {
-        meta->task_expert[tid] = sel_idx[tid];
+      if (tid < K) {  // lanes of warp 0, which has just written meta->idx
+        meta->task_expert[tid] = meta->idx[tid];
         meta->task_cnt[tid] = 1;
         meta->task_rows[tid][0] = (unsigned char)tid;
       }
@@ -711,6 +766,9 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
     __syncthreads();
     LD_STAMP(4);
+    alive = (wait_failed == 0);
+  }
+  if (alive) {
     if (blockIdx.x == 0 && tid < R) {
       if (p.weights) p.weights[tid] = meta->w[tid];
       if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
@@ -811,7 +869,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
             if (writer && col < cnt) {
               const float v = (epi == 2) ? swiglu_per_op(acc[0][j], acc[1][j]) : swiglu_cpu_contract(acc[0][j], acc[1][j]);
               const int dst = meta->task_rows[a][col];
-              p.h[(size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0)] = __float2bfloat16_rn(v);
+              st_relaxed_u32(p.h + (size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
             }
           }
         }
@@ -844,7 +902,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
 
     uint2 wbuf[kLdDownPD][4][1][2];
     const uint32_t* wp[1][2];
-    // the first item's packed weights and scales depend on the routing only: stream them before the barrier
+    // the first item's packed weights and scales depend on the routing only: stream them before waiting for h
     const bool pre = (int)blockIdx.x < ntiles_d && gid < n_tasks;
     if (pre)
       ld_issue_w<1, kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, f >> 3,
@@ -854,14 +912,21 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       ld_issue_sc<1>(ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, ngf, blockIdx.x << 4, sraw,
                      sc_stride, gtid, wkc * 32);
     LD_STAMP(7);
-    alive = ld_grid_barrier(p.sync + 1, p.sync + 3, nblocks, &barrier_ok);
-    LD_STAMP(8);
-    if (alive) {
-      // ---- phase 3: stage every h row, then 16 output columns at a time: all tasks, then the combine
+    {
+      // ---- phase 3: stage every h row (hand-over words: this is where the CTA waits for the gate/up tiles of
+      // the other CTAs), then 16 output columns at a time: all tasks, then the combine
       const int xs_stride = qmm_xs_stride(f);
-      ld_stage_rows<true>(xs, xs_stride, xsum, rtot, p.h, f, rtot, f >> 3);
+      const bool good = ld_stage_rows<true>(xs, xs_stride, xsum, rtot, p.h, f, rtot, f >> 3, tag);
+      if (!good) {
+        wait_failed = 1;
+        atomicExch(p.sync + 3, 1);
+      }
       __syncthreads();
       LD_STAMP(9);
+      alive = (wait_failed == 0);
+    }
+    if (alive) {
+      const int xs_stride = qmm_xs_stride(f);
       for (int tile = blockIdx.x; tile < ntiles_d; tile += nblocks) {
         const int n0 = tile << 4;
         for (int a = gid; a < n_tasks; a += ngrp) {
@@ -938,14 +1003,13 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
 
-  // ---- exit: the last CTA to leave puts the barrier counters back to zero for the next launch
+  // ---- exit: the last CTA to leave bumps the launch count (a new tag for the next launch)
   __syncthreads();
   LD_STAMP(10);
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(p.sync + 2, 1) == nblocks - 1) {
-      p.sync[0] = 0;
-      p.sync[1] = 0;
+      p.sync[4] = epoch + 1;
       __threadfence();
       p.sync[2] = 0;
     }
@@ -990,7 +1054,7 @@ static const char* ld_unsupported(const zmoe_layer_desc* L, int T) {
 
 static size_t ld_ws_logits_off() { return 256; }
 static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
-  return (ld_ws_logits_off() + (size_t)T * L->E * 2 + 255) & ~(size_t)255;
+  return (ld_ws_logits_off() + (size_t)T * L->E * 32 + 255) & ~(size_t)255;
 }
 
 template <int TT>
@@ -1024,7 +1088,7 @@ extern "C" {
 size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T) {
   if (!L || ld_unsupported(L, T)) return 0;
   const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
-  return ld_ws_h_off(L, T) + rows * L->d_ff * 2;
+  return ld_ws_h_off(L, T) + rows * L->d_ff * 4;
 }
 
 int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
@@ -1114,8 +1178,8 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.out_flags = L->out_flags;
   unsigned char* ws = (unsigned char*)workspace;
   p.sync = (int*)ws;
-  p.logits = (__nv_bfloat16*)(ws + ld_ws_logits_off());
-  p.h = (__nv_bfloat16*)(ws + ld_ws_h_off(L, T));
+  p.logits = (uint32_t*)(ws + ld_ws_logits_off());
+  p.h = (uint32_t*)(ws + ld_ws_h_off(L, T));
   p.weights = weights;
   p.indices = indices;
   p.out = out;

@@ -98,7 +98,9 @@ class MoELayer:
         if ws is None:
             return self.logits[:T]
         E = self.cfg.n_experts
-        return ws[256:256 + T * E * 2].view(torch.bfloat16).view(T, E)
+        # the kernel keeps each logit in the low half of a 32-bit hand-over word
+        words = ws[256:256 + T * E * 32].view(torch.int32)[::8]  # one 32-byte sector per logit
+        return (words & 0xFFFF).to(torch.int16).view(torch.bfloat16).view(T, E)
 
     def fused_status(self, T: int) -> int:
         """The status word of the T-token workspace: non-zero after a bounded grid-barrier wait ran out."""
