@@ -76,7 +76,7 @@ def _oracle_layer(cfg, params, x, logits, idx_gpu):
 
 # fused: the one-launch path (zmoe_layer_decode) takes the block; otherwise the separate kernels do
 @pytest.mark.parametrize("name,T,fused", [("c1", 1, False), ("c1", 5, False), ("c2", 1, False), ("c2", 4, False),
-                                          ("c2", 16, False), ("c2", 64, False), ("c3", 1, False), ("c3", 3, False),
+                                          ("c2", 16, False), ("c2", 64, False), ("c2", 200, False), ("c3", 1, False), ("c3", 3, False),
                                           ("c3", 16, False), ("c5", 1, False), ("c5", 9, False),
                                           ("c1", 1, True), ("c1", 2, True), ("c1", 5, True), ("c1", 8, True),
                                           ("c2", 1, True), ("c2", 2, True), ("c2", 3, True), ("c2", 4, True),

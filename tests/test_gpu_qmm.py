@@ -191,3 +191,27 @@ def test_mxfp4_swiglu_and_down(T, K_, d, f):
     ref = S.gather_qmm_combine_quantized(t2n(h).reshape(T, K_, f), t2n(dw), t2n(ds), None, t2n(gate), t2n(idx),
                                          mode="mxfp4", combine="fp32_no_fma")
     assert_close_rel(t2n(out), ref, REL, "mxfp4 down + combine")
+
+
+@pytest.mark.parametrize("E,P", [(128, 1024), (300, 4096), (1024, 8192), (256, 300)])
+def test_plan_with_every_expert_active(E, P):
+    """The task list, offsets and row maps stay right when 128 or more experts own rows (the counts of both scans
+    of the plan builder pass 127 and 255)."""
+    g = torch.Generator().manual_seed(E + P)
+    idx = torch.cat([torch.arange(E), torch.randint(0, E, (P - E,), generator=g)])[torch.randperm(P, generator=g)]
+    plan = ops.build_plan(idx.to(DEV), E).cpu().numpy()
+    counts = np.bincount(idx.numpy(), minlength=E)
+    assert plan[0] == int((counts > 0).sum()) and plan[1] == P and plan[2] == 0 and plan[3] == E
+    tasks = plan[4:4 + 4 * E].reshape(E, 4)
+    n_active = plan[0]
+    assert np.array_equal(tasks[:n_active, 0], np.flatnonzero(counts > 0))
+    assert np.array_equal(tasks[:n_active, 2], counts[counts > 0])
+    offset = plan[4 + 4 * E:4 + 4 * E + E + 1]
+    assert np.array_equal(offset, np.concatenate([[0], np.cumsum(counts)]))
+    assert np.array_equal(tasks[:n_active, 1], offset[:-1][counts > 0])
+    row_src = plan[4 + 4 * E + (E + 1) + E:][:P]
+    row_dst = plan[4 + 4 * E + (E + 1) + E + P:][:P]
+    assert np.array_equal(np.sort(row_dst), np.arange(P)) and np.array_equal(row_src, row_dst)
+    for e in (0, E // 2, E - 1):
+        seg = row_dst[offset[e]:offset[e + 1]]
+        assert np.array_equal(np.sort(seg), np.flatnonzero(idx.numpy() == e))

@@ -64,7 +64,7 @@ int zmoe_build_plan(const int32_t* lhs, int lhs_div, const int32_t* rhs, int P, 
   ZMOE_REQUIRE((long long)P * M < (1ll << 24), ZMOE_ERR_SHAPE, "zmoe_build_plan: too many rows (limit 2^24)");
   ZMOE_REQUIRE(plan_bytes >= zmoe_plan_bytes(P * M, E), ZMOE_ERR_WORKSPACE,
                "zmoe_build_plan: plan buffer of %zu bytes, need %zu", plan_bytes, zmoe_plan_bytes(P * M, E));
-  size_t smem = (size_t)(2 * E + kPlanThreads) * sizeof(int);
+  size_t smem = (size_t)(2 * E + 2 * kPlanThreads + 2) * sizeof(int);
   launch_pdl(build_plan_kernel, dim3(1), dim3(kPlanThreads), smem, (cudaStream_t)stream, lhs, lhs_div, rhs, P, M, E,
              (int*)plan);
   return check_launch("zmoe_build_plan");

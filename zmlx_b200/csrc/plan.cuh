@@ -7,7 +7,7 @@
 namespace zmoe {
 
 // One CTA of NTHREADS threads groups `rows` (pair, m) rows by expert: histogram, exclusive
-// scan, scatter.  `sm` needs 2 * E + NTHREADS ints.  The order of rows inside an expert's
+// scan, scatter.  `sm` needs 2 * E + 2 * NTHREADS + 2 ints (8-byte aligned).  The order of rows inside an expert's
 // segment is arbitrary; every output row is computed from its own input row only, so
 // results do not depend on it.  All threads of the CTA must call this.
 template <int NTHREADS>
@@ -15,7 +15,8 @@ __device__ __forceinline__ void build_plan_block(const int* lhs, int lhs_div, co
                                                  int* plan_base, int* sm) {
   int* count = sm;               // E
   int* cursor = sm + E;          // E
-  int* scan_tmp = sm + 2 * E;    // NTHREADS
+  // NTHREADS 64-bit cells: rows in the low half, number of experts that own rows in the high half
+  unsigned long long* scan_tmp = reinterpret_cast<unsigned long long*>(sm + 2 * E + (((size_t)sm >> 2) & 1));
   const int rows = P * M;
   PlanView pv = plan_view(plan_base, rows, E);
   const int tid = threadIdx.x;
@@ -37,18 +38,18 @@ __device__ __forceinline__ void build_plan_block(const int* lhs, int lhs_div, co
     int e = e0 + tid;
     int c = (e < E) ? count[e] : 0;
     int flag = c > 0;
-    scan_tmp[tid] = c | (flag << 24);  // rows < 2^24 per chunk: both scans in one pass
+    scan_tmp[tid] = (unsigned long long)(unsigned)c | ((unsigned long long)flag << 32);  // both scans in one pass
     __syncthreads();
     for (int o = 1; o < NTHREADS; o <<= 1) {
-      int v = (tid >= o) ? scan_tmp[tid - o] : 0;
+      unsigned long long v = (tid >= o) ? scan_tmp[tid - o] : 0ull;
       __syncthreads();
       scan_tmp[tid] += v;
       __syncthreads();
     }
-    const int packed = scan_tmp[tid];
-    const int ptotal = scan_tmp[NTHREADS - 1];
+    const unsigned long long packed = scan_tmp[tid];
+    const unsigned long long ptotal = scan_tmp[NTHREADS - 1];
     __syncthreads();
-    const int incl = packed & 0xFFFFFF, aincl = packed >> 24;
+    const int incl = (int)(packed & 0xFFFFFFFFull), aincl = (int)(packed >> 32);
     if (e < E) {
       int off = base + incl - c;
       pv.offset[e] = off;
@@ -59,8 +60,8 @@ __device__ __forceinline__ void build_plan_block(const int* lhs, int lhs_div, co
         reinterpret_cast<int4*>(pv.tasks)[a] = make_int4(e, off, c, 0);
       }
     }
-    base += ptotal & 0xFFFFFF;
-    abase += ptotal >> 24;
+    base += (int)(ptotal & 0xFFFFFFFFull);
+    abase += (int)(ptotal >> 32);
   }
   for (int a = abase + tid; a < E; a += NTHREADS) reinterpret_cast<int4*>(pv.tasks)[a] = make_int4(0, 0, 0, 0);
   if (tid == 0) {

@@ -306,7 +306,7 @@ int zmoe_route(const void* x, const void* wr, int T, int E, int d, int K, int fa
   p.indices = indices;
   p.plan = (int*)plan;
   p.counter = counter;
-  size_t smem_plan = (size_t)(2 * E + 128) * sizeof(int);
+  size_t smem_plan = (size_t)(2 * E + 2 * 128 + 2) * sizeof(int);
   size_t smem_sig = 4 * (size_t)(2 * E + 64 + 2 * kMaxK) * sizeof(float);
   size_t smem = smem_plan > smem_sig ? smem_plan : smem_sig;
   dim3 grid((E + 3) / 4), block(128);
