@@ -26,6 +26,7 @@
 // bias and the 128 offset are applied per group in fp32; spare mma columns carry other
 // groups (column multiplexing).  Every wait on another CTA is bounded: when the limit
 // is hit the CTA records it in the status word and leaves.
+#include <cstdlib>
 #include <mutex>
 
 #include "qmm_common.cuh"
@@ -61,6 +62,7 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
+  int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
   int* sync;         // {-, -, exit count, status, launch count}
   uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
   uint32_t* h;       // (rows, f) hand-over words
@@ -221,12 +223,12 @@ __device__ __forceinline__ bool ld_stage_rows(unsigned char* xs, int xs_stride, 
 // Step 1, one warp per row: wait for the row's logits (hand-over words written by the router warps of all
 // CTAs), compute the selection scores and leave, per expert, the score, the logit and a 64-bit sort key
 // {order-preserving score : 32 | ~expert id : 32} in shared memory.  Returns false when the wait ran out.
-template <int NJ>
 __device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32_t tag, int E, int family,
                                                 const float* bias, int n_group, int topk_group, float* vals,
                                                 float* lgs, uint2* keys, float* gsc /* 64 floats */, int lane,
                                                 long long* dbg = nullptr) {
-  float lg[NJ], v[NJ];
+  constexpr int NJ = 8;  // values per lane: E <= 256
+  const int nj = (E + 31) >> 5;
   {
     uint32_t raw[NJ];
     int spins = 0;
@@ -243,43 +245,53 @@ __device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32
     } while (!ok && ++spins < kLdSpinLimit);
     if (!ok) return false;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) lg[j] = bf16_bits_to_float(raw[j] & 0xffffu);
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < E) lgs[lane + 32 * j] = bf16_bits_to_float(raw[j] & 0xffffu);
     if (dbg && lane == 0) {
       dbg[22] = clock64();
       dbg[23] = spins;
     }
   }
+  // From here on the loops over a lane's values stay rolled (they run once per launch: code size matters more
+  // than overlap); every lane touches only its own entries lane, lane + 32, ... of the shared arrays.
   if (family == 0) {
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) v[j] = lg[j];
+#pragma unroll 1
+    for (int j = 0; j < nj; ++j) {
+      const int idx = lane + 32 * j;
+      if (idx < E) vals[idx] = lgs[idx];
+    }
   } else if (family == 1) {
     float mx = -CUDART_INF_F;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < E) mx = fmaxf(mx, lg[j]);
+#pragma unroll 1
+    for (int j = 0; j < nj; ++j) {
+      const int idx = lane + 32 * j;
+      if (idx < E) mx = fmaxf(mx, lgs[idx]);
+    }
     mx = warp_max(mx);
     float sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      v[j] = (lane + 32 * j < E) ? expf(lg[j] - mx) : 0.0f;
-      sum += v[j];
+#pragma unroll 1
+    for (int j = 0; j < nj; ++j) {
+      const int idx = lane + 32 * j;
+      const float e = (idx < E) ? expf(lgs[idx] - mx) : 0.0f;
+      if (idx < E) vals[idx] = e;
+      sum += e;
     }
     sum = warp_sum(sum);
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      v[j] = v[j] / sum;
-      if (bias && lane + 32 * j < E) v[j] += bias[lane + 32 * j];
+#pragma unroll 1
+    for (int j = 0; j < nj; ++j) {
+      const int idx = lane + 32 * j;
+      if (idx < E) {
+        float q = vals[idx] / sum;
+        if (bias) q += bias[idx];
+        vals[idx] = q;
+      }
     }
   } else {
     // sigmoid + selection bias, optional group-limited selection
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+#pragma unroll 1
+    for (int j = 0; j < nj; ++j) {
       const int idx = lane + 32 * j;
-      v[j] = 0.0f;
-      if (idx < E) {
-        v[j] = sigmoid_stable(lg[j]) + bias[idx];
-        vals[idx] = v[j];
-      }
+      if (idx < E) vals[idx] = sigmoid_stable(lgs[idx]) + bias[idx];
     }
     if (n_group > 1) {
       float* gkeep = gsc + 32;
@@ -310,21 +322,17 @@ __device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32
         gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
       }
       __syncwarp();
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
+#pragma unroll 1
+      for (int j = 0; j < nj; ++j) {
         const int idx = lane + 32 * j;
-        if (idx < E && gkeep[idx / per] == 0.0f) v[j] = 0.0f;
+        if (idx < E && gkeep[idx / per] == 0.0f) vals[idx] = 0.0f;
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < NJ; ++j) {
+#pragma unroll 1
+  for (int j = 0; j < nj; ++j) {
     const int idx = lane + 32 * j;
-    if (idx < E) {
-      vals[idx] = v[j];
-      lgs[idx] = lg[j];
-      keys[idx] = make_uint2(~(uint32_t)idx, ld_order_key(v[j] + 0.0f));  // .y is the high half
-    }
+    if (idx < E) keys[idx] = make_uint2(~(uint32_t)idx, ld_order_key(vals[idx] + 0.0f));  // .y is the high half
   }
   return true;
 }
@@ -591,6 +599,7 @@ __device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red
     }
     ld_group_sync(gid, wk_count);
     if (wk == 0) {
+#pragma unroll 1
       for (int o = 1; o < wk_count; ++o) {
         const float* other = red + ((wid + o) * 32 + lane) * 8;
 #pragma unroll
@@ -621,6 +630,110 @@ __device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red
   }
 }
 
+// ------------------------------------------------------------------ bulk-copy variant (one token)
+// With BULK the packed weights do not go to registers: every row of an item is one cp.async.bulk copy into a
+// padded shared-memory row (stride = row bytes + 32 == 32 mod 128: the 8-byte fragment reads of a warp hit 32
+// different banks), completion is counted on an mbarrier, and the matmul is a compact loop over shared
+// memory.  Issuing a copy never blocks the warp, so the copies of all of a CTA's items are in flight while
+// the first ones are already being consumed, and the loop body is fetched once instead of a long unrolled
+// register pipeline.  Needs 16-byte aligned tensors and rows that fit (d_model, d_ff <= 2048 or so).
+__device__ __forceinline__ uint32_t ld_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ld_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void ld_mbar_expect_tx(uint32_t bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ld_mbar_try(uint32_t bar, int parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+// Bounded wait for a phase of an mbarrier; false when it ran out.
+__device__ __forceinline__ bool ld_mbar_wait(uint32_t bar, int parity) {
+  for (int i = 0; i < kLdSpinLimit; ++i)
+    if (ld_mbar_try(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void ld_bulk_g2s(uint32_t dst, const void* src, int bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// One token (TT = 1: eight groups share an accumulator), weights of the item in shared memory: rows m*16 + r at
+// `wslot + row * row_stride`.  The warp walks the quads wk, wk + wk_count, ...; the loop is kept rolled.
+template <int NMAT, int NACC>
+__device__ __forceinline__ void ld_smem_mainloop(float (&acc)[NMAT][4], const unsigned char* wslot, int row_stride,
+                                                 const unsigned char* smem, int xoff, int zpage, const float* xsum,
+                                                 int xsum_stride, const int (&srow_c)[2], const unsigned char* sraw,
+                                                 int sc_stride, int wk, int wk_count, int nq, int g, int tig) {
+  float dg[NMAT][NACC][4];
+  float dsum[NMAT][4];
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
+#pragma unroll
+    for (int n = 0; n < NACC; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dg[m][n][j] = 0.0f;
+  }
+  auto fold = [&]() {
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (NACC == 1) dsum[m][j] = dg[m][0][j];
+        if (NACC == 2) dsum[m][j] = dg[m][0][j] + dg[m][NACC - 1][j];
+        if (NACC == 4) dsum[m][j] = (dg[m][0][j] + dg[m][1 % NACC][j]) + (dg[m][2 % NACC][j] + dg[m][3 % NACC][j]);
+      }
+  };
+  const int nq_w = (nq > wk) ? (nq - wk + wk_count - 1) / wk_count : 0;
+  const unsigned char* wlane = wslot + g * row_stride + tig * 8;
+  // blocks of eight groups (two of the warp's quads) share the accumulators; one fix-up per block
+#pragma unroll 1
+  for (int qb = 0; qb < nq_w; qb += 2) {
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+      for (int n = 0; n < NACC; ++n)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) dg[m][n][jj] = 0.0f;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      if (qb + half >= nq_w) break;
+      const int quad = wk + (qb + half) * wk_count;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool mine = (g == half * 4 + j);
+        const int xo = mine ? (xoff + quad * 512 + j * 128) : zpage;
+        const uint4 xb0 = *reinterpret_cast<const uint4*>(smem + xo);
+        const uint4 xb1 = *reinterpret_cast<const uint4*>(smem + xo + 16);
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+          const unsigned char* wr = wlane + m * 16 * row_stride + quad * 128 + j * 32;
+          const uint2 wa = *reinterpret_cast<const uint2*>(wr);
+          const uint2 wb = *reinterpret_cast<const uint2*>(wr + 8 * row_stride);
+          mma_bf16_m16n8k16(dg[m][0], deq_imm<0>(wa.x), deq_imm<0>(wb.x), deq_imm<4>(wa.x), deq_imm<4>(wb.x), xb0.x,
+                            xb0.y);
+          mma_bf16_m16n8k16(dg[m][1 % NACC], deq_imm<8>(wa.x), deq_imm<8>(wb.x), deq_imm<12>(wa.x), deq_imm<12>(wb.x),
+                            xb0.z, xb0.w);
+          mma_bf16_m16n8k16(dg[m][2 % NACC], deq_imm<0>(wa.y), deq_imm<0>(wb.y), deq_imm<4>(wa.y), deq_imm<4>(wb.y),
+                            xb1.x, xb1.y);
+          mma_bf16_m16n8k16(dg[m][3 % NACC], deq_imm<8>(wa.y), deq_imm<8>(wb.y), deq_imm<12>(wa.y), deq_imm<12>(wb.y),
+                            xb1.z, xb1.w);
+        }
+      }
+    }
+    fold();
+    ld_fixup<NMAT, 1>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig, qb * 4, nq_w);
+  }
+}
+
 // Debug builds (-DZMOE_LD_TIMING) record CTA 0's cycle counter at the phase boundaries in the workspace
 // header (8-byte slots from byte 64).
 #ifdef ZMOE_LD_TIMING
@@ -639,8 +752,9 @@ __device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red
 #endif
 
 // ------------------------------------------------------------------ the kernel
-template <int TT>
+template <int TT, bool BULK>
 __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
+  static_assert(!BULK || TT == 1, "the bulk-copy variant is the one-token kernel");
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int wait_failed;  // a bounded wait on another CTA's words ran out somewhere in this CTA
   const int tid = threadIdx.x;
@@ -673,6 +787,17 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const int epoch = __ldcg(p.sync + 4);
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
   if (tid == 0) wait_failed = 0;
+  // bulk-copy variant: 16 mbarriers {gate/up slot 0..3, down task 0..}, then the gate/up slots, then the down slots
+  const int rs_g = (d >> 1) + 32, rs_d = (f >> 1) + 32;  // padded row strides of the two kinds of slots
+  unsigned char* bulk = smem + p.bulk_off;
+  const uint32_t bars = ld_smem_u32(bulk);
+  unsigned char* gslots = bulk + 128;
+  unsigned char* dslots = gslots + p.g_slots * 32 * rs_g;
+  if (BULK && tid == 0) {
+    for (int i = 0; i < 4; ++i) ld_mbar_init(bars + i * 8, 32);
+    for (int i = 4; i < 16; ++i) ld_mbar_init(bars + i * 8, 16);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
 
   LD_STAMP(0);
   // ---- phase 0: token rows -> shared memory (permuted, with group sums)
@@ -727,12 +852,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     // hand-over words, so this is also where the CTA waits for the router warps of the other CTAs
     if (wid < T) {
       bool ok;
-      if (E <= 128)
-        ok = ld_route_scores<4>(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
-                                vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane, LD_DBG_PTR);
-      else
-        ok = ld_route_scores<8>(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
-                                vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane);
+      ok = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
+                           vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane, LD_DBG_PTR);
       if (!ok && lane == 0) {
         wait_failed = 1;
         atomicExch(p.sync + 3, 1);
@@ -773,7 +894,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       if (p.weights) p.weights[tid] = meta->w[tid];
       if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
     }
-    if (T > 1) {
+    if (TT > 1 && T > 1) {
       // ---- phase 2b: tasks = distinct experts in order of first use; a task's rows in row order
       if (tid < R) {
         const int e = meta->idx[tid];
@@ -821,6 +942,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       const int sc_stride = qmm_sc_stride(ngd);
       unsigned char* sraw = smem + lay.sc + gid * (4 * 16 * sc_stride);
       const int xs_stride = qmm_xs_stride(d);
+      int gu_uses = 0;  // how often this team's slot has been filled (parity of its barrier)
       for (int it = gid * nblocks + blockIdx.x; it < nitems; it += nblocks * 4) {
         const int a = it / ntiles;
         const int n0 = (it - a * ntiles) << 4;
@@ -828,10 +950,20 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         const LdBank bank = ld_pick(p.gu, p.sgu, is_sh);
         const int e = meta->task_expert[a];
         const int cnt = meta->task_cnt[a];
-        uint2 wbuf[2][4][2][2];
+        uint2 wbuf[BULK ? 1 : 2][4][2][2];
         const uint32_t* wp[2][2];
-        ld_issue_w<2, 2>(wbuf, wp, bank, e, f, d >> 3, n0, g, tig, wk, WK, nq_w);
-        ld_group_sync(gid, WK);  // the previous item is done with the group's scale area
+        if (!BULK) ld_issue_w<2, BULK ? 1 : 2>(wbuf, wp, bank, e, f, d >> 3, n0, g, tig, wk, WK, nq_w);
+        ld_group_sync(gid, WK);  // the previous item is done with the group's scale area (and weight slot)
+        if (BULK) {
+          // rows 0..15 gate, 16..31 up: eight lanes of each of the team's warps copy one row each
+          if (gu_uses > 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (lane < 8) {
+            const int r = wk * 8 + lane;
+            const uint32_t* src = bank.w[r >> 4] + ((size_t)e * f + n0 + (r & 15)) * (d >> 3);
+            ld_mbar_expect_tx(bars + gid * 8, d >> 1);
+            ld_bulk_g2s(ld_smem_u32(gslots + (gid * 32 + r) * rs_g), src, d >> 1, bars + gid * 8);
+          }
+        }
         ld_issue_sc<2>(bank, e, f, ngd, n0, sraw, sc_stride, tid & 127, 128);
         // token of a task row: routed row r belongs to token r / K, shared row R + t to token t
         const bool tok_ok = tok_g < cnt;
@@ -852,11 +984,20 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         }
         LD_STAMP(11);
         cp_async_wait_all();
+        if (BULK && !ld_mbar_wait(bars + gid * 8, gu_uses & 1)) {
+          wait_failed = 1;
+          atomicExch(p.sync + 3, 1);
+        }
+        ++gu_uses;
         ld_group_sync(gid, WK);
         LD_STAMP(12);
         float acc[2][4];
-        ld_mainloop<2, 2, TT, 2>(acc, wbuf, wp, smem, lay.xs + trow * xs_stride + tig * 32, tok_ok, zpage, slot_g, xsum,
-                              T, srow_c, sraw, sc_stride, wk, WK, nq_w, g, tig);
+        if (BULK)
+          ld_smem_mainloop<2, 2>(acc, gslots + gid * 32 * rs_g, rs_g, smem, lay.xs + trow * xs_stride + tig * 32,
+                                 zpage, xsum, T, srow_c, sraw, sc_stride, wk, WK, nq, g, tig);
+        else
+          ld_mainloop<2, BULK ? 1 : 2, TT, 2>(acc, wbuf, wp, smem, lay.xs + trow * xs_stride + tig * 32, tok_ok, zpage,
+                                              slot_g, xsum, T, srow_c, sraw, sc_stride, wk, WK, nq_w, g, tig);
         LD_STAMP(13);
         ld_reduce_fold<2, TT>(acc, red, gid, wk, WK, lane);
         LD_STAMP(14);
@@ -900,13 +1041,22 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     const int ntiles_d = d >> 4;
     const int gtid = tid - gid * wkc * 32;
 
-    uint2 wbuf[kLdDownPD][4][1][2];
+    uint2 wbuf[BULK ? 1 : kLdDownPD][4][1][2];
     const uint32_t* wp[1][2];
     // the first item's packed weights and scales depend on the routing only: stream them before waiting for h
     const bool pre = (int)blockIdx.x < ntiles_d && gid < n_tasks;
-    if (pre)
-      ld_issue_w<1, kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, f >> 3,
-                       blockIdx.x << 4, g, tig, wk, wkc, nq_w);
+    if (BULK) {
+      // all tasks of the CTA's first tile: warp a copies the 16 rows of task a into down slot a
+      if ((int)blockIdx.x < ntiles_d && wid < n_tasks && lane < 16) {
+        const LdBank bank = ld_pick(p.dn, p.sdn, wid >= n_routed);
+        const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + (blockIdx.x << 4) + lane) * (f >> 3);
+        ld_mbar_expect_tx(bars + (4 + wid) * 8, f >> 1);
+        ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
+      }
+    } else if (pre) {
+      ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d,
+                                          f >> 3, blockIdx.x << 4, g, tig, wk, wkc, nq_w);
+    }
     __syncthreads();  // every group of this CTA is done with the gate/up scale areas, which the next copies reuse
     if (pre)
       ld_issue_sc<1>(ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, ngf, blockIdx.x << 4, sraw,
@@ -927,14 +1077,27 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
     if (alive) {
       const int xs_stride = qmm_xs_stride(f);
-      for (int tile = blockIdx.x; tile < ntiles_d; tile += nblocks) {
+      int d_uses = 0;  // how often the down slots have been filled (parity of their barriers)
+      for (int tile = blockIdx.x; tile < ntiles_d; tile += nblocks, ++d_uses) {
         const int n0 = tile << 4;
+        if (BULK && d_uses > 0) {
+          // the previous tile ended with a CTA-wide barrier: every slot is free again
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (wid < n_tasks && lane < 16) {
+            const LdBank bank = ld_pick(p.dn, p.sdn, wid >= n_routed);
+            const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + n0 + lane) * (f >> 3);
+            ld_mbar_expect_tx(bars + (4 + wid) * 8, f >> 1);
+            ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
+          }
+        }
         for (int a = gid; a < n_tasks; a += ngrp) {
           const bool is_sh = a >= n_routed;
           const int cnt = meta->task_cnt[a];
           if (!(pre && tile == (int)blockIdx.x && a == gid)) {
             const LdBank bank = ld_pick(p.dn, p.sdn, is_sh);
-            ld_issue_w<1, kLdDownPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc, nq_w);
+            if (!BULK)
+              ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc,
+                                                  nq_w);
             ld_group_sync(gid, wkc);  // the previous item is done with the group's scale area
             ld_issue_sc<1>(bank, meta->task_expert[a], d, ngf, n0, sraw, sc_stride, gtid, wkc * 32);
           }
@@ -948,11 +1111,20 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
           }
           LD_STAMP(15);
           cp_async_wait_all();
+          if (BULK && !ld_mbar_wait(bars + (4 + a) * 8, d_uses & 1)) {
+            wait_failed = 1;  // the results of this launch are void; the status word says so
+            atomicExch(p.sync + 3, 1);
+          }
           ld_group_sync(gid, wkc);
           LD_STAMP(16);
           float acc[1][4];
-          ld_mainloop<1, kLdDownPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok, zpage, slot_g, xsum,
-                                rtot, srow_c, sraw, sc_stride, wk, wkc, nq_w, g, tig);
+          if (BULK)
+            ld_smem_mainloop<1, 4>(acc, dslots + a * 16 * rs_d, rs_d, smem, lay.xs + srow * xs_stride + tig * 32, zpage,
+                                   xsum, rtot, srow_c, sraw, sc_stride, wk, wkc, nqf, g, tig);
+          else
+            ld_mainloop<1, BULK ? 1 : kLdDownPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok,
+                                                        zpage, slot_g, xsum, rtot, srow_c, sraw, sc_stride, wk, wkc,
+                                                        nq_w, g, tig);
           LD_STAMP(17);
           ld_reduce_fold<1, TT>(acc, red, gid, wk, wkc, lane);
           LD_STAMP(18);
@@ -973,6 +1145,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
           const int t = tid >> 4, n = tid & 15;
           const int mode = p.combine_mode;
           float a0 = 0.0f;
+#pragma unroll 1
           for (int i = 0; i < K; ++i) {
             float wi = meta->w[t * K + i];
             if (p.out_flags & 2) wi = round_bf16(wi);
@@ -1057,9 +1230,9 @@ static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
   return (ld_ws_logits_off() + (size_t)T * L->E * 32 + 255) & ~(size_t)255;
 }
 
-template <int TT>
+template <int TT, bool BULK>
 static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = layer_decode_kernel<TT>;
+  auto kern = layer_decode_kernel<TT, BULK>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
@@ -1070,7 +1243,7 @@ static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;  // every CTA resident at once: the barriers rely on it
+  attr[0].id = cudaLaunchAttributeCooperative;  // every CTA resident at once: the waits between CTAs rely on it
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -1189,10 +1362,34 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   if (rc != ZMOE_OK) return rc;
   const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared);
   cudaStream_t st = (cudaStream_t)stream;
-  if (T <= 1) return ld_launch<1>(p, sms, lay.total, st);
-  if (T <= 2) return ld_launch<2>(p, sms, lay.total, st);
-  if (T <= 4) return ld_launch<4>(p, sms, lay.total, st);
-  return ld_launch<8>(p, sms, lay.total, st);
+  p.bulk_off = 0;
+  p.g_slots = 0;
+  if (T == 1) {
+    // bulk-copy variant: every tensor 16-byte aligned and its shared-memory slots fit beside the rest
+    static const bool no_bulk = getenv("ZMOE_LD_NO_BULK") != nullptr && atoi(getenv("ZMOE_LD_NO_BULK")) != 0;
+    bool aligned = true;
+    for (int i = 0; i < 2; ++i) {
+      if (!banks[i]) continue;
+      const void* wptr[3] = {banks[i]->gate_w, banks[i]->up_w, banks[i]->down_w};
+      for (int j = 0; j < 3; ++j) aligned = aligned && (((uintptr_t)wptr[j] % 16) == 0);
+    }
+    const int n_tasks = L->top_k + (L->n_shared ? 1 : 0);
+    const int items = n_tasks * (L->d_ff / 16);
+    int g_slots = (items + sms - 1) / sms;
+    if (g_slots > 4) g_slots = 4;
+    const int rs_g = L->d_model / 2 + 32, rs_d = L->d_ff / 2 + 32;
+    const int bulk_off = (lay.total + 127) & ~127;
+    const size_t total = (size_t)bulk_off + 128 + (size_t)g_slots * 32 * rs_g + (size_t)n_tasks * 16 * rs_d;
+    if (!no_bulk && aligned && n_tasks <= 12 && total <= 220 * 1024) {
+      p.bulk_off = bulk_off;
+      p.g_slots = g_slots;
+      return ld_launch<1, true>(p, sms, total, st);
+    }
+    return ld_launch<1, false>(p, sms, lay.total, st);
+  }
+  if (T <= 2) return ld_launch<2, false>(p, sms, lay.total, st);
+  if (T <= 4) return ld_launch<4, false>(p, sms, lay.total, st);
+  return ld_launch<8, false>(p, sms, lay.total, st);
 }
 
 }  // extern "C"
