@@ -1366,7 +1366,7 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.g_slots = 0;
   if (T == 1) {
     // bulk-copy variant: every tensor 16-byte aligned and its shared-memory slots fit beside the rest
-    static const bool no_bulk = getenv("ZMOE_LD_NO_BULK") != nullptr && atoi(getenv("ZMOE_LD_NO_BULK")) != 0;
+    static const bool no_bulk = !(getenv("ZMOE_LD_BULK") != nullptr && atoi(getenv("ZMOE_LD_BULK")) != 0);
     bool aligned = true;
     for (int i = 0; i < 2; ++i) {
       if (!banks[i]) continue;
