@@ -42,6 +42,7 @@ constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;      // (token, slot) rows
 constexpr int kLdMaxRows = kLdMaxRouted + kLdMaxT;   // + one shared-expert row per token
 constexpr int kLdMaxTasks = kLdMaxRouted + 1;
 constexpr int kLdDownPD = 2;  // quads of packed weights a warp keeps in flight in the down projection
+constexpr bool kLdBulkByDefault = false;  // the bulk-copy form of the one-token kernel
 constexpr int kLdSpinLimit = 1 << 21;  // polls of the barrier counter before a CTA gives up (~1 s)
 
 struct LdBank {
@@ -1366,7 +1367,10 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.g_slots = 0;
   if (T == 1) {
     // bulk-copy variant: every tensor 16-byte aligned and its shared-memory slots fit beside the rest
-    static const bool no_bulk = !(getenv("ZMOE_LD_BULK") != nullptr && atoi(getenv("ZMOE_LD_BULK")) != 0);
+    // ZMOE_LD_BULK=1 / ZMOE_LD_NO_BULK=1 force the choice (read once per process)
+    static const bool force_on = getenv("ZMOE_LD_BULK") != nullptr && atoi(getenv("ZMOE_LD_BULK")) != 0;
+    static const bool force_off = getenv("ZMOE_LD_NO_BULK") != nullptr && atoi(getenv("ZMOE_LD_NO_BULK")) != 0;
+    const bool no_bulk = force_off || !(force_on || kLdBulkByDefault);
     bool aligned = true;
     for (int i = 0; i < 2; ++i) {
       if (!banks[i]) continue;
