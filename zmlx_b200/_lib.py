@@ -11,7 +11,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libzmoe.so")
+# ZMOE_LIB selects another build of the same ABI (e.g. one compiled with -DZMOE_LD_TIMING)
+LIB_PATH = os.environ.get("ZMOE_LIB") or os.path.join(_HERE, "libzmoe.so")
 
 OK = 0
 ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = -1, -2, -3, -4, -5, -6, -7

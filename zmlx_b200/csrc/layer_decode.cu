@@ -3,29 +3,31 @@
 //
 // The separate-kernel path pays four dependent launches per block; at one token each of
 // them is a few microseconds of launch and pipeline-fill latency around ~1 us of memory
-// traffic.  Here a persistent grid of one 512-thread CTA per SM walks the three phases
-// and meets at two grid-wide barriers (cooperative launch, so every CTA is resident):
+// traffic.  Here a persistent grid of one 512-thread CTA per SM (cooperative launch, so
+// every CTA is resident) walks three phases.  There is no grid-wide barrier: what one CTA
+// produces for the others travels as tagged 32-bit "hand-over words" that a consumer
+// re-reads until they carry the current launch's tag.
 //
-//   phase 0  every CTA stages the T token rows in shared memory (they feed both the
-//            router and every gate/up tile);
-//   phase 1  router linear, one warp per expert row across the whole grid -> logits in
-//            global scratch;                                              [barrier 1]
-//   phase 2  every CTA repeats the top-k of the T rows (cheap, avoids a third barrier)
-//            and derives the task list (distinct experts and their rows) in shared
-//            memory; gate/up + SwiGLU tiles (task, 16 rows) are dealt to groups of four
-//            warps across the grid; h rows go to global scratch.  Before the second
-//            barrier each warp already streams the first packed down-projection weights
-//            into registers: they depend on the routing only.           [barrier 2]
-//   phase 3  every CTA stages all h rows, owns 16 output columns at a time, computes
-//            them for every task (warps split tasks and K) and combines the K slots of
-//            each token in slot order under the requested rounding contract.
+//   phase 1  every CTA stages the T token rows in shared memory (they feed every gate/up
+//            tile); the router linear runs one warp per expert row across the whole grid
+//            and publishes each logit as a hand-over word;
+//   phase 2  every CTA waits for the logits and repeats the top-k of the T rows (cheap,
+//            and it spares a second exchange), derives the task list (distinct experts and
+//            their rows) in shared memory; gate/up + SwiGLU tiles (task, 16 rows) are dealt
+//            to groups of four warps across the grid; h rows are published as hand-over
+//            words.  Each warp then already streams the first packed down-projection
+//            weights: they depend on the routing only;
+//   phase 3  every CTA waits for and stages all h rows, owns 16 output columns at a time,
+//            computes them for every task (warps split tasks and K) and combines the K slots
+//            of each token in slot order under the requested rounding contract.
 //
-// The matmul core is the one of qmm.cu: packed codes go from HBM to registers with
-// 8-byte streaming loads, become bf16 (128 + q) with a shift and a lop3, and meet the
-// token rows on the tensor cores (mma.sync m16n8k16, weights are the A operand); scale,
-// bias and the 128 offset are applied per group in fp32; spare mma columns carry other
-// groups (column multiplexing).  Every wait on another CTA is bounded: when the limit
-// is hit the CTA records it in the status word and leaves.
+// The matmul core is the one of qmm.cu: packed codes go from HBM to registers with 8-byte
+// streaming loads (for one token an opt-in variant brings them to shared memory with
+// cp.async.bulk instead), become bf16 (128 + q) with a shift and a lop3, and meet the token
+// rows on the tensor cores (mma.sync m16n8k16, weights are the A operand); scale, bias and
+// the 128 offset are applied per group in fp32; spare mma columns carry other groups
+// (column multiplexing).  Every wait on another CTA is bounded: when the limit is hit the
+// CTA records it in the status word and leaves.
 #include <cstdlib>
 #include <mutex>
 
@@ -39,7 +41,6 @@ constexpr int kLdWarps = kLdThreads / 32;
 constexpr int kLdMaxT = 8;
 constexpr int kLdMaxK = 8;
 constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;      // (token, slot) rows
-constexpr int kLdMaxRows = kLdMaxRouted + kLdMaxT;   // + one shared-expert row per token
 constexpr int kLdMaxTasks = kLdMaxRouted + 1;
 constexpr int kLdDownPD = 2;  // quads of packed weights a warp keeps in flight in the down projection
 constexpr bool kLdBulkByDefault = false;  // the bulk-copy form of the one-token kernel
