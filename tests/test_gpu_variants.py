@@ -41,7 +41,6 @@ def _reference(name: str, T: int):
     ({"ZMOE_LD_BULK": "1"}, "c1", 1, "fused"),
     ({"ZMOE_LD_BULK": "0", "ZMOE_LD_NO_BULK": "1"}, "c2", 1, "fused"),
     ({"ZMOE_STREAM": "1"}, "c2", 1, "separate"),
-    ({"ZMOE_STREAM": "1"}, "c2", 8, "separate"),
 ])
 def test_variant_agrees_with_the_default_kernels(env, name, T, mode):
     rec = _child(env, name, T, mode)

@@ -64,6 +64,7 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
+  int tiles_per_cta;      // upper bound of the 16-column output tiles one CTA owns (sizes ybuf)
   int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
   int* sync;         // {-, -, exit count, status, launch count}
   uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
@@ -89,7 +90,7 @@ struct LdSmem {
 
 __host__ __device__ inline int ld_align16(int a) { return (a + 15) & ~15; }
 
-__host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int n_shared) {
+__host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int n_shared, int tiles_per_cta) {
   LdSmem m;
   const int rtot = T * K + (n_shared ? T : 0);
   const int ngd = d / 64, ngf = f / 64;
@@ -107,7 +108,7 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   m.red = a;
   a += kLdWarps * 32 * 8 * 4;
   m.ybuf = a;
-  a += ld_align16(rtot * 16 * 4);
+  a += ld_align16(tiles_per_cta * rtot * 16 * 4);  // projected rows of every output tile the CTA owns
   m.route = a;
   a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);  // per row: scores, logits, sort keys, group scratch, winners
   m.meta = a;
@@ -560,14 +561,27 @@ __device__ __forceinline__ void ld_mainloop(float (&acc)[NMAT][4], uint2 (&wbuf)
             mma_bf16_m16n8k16(dg[m][3 % NACC], deq_imm<8>(wa.y), deq_imm<8>(wb.y), deq_imm<12>(wa.y),
                               deq_imm<12>(wb.y), xb1.z, xb1.w);
           }
+          // rolling refill: the registers of the group just consumed take the same group of the quad PD steps
+          // ahead at once (keeps the bytes in flight near their maximum instead of dipping once per quad)
+          if (qi + bq + PD < nq_w) {
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (j == 0) wbuf[bq][0][m][h] = ldg_stream_u2<0>(wp[m][h]);
+                if (j == 1) wbuf[bq][1][m][h] = ldg_stream_u2<32>(wp[m][h]);
+                if (j == 2) wbuf[bq][2][m][h] = ldg_stream_u2<64>(wp[m][h]);
+                if (j == 3) wbuf[bq][3][m][h] = ldg_stream_u2<96>(wp[m][h]);
+              }
+            }
+          }
           if (slot == GPB - 1) {
             fold();
             ld_fixup<NMAT, TT>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig,
                                (qi + bq) * 4 + j - (GPB - 1), nq_w);
           }
         }
-        if (qi + bq + PD < nq_w) {  // refill this pipeline slot with the quad PD steps ahead
-          ld_load_quad<NMAT>(wbuf[bq], wp);
+        if (qi + bq + PD < nq_w) {  // the refilled quad's pointers move on
 #pragma unroll
           for (int m = 0; m < NMAT; ++m) {
             wp[m][0] += wk_count * 32;
@@ -771,7 +785,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const int R = T * K;
   const int rtot = R + (p.n_shared ? T : 0);
   const int ngd = d >> 6, ngf = f >> 6;
-  const LdSmem lay = ld_smem(T, K, E, d, f, p.n_shared);
+  const LdSmem lay = ld_smem(T, K, E, d, f, p.n_shared, p.tiles_per_cta);
   unsigned char* xs = smem + lay.xs;
   float* xsum = reinterpret_cast<float*>(smem + lay.xsum);
   float* red = reinterpret_cast<float*>(smem + lay.red);
@@ -1020,15 +1034,22 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
 
     LD_STAMP(6);
-    // ---- phase 3 set-up: how the 16 warps split tasks and K for one 16-column output tile
+    // ---- phase 3 set-up.  The CTA owns the 16-column output tiles blockIdx.x, blockIdx.x + grid, ...; an item
+    // is (tile, task).  The register-pipelined form takes all of its tiles as one batch, so that the warps have
+    // many independent items and few idle rounds; the bulk-copy form has shared-memory slots for one tile.
     const int nqf = ngf >> 2;
-    int wkc = 1;
+    const int ntiles_d = d >> 4;
+    const int ntile_mine = ((int)blockIdx.x < ntiles_d) ? (ntiles_d - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
+    const int tb = BULK ? 1 : ntile_mine;  // tiles per batch
+    int wkc = 1;  // warps that split K for one item
     {
+      const int items = (tb < ntile_mine ? tb : ntile_mine) * n_tasks;
       int best = 1 << 30;
       for (int c = 4; c >= 1; c >>= 1) {  // ties go to the smaller split (fewer partial sums)
         if (c > nqf) continue;
         const int groups = kLdWarps / c;
-        const int cost = ((n_tasks + groups - 1) / groups) * ((nqf + c - 1) / c);
+        // a round of items costs its quads plus a fixed latency of about four quads
+        const int cost = ((items + groups - 1) / groups) * ((nqf + c - 1) / c + 4);
         if (cost <= best) {
           best = cost;
           wkc = c;
@@ -1040,13 +1061,15 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     const int nq_w = (nqf > wk) ? (nqf - wk + wkc - 1) / wkc : 0;
     const int sc_stride = qmm_sc_stride(ngf);
     unsigned char* sraw = smem + lay.sc + gid * (2 * 16 * sc_stride);
-    const int ntiles_d = d >> 4;
     const int gtid = tid - gid * wkc * 32;
+    const int nb0 = tb < ntile_mine ? tb : ntile_mine;  // tiles of the first batch
+    const int pre_tl = gid / n_tasks, pre_a = gid - pre_tl * n_tasks;  // the group's first item
+    const int pre_n0 = ((int)blockIdx.x + pre_tl * nblocks) << 4;
 
     uint2 wbuf[BULK ? 1 : kLdDownPD][4][1][2];
     const uint32_t* wp[1][2];
     // the first item's packed weights and scales depend on the routing only: stream them before waiting for h
-    const bool pre = (int)blockIdx.x < ntiles_d && gid < n_tasks;
+    const bool pre = gid < nb0 * n_tasks;
     if (BULK) {
       // all tasks of the CTA's first tile: warp a copies the 16 rows of task a into down slot a
       if ((int)blockIdx.x < ntiles_d && wid < n_tasks && lane < 16) {
@@ -1056,12 +1079,12 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
       }
     } else if (pre) {
-      ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d,
-                                          f >> 3, blockIdx.x << 4, g, tig, wk, wkc, nq_w);
+      ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a],
+                                          d, f >> 3, pre_n0, g, tig, wk, wkc, nq_w);
     }
     __syncthreads();  // every group of this CTA is done with the gate/up scale areas, which the next copies reuse
     if (pre)
-      ld_issue_sc<1>(ld_pick(p.dn, p.sdn, gid >= n_routed), meta->task_expert[gid], d, ngf, blockIdx.x << 4, sraw,
+      ld_issue_sc<1>(ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a], d, ngf, pre_n0, sraw,
                      sc_stride, gtid, wkc * 32);
     LD_STAMP(7);
     {
@@ -1080,22 +1103,26 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     if (alive) {
       const int xs_stride = qmm_xs_stride(f);
       int d_uses = 0;  // how often the down slots have been filled (parity of their barriers)
-      for (int tile = blockIdx.x; tile < ntiles_d; tile += nblocks, ++d_uses) {
-        const int n0 = tile << 4;
+      for (int b0 = 0; b0 < ntile_mine; b0 += tb, ++d_uses) {
+        const int nb = (tb < ntile_mine - b0) ? tb : ntile_mine - b0;  // tiles of this batch
         if (BULK && d_uses > 0) {
           // the previous tile ended with a CTA-wide barrier: every slot is free again
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           if (wid < n_tasks && lane < 16) {
             const LdBank bank = ld_pick(p.dn, p.sdn, wid >= n_routed);
-            const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + n0 + lane) * (f >> 3);
+            const int n0b = ((int)blockIdx.x + b0 * nblocks) << 4;
+            const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + n0b + lane) * (f >> 3);
             ld_mbar_expect_tx(bars + (4 + wid) * 8, f >> 1);
             ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
           }
         }
-        for (int a = gid; a < n_tasks; a += ngrp) {
+        for (int item = gid; item < nb * n_tasks; item += ngrp) {
+          const int tl = item / n_tasks;
+          const int a = item - tl * n_tasks;
+          const int n0 = ((int)blockIdx.x + (b0 + tl) * nblocks) << 4;
           const bool is_sh = a >= n_routed;
           const int cnt = meta->task_cnt[a];
-          if (!(pre && tile == (int)blockIdx.x && a == gid)) {
+          if (!(pre && b0 == 0 && item == gid)) {
             const LdBank bank = ld_pick(p.dn, p.sdn, is_sh);
             if (!BULK)
               ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc,
@@ -1135,23 +1162,26 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
             for (int j = 0; j < 4; ++j) {
               const int col = 2 * tig + (j & 1);
               const bool writer = (TT == 8) || (col < TT);
-              if (writer && col < cnt) ybuf[(int)meta->task_rows[a][col] * 16 + g + ((j >> 1) ? 8 : 0)] = acc[0][j];
+              if (writer && col < cnt)
+                ybuf[(tl * rtot + (int)meta->task_rows[a][col]) * 16 + g + ((j >> 1) ? 8 : 0)] = acc[0][j];
             }
           }
         }
         __syncthreads();
         LD_STAMP(19);
-        // ordered combine: thread (token, column) walks the K slots; projected values are rounded to T first,
-        // as the separate-kernel path stores them
-        if (tid < T * 16) {
-          const int t = tid >> 4, n = tid & 15;
+        // ordered combine: thread (tile, token, column) walks the K slots; projected values are rounded to T
+        // first, as the separate-kernel path stores them
+        for (int idx = tid; idx < nb * T * 16; idx += kLdThreads) {
+          const int tl = idx / (T * 16);
+          const int t = (idx - tl * T * 16) >> 4, n = idx & 15;
+          const float* yb = ybuf + tl * rtot * 16;
           const int mode = p.combine_mode;
           float a0 = 0.0f;
 #pragma unroll 1
           for (int i = 0; i < K; ++i) {
             float wi = meta->w[t * K + i];
             if (p.out_flags & 2) wi = round_bf16(wi);
-            const float v0 = round_bf16(ybuf[(t * K + i) * 16 + n]);
+            const float v0 = round_bf16(yb[(t * K + i) * 16 + n]);
             if (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_T) {
               a0 = fmaf(wi, v0, a0);
             } else if (mode == ZMOE_COMBINE_FP32_NO_FMA || mode == ZMOE_COMBINE_NO_FMA) {
@@ -1163,13 +1193,13 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
               a0 = round_bf16(__fadd_rn(a0, __fmul_rn(wi, v0)));
             }
           }
-          const size_t oo = (size_t)t * d + n0 + n;
+          const size_t oo = (size_t)t * d + (((int)blockIdx.x + (b0 + tl) * nblocks) << 4) + n;
           const bool fp32_mode = (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_FP32_NO_FMA);
           if (fp32_mode && !(p.out_flags & 1)) {
             reinterpret_cast<float*>(p.out)[oo] = a0;
           } else {
             a0 = round_bf16(a0);
-            if (p.n_shared) a0 = __fadd_rn(a0, round_bf16(ybuf[(R + t) * 16 + n]));
+            if (p.n_shared) a0 = __fadd_rn(a0, round_bf16(yb[(R + t) * 16 + n]));
             reinterpret_cast<__nv_bfloat16*>(p.out)[oo] = __float2bfloat16_rn(a0);
           }
         }
@@ -1214,6 +1244,9 @@ static int ld_sm_count(int* out) {
   return ZMOE_OK;
 }
 
+// Output tiles per CTA that the shared-memory layout provides for: right for grids of 128 CTAs or more.
+static int ld_tiles_assumed(int d_model) { return (d_model / 16 + 127) / 128; }
+
 // Why a block shape cannot take the one-launch path (nullptr: it can).
 static const char* ld_unsupported(const zmoe_layer_desc* L, int T) {
   if (L->qmode != ZMOE_Q_AFFINE4 || L->group_size != 64) return "needs 4-bit affine weights with group size 64";
@@ -1222,7 +1255,7 @@ static const char* ld_unsupported(const zmoe_layer_desc* L, int T) {
   if (L->E < L->top_k || L->E > 256) return "takes at most 256 experts";
   if (L->d_model % 256 != 0 || L->d_ff % 256 != 0) return "needs d_model and d_ff to be multiples of 256";
   if (L->n_shared < 0 || L->n_shared > 1) return "takes at most one shared expert";
-  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared);
+  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared, ld_tiles_assumed(L->d_model));
   if (lay.total > 220 * 1024) return "needs more shared memory than an SM has";
   return nullptr;
 }
@@ -1362,7 +1395,10 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   int sms = 0;
   int rc = ld_sm_count(&sms);
   if (rc != ZMOE_OK) return rc;
-  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared);
+  p.tiles_per_cta = ld_tiles_assumed(L->d_model);
+  ZMOE_REQUIRE((L->d_model / 16 + sms - 1) / sms <= p.tiles_per_cta, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: this GPU has %d SMs, the one-launch path is laid out for 128 or more", sms);
+  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared, p.tiles_per_cta);
   cudaStream_t st = (cudaStream_t)stream;
   p.bulk_off = 0;
   p.g_slots = 0;
