@@ -309,13 +309,14 @@ def main() -> None:
     barrier()
     ev0 = torch.cuda.Event(enable_timing=True)
     ev1 = torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        with torch.cuda.stream(stream):
-            ev0.record(stream)
-            for _ in range(args.steps):
-                run_step()
-            ev1.record(stream)
-        barrier()
+    clocks = ClockSampler(local)  # samples over both timed regions (device-timed steps, then end to end)
+    clocks.__enter__()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        ev1.record(stream)
+    barrier()
     ms = ev0.elapsed_time(ev1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -342,6 +343,7 @@ def main() -> None:
             stream.synchronize()  # the caller reads the result before issuing the next step
         e1.record(stream)
     barrier()
+    clocks.__exit__()
     e2e_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
@@ -351,6 +353,9 @@ def main() -> None:
 
     if rank == 0:
         peak, peak_kind = _peaks()
+        # DRAM bytes per launch of the one-launch block at the default workload, from the ncu capture summarised in
+        # profiles/layer_decode_c2_T1_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum, mean of 4 launches)
+        traffic = 21.874e6 if (one_launch and cfg.name.startswith("c2") and T == 1) else None
         achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -365,7 +370,8 @@ def main() -> None:
                        "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
                                        "reduce-scattered (NCCL)") if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": (alg_bytes_step / L) if one_launch else None,
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
                                   "whole block in one cooperative launch (zmoe_layer_decode)" if one_launch else

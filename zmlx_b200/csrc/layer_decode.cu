@@ -290,47 +290,7 @@ __device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32
       }
     }
   } else {
-    // sigmoid + selection bias, optional group-limited selection
-#pragma unroll 1
-    for (int j = 0; j < nj; ++j) {
-      const int idx = lane + 32 * j;
-      if (idx < E) vals[idx] = sigmoid_stable(lgs[idx]) + bias[idx];
-    }
-    if (n_group > 1) {
-      float* gkeep = gsc + 32;
-      __syncwarp();
-      const int per = E / n_group;
-      if (lane < n_group) {
-        float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
-#pragma unroll 4
-        for (int j = 0; j < per; ++j) {
-          const float x = vals[lane * per + j];
-          if (x > t1) {
-            t2 = t1;
-            t1 = x;
-          } else if (x > t2) {
-            t2 = x;
-          }
-        }
-        gsc[lane] = t1 + t2;
-      }
-      __syncwarp();
-      if (lane < n_group) {
-        const float mine = gsc[lane];
-        int rank = 0;
-        for (int h = 0; h < n_group; ++h) {
-          const float o = gsc[h];
-          rank += (o > mine) || (o == mine && h < lane);
-        }
-        gkeep[lane] = (rank < topk_group) ? 1.0f : 0.0f;
-      }
-      __syncwarp();
-#pragma unroll 1
-      for (int j = 0; j < nj; ++j) {
-        const int idx = lane + 32 * j;
-        if (idx < E && gkeep[idx / per] == 0.0f) vals[idx] = 0.0f;
-      }
-    }
+    return true;  // sigmoid family: the scores are computed by all threads (ld_sigmoid_scores)
   }
 #pragma unroll 1
   for (int j = 0; j < nj; ++j) {
@@ -338,6 +298,62 @@ __device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32
     if (idx < E) keys[idx] = make_uint2(~(uint32_t)idx, ld_order_key(vals[idx] + 0.0f));  // .y is the high half
   }
   return true;
+}
+
+// Step 1b, sigmoid family, all threads: scores = sigmoid(logit) + bias, group-limited selection (a group's
+// score is the sum of its two largest scores; the best topk_group groups are kept, ties to the lower group;
+// the experts of the other groups are scored 0.0), then the sort keys.  Maxima and the sum of two numbers do
+// not depend on evaluation order, so the result is bit-identical to the one-warp form of sigmoid_topk_row.
+// Contains CTA-wide barriers: every thread must call it.
+__device__ __forceinline__ void ld_sigmoid_scores(int T, int E, const float* bias, int n_group, int topk_group,
+                                                  float* vals, const float* lgs, uint2* keys, float* gsc) {
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  for (int i = tid; i < T * E; i += kLdThreads) vals[i] = sigmoid_stable(lgs[i]) + bias[i % E];
+  if (n_group > 1) {  // uniform over the CTA
+    __syncthreads();
+    const int per = E / n_group;
+    for (int pg = wid; pg < T * n_group; pg += kLdWarps) {  // one warp per (row, group)
+      const int t = pg / n_group, grp = pg - t * n_group;
+      const float* src = vals + (size_t)t * E + grp * per;
+      float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+      for (int j = lane; j < per; j += 32) {
+        const float x = src[j];
+        if (x > t1) {
+          t2 = t1;
+          t1 = x;
+        } else if (x > t2) {
+          t2 = x;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {  // merge the lanes' (largest, second largest) pairs
+        const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
+        const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
+        const float hi = fmaxf(t1, o1);
+        t2 = fmaxf(fminf(t1, o1), fmaxf(t2, o2));
+        t1 = hi;
+      }
+      if (lane == 0) gsc[t * 64 + grp] = t1 + t2;
+    }
+    __syncthreads();
+    if (tid < T * n_group) {
+      const int t = tid / n_group, grp = tid - t * n_group;
+      const float mine = gsc[t * 64 + grp];
+      int rank = 0;
+      for (int h = 0; h < n_group; ++h) {
+        const float o = gsc[t * 64 + h];
+        rank += (o > mine) || (o == mine && h < grp);
+      }
+      gsc[t * 64 + 32 + grp] = (rank < topk_group) ? 1.0f : 0.0f;
+    }
+    __syncthreads();
+    for (int i = tid; i < T * E; i += kLdThreads) {
+      const int t = i / E, e = i - t * E;
+      if (gsc[t * 64 + 32 + e / per] == 0.0f) vals[i] = 0.0f;
+    }
+  }
+  // each thread reads back only what it wrote itself
+  for (int i = tid; i < T * E; i += kLdThreads) keys[i] = make_uint2(~(uint32_t)(i % E), ld_order_key(vals[i] + 0.0f));
 }
 
 // Step 2, all threads: rank of every score under (score descending, expert id ascending) -- one unsigned
@@ -876,6 +892,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       }
     }
     __syncthreads();
+    if (p.family == 2) {
+      ld_sigmoid_scores(T, E, p.rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
+      __syncthreads();
+    }
     LD_STAMP(20);
     if (wait_failed == 0) ld_rank_select(keys, T, E, K, sel_idx);
     __syncthreads();

@@ -82,6 +82,10 @@ class MoELayer:
         T = x.shape[0]
         ws = self._fused_ws.get(T)
         if ws is None:
+            if torch.cuda.is_current_stream_capturing():
+                # a workspace zeroed inside the graph would be zeroed again at every replay, and with it the launch
+                # count that tells this launch's hand-over words from the previous one's
+                raise RuntimeError(f"run the block once with {T} token(s) before capturing it in a CUDA graph")
             need = self.fused_workspace_bytes(T)
             if need == 0:
                 raise _lib.ZmoeError(_lib.ERR_UNSUPPORTED, f"no one-launch path for this block at T={T}")
