@@ -47,6 +47,9 @@ def _args():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--launch", default="pdl", choices=["pdl", "cooperative"],
+                    help="how the one-launch block is launched: 'pdl' = regular launch set up while the previous "
+                         "block still runs (this benchmark has the GPU to itself), 'cooperative' = the library default")
     ap.add_argument("--no-fused", action="store_true",
                     help="run every block as separate kernels even where the one-launch decode kernel covers it")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallel")
@@ -75,6 +78,38 @@ class ClockSampler:
         self._thr = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
+
+    def _run_nvml(self):
+        """NVML reads (a few microseconds each) every 5 ms: many samples even inside a 30 ms timed region."""
+        import pynvml as nv
+
+        nv.nvmlInit()
+        try:
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown if hasattr(nv, "nvmlClocksEventReasonHwSlowdown")
+                    else nv.nvmlClocksThrottleReasonHwSlowdown,
+                    "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown",
+                                                   getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0)),
+                    "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown",
+                                                   getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0)),
+                    "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap",
+                                            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0))}
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop.is_set():
+                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = int(get_reasons(h))
+                self.samples.append((sm, mx, [n for n, b in bits.items() if b and (mask & b)]))
+                self._stop.wait(0.005)
+        finally:
+            nv.nvmlShutdown()
+
+    def _run_smi(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -222,7 +257,7 @@ def main() -> None:
         torch.cuda.empty_cache()
     else:
         layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T,
-                           fused=not args.no_fused)
+                           fused=not args.no_fused, launch=args.launch)
                   for i in range(L)]
     x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
     x_dev = x_host.to(dev)
@@ -367,6 +402,7 @@ def main() -> None:
                        "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
+                       "block_launch": args.launch if one_launch else None,
                        "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
                                        "reduce-scattered (NCCL)") if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

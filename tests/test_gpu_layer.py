@@ -119,6 +119,28 @@ def test_one_launch_block_agrees_with_the_separate_kernels(name, T):
     assert one.fused_status(T) == 0
 
 
+@pytest.mark.parametrize("name,T", [("c2", 1), ("c2", 4), ("c5", 1)])
+def test_programmatic_dependent_launch_mode_gives_the_same_bits(name, T):
+    """A chain of blocks launched as regular kernels that are set up while their predecessor still runs must equal
+    the same chain launched cooperatively (also across repeated passes: the hand-over tags advance per launch)."""
+    cfg, params = _layer(name)
+    chains = {}
+    for launch in ("cooperative", "pdl"):
+        layers = [MoELayer(cfg, params, max_tokens=8, launch=launch) for _ in range(3)]
+        x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
+        outs = []
+        for _ in range(3):
+            h = x
+            for ly in layers:
+                h = ly(h)
+            outs.append(h.clone())
+        torch.cuda.synchronize()
+        assert all(ly.fused_status(T) == 0 for ly in layers)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        chains[launch] = outs[0]
+    assert torch.equal(chains["cooperative"], chains["pdl"])
+
+
 def test_one_launch_block_rejects_what_it_does_not_cover():
     cfg, params = _layer("c3")  # mxfp4
     layer = MoELayer(cfg, params, max_tokens=8)

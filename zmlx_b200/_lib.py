@@ -47,7 +47,7 @@ class LayerDesc(ctypes.Structure):
                                                "router_family", "renorm", "n_group", "topk_group")]
                 + [("routed_scale", c_float)]
                 + [(n, ctypes.c_int32) for n in ("n_shared", "swiglu_mode", "shared_swiglu_mode", "combine_mode",
-                                                 "out_flags")]
+                                                 "out_flags", "launch_mode")]
                 + [("router_w", c_void_p), ("router_bias", c_void_p), ("routed", ExpertBank), ("shared", ExpertBank)])
 
 

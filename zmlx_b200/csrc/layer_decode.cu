@@ -64,6 +64,7 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
+  int pdl;                // regular launch with programmatic dependent launch instead of a cooperative one
   int tiles_per_cta;      // upper bound of the 16-column output tiles one CTA owns (sizes ybuf)
   int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
   int* sync;         // {-, -, exit count, status, launch count}
@@ -815,6 +816,19 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const int zpage = lay.zero;
   const int nblocks = gridDim.x;
   bool alive = true;
+  // Router rows are constants: the warp's first one is requested before anything that depends on the previous
+  // kernel of the stream, so that with programmatic dependent launch its HBM latency hides behind that kernel.
+  const int e_first = blockIdx.x + nblocks * wid;
+  uint4 wpre[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+    wpre[u] = (e_first < E && lane + 32 * u < (d >> 3))
+                  ? __ldg(reinterpret_cast<const uint4*>(p.wr + (size_t)e_first * d) + lane + 32 * u)
+                  : make_uint4(0u, 0u, 0u, 0u);
+  if (p.pdl) {
+    pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
+    pdl_wait();     // nothing below may run before the previous kernel has finished and flushed
+  }
   // launch count: stable while this launch runs (the last CTA to leave bumps it); tag of this launch's words
   const int epoch = __ldcg(p.sync + 4);
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
@@ -852,9 +866,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
 #pragma unroll 1
         for (int i0 = lane; i0 < nvec; i0 += 256) {
           uint4 wv[8], xv[8];
+          const bool have = (e == e_first) && (i0 == lane);  // warp-uniform: the chunk requested at kernel start
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            wv[u] = (i0 + 32 * u < nvec) ? __ldg(wrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u);
+            wv[u] = have ? wpre[u] : ((i0 + 32 * u < nvec) ? __ldg(wrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u));
 #pragma unroll
           for (int u = 0; u < 8; ++u)
             xv[u] = (i0 + 32 * u < nvec) ? __ldg(xrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u);
@@ -1292,6 +1307,12 @@ static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
                 cudaGetErrorString(e));
+  if (p.pdl) {
+    // regular launch, one CTA per SM by its size; the caller vouches that no other work holds SMs for long
+    e = launch_pdl(kern, dim3(grid), dim3(kLdThreads), smem_bytes, st, p);
+    if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: launch failed: %s", cudaGetErrorString(e));
+    return check_launch("layer_decode_kernel");
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kLdThreads);
@@ -1404,6 +1425,9 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.sepi = L->shared_swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : 2;
   p.combine_mode = L->combine_mode;
   p.out_flags = L->out_flags;
+  ZMOE_REQUIRE(L->launch_mode == 0 || L->launch_mode == 1, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: launch_mode %d", L->launch_mode);
+  p.pdl = L->launch_mode;
   unsigned char* ws = (unsigned char*)workspace;
   p.sync = (int*)ws;
   p.logits = (uint32_t*)(ws + ld_ws_logits_off());

@@ -23,7 +23,7 @@ class MoELayer:
     """Packed weights of one MoE layer plus the buffers of its forward pass."""
 
     def __init__(self, cfg: MoEConfig, params: dict, *, max_tokens: int = 64, combine: str | None = None,
-                 swiglu: str | None = None, fused: bool = True):
+                 swiglu: str | None = None, fused: bool = True, launch: str = "cooperative"):
         self.cfg = cfg
         self.p = params
         dev = params["gate_w"].device
@@ -37,6 +37,11 @@ class MoELayer:
         self.gs = 32 if cfg.mode == "mxfp4" else cfg.group_size
         self._alloc(max_tokens)
         self.fused = bool(fused)
+        if launch not in ("cooperative", "pdl"):
+            raise ValueError("launch must be 'cooperative' or 'pdl'")
+        # 'pdl': the one-launch block as a regular launch that is set up while the previous kernel still runs
+        # (saves the launch gap in a chain of blocks); only when this stream has the GPU to itself
+        self.launch = launch
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
 
@@ -56,6 +61,7 @@ class MoELayer:
         d.swiglu_mode, d.shared_swiglu_mode = self.swiglu, _lib.SWIGLU_PER_OP
         d.combine_mode = self.combine_mode
         d.out_flags = 3 if cfg.family == "generic" else 1
+        d.launch_mode = 1 if self.launch == "pdl" else 0
         d.router_w = W["router_w"].data_ptr()
         d.router_bias = bias.data_ptr() if bias is not None else None
 
