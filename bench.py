@@ -297,8 +297,9 @@ def main() -> None:
         # bytes this rank must move: its local experts, the replicated router over all gathered tokens, rows in/out
         alg_bytes_step = sum(dn * cfg.expert_bytes + cfg.n_shared * cfg.expert_bytes + cfg.router_bytes
                              + 4 * T * world * cfg.d_model for dn in distinct)
-        # the collectives run eagerly between the kernels: capturing them in a CUDA graph together with the
-        # programmatic-dependent-launch kernels stalled on this software stack, so the EP step is not captured
+        # The collectives run eagerly between the kernels: capturing them in a CUDA graph together with the kernels
+        # stalled twice on this software stack (default and thread-local capture error mode; both calls ran into
+        # their time limit without a GPU fault), so the expert-parallel step is not captured.
         args.no_graph = True
     else:
         distinct = [int(torch.unique(ly.indices[:T]).numel()) for ly in layers]

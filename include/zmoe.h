@@ -267,7 +267,7 @@ typedef struct zmoe_layer_desc {
  *
  * workspace: zmoe_layer_decode_workspace_bytes(L, T) bytes, 256-byte aligned, ALL ZERO before the first
  * call, then left to the library and used with the same T (zero it again before changing T).  It starts
- * with five ints {-, -, exit count, status, launch count}.  CTAs hand the router logits and the
+ * with five ints {-, -, sign-in count, status, launch count}.  CTAs hand the router logits and the
  * activated rows to each other through the workspace as tagged 32-bit words and re-read a word until it
  * carries the current launch's tag; every such wait is bounded, and one that runs out sets status to 1
  * and ends the launch with `out` undefined.  One workspace serves one stream at a time.

@@ -141,6 +141,26 @@ def test_programmatic_dependent_launch_mode_gives_the_same_bits(name, T):
     assert torch.equal(chains["cooperative"], chains["pdl"])
 
 
+@pytest.mark.parametrize("norm,with_bias,T", [(False, False, 1), (True, True, 1), (False, True, 3), (True, True, 8)])
+def test_one_launch_block_covers_the_softmax_then_top_k_family_with_bias(norm, with_bias, T):
+    """The generic block with `norm_topk_prob` off and/or an `expert_bias` takes the full-softmax [+ bias] -> top-k
+    [-> renormalise] router (moe.py:1326-1377); routing must be bit-identical to the stand-alone router kernels."""
+    cfg = synthetic.CONFIGS["c1"].scaled(norm_topk_prob=norm)
+    params = dict(synthetic.make_layer(cfg, device=DEV))
+    if with_bias:
+        g = torch.Generator(device="cpu").manual_seed(99)
+        params["expert_bias"] = (torch.randn(cfg.n_experts, generator=g) * 0.01).to(DEV)
+    one = MoELayer(cfg, params, max_tokens=8, fused=True)
+    sep = MoELayer(cfg, params, max_tokens=8, fused=False)
+    assert one._route_args()[0] == 1  # softmax-then-top-k family
+    x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
+    a, b = one(x).clone(), sep(x).clone()
+    assert one.fused_status(T) == 0
+    assert torch.equal(one.indices[:T], sep.indices[:T])
+    assert torch.equal(one.weights[:T], sep.weights[:T])
+    assert_close_rel(t2n(a), t2n(b), 2e-2, f"c1 norm={norm} bias={with_bias} T={T}")
+
+
 def test_one_launch_block_rejects_what_it_does_not_cover():
     cfg, params = _layer("c3")  # mxfp4
     layer = MoELayer(cfg, params, max_tokens=8)

@@ -42,7 +42,9 @@ constexpr int kLdMaxT = 8;
 constexpr int kLdMaxK = 8;
 constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;      // (token, slot) rows
 constexpr int kLdMaxTasks = kLdMaxRouted + 1;
-constexpr int kLdDownPD = 2;  // quads of packed weights a warp keeps in flight in the down projection
+// DPD (kernel template parameter): quads of packed weights a warp keeps in flight in the down projection: 2 when
+// a warp's share of an item is two quads anyway (d_ff < 2048), 4 for long rows, where one warp streams a whole
+// item and the bytes in flight per SM decide the bandwidth
 constexpr bool kLdBulkByDefault = false;  // the bulk-copy form of the one-token kernel
 constexpr int kLdSpinLimit = 1 << 21;  // polls of the barrier counter before a CTA gives up (~1 s)
 
@@ -67,7 +69,7 @@ struct LdParams {
   int pdl;                // regular launch with programmatic dependent launch instead of a cooperative one
   int tiles_per_cta;      // upper bound of the 16-column output tiles one CTA owns (sizes ybuf)
   int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
-  int* sync;         // {-, -, exit count, status, launch count}
+  int* sync;         // {-, -, sign-in count, status, launch count}
   uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
   uint32_t* h;       // (rows, f) hand-over words
   float* weights;
@@ -785,7 +787,7 @@ __device__ __forceinline__ void ld_smem_mainloop(float (&acc)[NMAT][4], const un
 #endif
 
 // ------------------------------------------------------------------ the kernel
-template <int TT, bool BULK>
+template <int TT, bool BULK, int DPD>
 __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
   static_assert(!BULK || TT == 1, "the bulk-copy variant is the one-token kernel");
   extern __shared__ __align__(16) unsigned char smem[];
@@ -829,7 +831,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
     pdl_wait();     // nothing below may run before the previous kernel has finished and flushed
   }
-  // launch count: stable while this launch runs (the last CTA to leave bumps it); tag of this launch's words
+  // launch count: every thread reads it here; the last CTA to sign in (below) bumps it for the next launch; tag of
+  // this launch's words
   const int epoch = __ldcg(p.sync + 4);
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
   if (tid == 0) wait_failed = 0;
@@ -893,6 +896,15 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   }
   LD_STAMP(2);
   __syncthreads();  // wait_failed, the zero page and the cleared task counts are in place
+  // Launch count for the next launch.  Every thread of this CTA has read the count by now, so the CTA can sign
+  // in; the last CTA of the grid to do so bumps the count (the tags of THIS launch live in registers already)
+  // and clears the sign-in counter.  Doing it here, not at the end, keeps the atomic's round trip off the tail.
+  if (tid == 0) {
+    if (atomicAdd(p.sync + 2, 1) == nblocks - 1) {
+      p.sync[4] = epoch + 1;
+      p.sync[2] = 0;
+    }
+  }
 
   {
     // ---- phase 2a: routing of every row, repeated by every CTA (one warp per row); the logits arrive as
@@ -1101,7 +1113,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     const int pre_tl = gid / n_tasks, pre_a = gid - pre_tl * n_tasks;  // the group's first item
     const int pre_n0 = ((int)blockIdx.x + pre_tl * nblocks) << 4;
 
-    uint2 wbuf[BULK ? 1 : kLdDownPD][4][1][2];
+    uint2 wbuf[BULK ? 1 : DPD][4][1][2];
     const uint32_t* wp[1][2];
     // the first item's packed weights and scales depend on the routing only: stream them before waiting for h
     const bool pre = gid < nb0 * n_tasks;
@@ -1114,7 +1126,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
       }
     } else if (pre) {
-      ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a],
+      ld_issue_w<1, BULK ? 1 : DPD>(wbuf, wp, ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a],
                                           d, f >> 3, pre_n0, g, tig, wk, wkc, nq_w);
     }
     __syncthreads();  // every group of this CTA is done with the gate/up scale areas, which the next copies reuse
@@ -1160,7 +1172,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
           if (!(pre && b0 == 0 && item == gid)) {
             const LdBank bank = ld_pick(p.dn, p.sdn, is_sh);
             if (!BULK)
-              ld_issue_w<1, BULK ? 1 : kLdDownPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc,
+              ld_issue_w<1, BULK ? 1 : DPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc,
                                                   nq_w);
             ld_group_sync(gid, wkc);  // the previous item is done with the group's scale area
             ld_issue_sc<1>(bank, meta->task_expert[a], d, ngf, n0, sraw, sc_stride, gtid, wkc * 32);
@@ -1186,7 +1198,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
             ld_smem_mainloop<1, 4>(acc, dslots + a * 16 * rs_d, rs_d, smem, lay.xs + srow * xs_stride + tig * 32, zpage,
                                    xsum, rtot, srow_c, sraw, sc_stride, wk, wkc, nqf, g, tig);
           else
-            ld_mainloop<1, BULK ? 1 : kLdDownPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok,
+            ld_mainloop<1, BULK ? 1 : DPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok,
                                                         zpage, slot_g, xsum, rtot, srow_c, sraw, sc_stride, wk, wkc,
                                                         nq_w, g, tig);
           LD_STAMP(17);
@@ -1243,17 +1255,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
 
-  // ---- exit: the last CTA to leave bumps the launch count (a new tag for the next launch)
-  __syncthreads();
   LD_STAMP(10);
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(p.sync + 2, 1) == nblocks - 1) {
-      p.sync[4] = epoch + 1;
-      __threadfence();
-      p.sync[2] = 0;
-    }
-  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -1300,9 +1302,9 @@ static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
   return (ld_ws_logits_off() + (size_t)T * L->E * 32 + 255) & ~(size_t)255;
 }
 
-template <int TT, bool BULK>
+template <int TT, bool BULK, int DPD>
 static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = layer_decode_kernel<TT, BULK>;
+  auto kern = layer_decode_kernel<TT, BULK, DPD>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
@@ -1468,13 +1470,19 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
     if (!no_bulk && aligned && n_tasks <= 12 && total <= 220 * 1024) {
       p.bulk_off = bulk_off;
       p.g_slots = g_slots;
-      return ld_launch<1, true>(p, sms, total, st);
+      return ld_launch<1, true, 2>(p, sms, total, st);
     }
-    return ld_launch<1, false>(p, sms, lay.total, st);
+    if (L->d_ff >= 2048) return ld_launch<1, false, 4>(p, sms, lay.total, st);
+    return ld_launch<1, false, 2>(p, sms, lay.total, st);
   }
-  if (T <= 2) return ld_launch<2, false>(p, sms, lay.total, st);
-  if (T <= 4) return ld_launch<4, false>(p, sms, lay.total, st);
-  return ld_launch<8, false>(p, sms, lay.total, st);
+  if (L->d_ff >= 2048) {
+    if (T <= 2) return ld_launch<2, false, 4>(p, sms, lay.total, st);
+    if (T <= 4) return ld_launch<4, false, 4>(p, sms, lay.total, st);
+    return ld_launch<8, false, 4>(p, sms, lay.total, st);
+  }
+  if (T <= 2) return ld_launch<2, false, 2>(p, sms, lay.total, st);
+  if (T <= 4) return ld_launch<4, false, 2>(p, sms, lay.total, st);
+  return ld_launch<8, false, 2>(p, sms, lay.total, st);
 }
 
 }  // extern "C"
