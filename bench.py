@@ -53,6 +53,8 @@ def _args():
     ap.add_argument("--no-fused", action="store_true",
                     help="run every block as separate kernels even where the one-launch decode kernel covers it")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallel")
+    ap.add_argument("--ep-segments", action="store_true",
+                    help="N>1: replay the kernels between the two collectives of a layer from one CUDA graph")
     ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
 
@@ -249,7 +251,7 @@ def main() -> None:
             full = synthetic.make_layer(cfg, layer=i, device=dev)  # same seed on every rank: one model
             lo, hi = ep.expert_range(cfg.n_experts, world, rank)
             layers.append(ep.EPMoELayer(cfg, ep.shard_params(full, lo, hi), rank=rank, world=world, max_tokens=T,
-                                        sharded=True))
+                                        sharded=True, segment_graphs=args.ep_segments))
             if args.check and i == 0:
                 ref_layer = MoELayer(cfg, full, max_tokens=T)
             else:
@@ -405,7 +407,9 @@ def main() -> None:
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
                        "block_launch": args.launch if one_launch else None,
                        "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
-                                       "reduce-scattered (NCCL)") if use_ep else f"replicas x{world}"},
+                                       "reduce-scattered (NCCL)"
+                                       + ("; kernels between the collectives replayed from per-layer CUDA graphs"
+                                          if args.ep_segments else "")) if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_launch": (alg_bytes_step / L) if one_launch else None,

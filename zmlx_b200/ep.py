@@ -94,7 +94,7 @@ class EPMoELayer:
     shard (``sharded=True``)."""
 
     def __init__(self, cfg: MoEConfig, params: dict, *, rank: int, world: int, max_tokens: int = 16, group=None,
-                 sharded: bool = False):
+                 sharded: bool = False, segment_graphs: bool = False):
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self.lo, self.hi = expert_range(cfg.n_experts, world, rank)
         local = params if sharded else shard_params(params, self.lo, self.hi)
@@ -106,7 +106,61 @@ class EPMoELayer:
         self.local_idx = torch.empty((TK,), dtype=torch.int32, device=dev)
         self.local_plan = torch.empty(ops.plan_bytes(TK, self.n_local) // 4, dtype=torch.int32, device=dev)
         self.out = torch.empty((max_tokens, cfg.d_model), dtype=torch.bfloat16, device=dev)
+        self.x_all = torch.empty((max_tokens * world, cfg.d_model), dtype=torch.bfloat16, device=dev)
+        self.y_mine = torch.empty((max_tokens * cfg.top_k, cfg.d_model), dtype=torch.bfloat16, device=dev)
         self.max_tokens = max_tokens
+        # segment_graphs: the kernels between the two collectives (router, local plan, gate/up, down: six launches
+        # on fixed buffers) are captured in one CUDA graph per token count and replayed; the collectives stay eager
+        self.segment_graphs = bool(segment_graphs)
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._seen: set[int] = set()
+
+    def _segment(self, TA: int) -> None:
+        """Router for all gathered tokens, the plan of the local experts, gate/up + SwiGLU and down projection into
+        zeroed per-slot rows: everything between the all-gather and the reduce-scatter."""
+        cfg, inner = self.cfg, self.inner
+        K = cfg.top_k
+        lib = _lib.load()
+        p = ops._ptr
+        x_all = self.x_all[:TA]
+        inner.route(x_all)  # replicated: weights/indices of all R*T tokens (the full-E plan is unused)
+        li = self.local_idx[:TA * K]
+        torch.sub(inner.indices[:TA].reshape(-1), self.lo, out=li)  # ids outside [0, n_local) are dropped
+        st = ops._stream()
+        _lib.check(lib.zmoe_build_plan(None, K, p(li), TA * K, 1, self.n_local, p(self.local_plan),
+                                       self.local_plan.numel() * 4, st))
+        qm = ops.qmode_code(cfg.mode)
+        W = inner.p
+        y = inner.y[:TA * K]
+        y.zero_()
+        _lib.check(lib.zmoe_gather_qmm_swiglu(p(x_all), TA, x_all.stride(0), p(W["gate_w"]), p(W["gate_s"]),
+                                              p(W["gate_b"]), p(W["up_w"]), p(W["up_s"]), p(W["up_b"]),
+                                              self.n_local, cfg.d_ff, cfg.d_model, inner.gs, qm,
+                                              p(self.local_plan), TA * K, TA, p(inner.h), inner.swiglu, st))
+        _lib.check(lib.zmoe_gather_qmm(p(inner.h), TA * K, cfg.d_ff, p(W["down_w"]), p(W["down_s"]),
+                                       p(W["down_b"]), self.n_local, cfg.d_model, cfg.d_ff, inner.gs, qm,
+                                       p(self.local_plan), TA * K, TA, 1, p(y), st))
+
+    def _run_segment(self, TA: int) -> None:
+        if not self.segment_graphs:
+            self._segment(TA)
+            return
+        g = self._graphs.get(TA)
+        if g is None:
+            if TA not in self._seen:  # first pass at this size runs eagerly (loads kernels, sizes buffers)
+                self._seen.add(TA)
+                self._segment(TA)
+                return
+            cur = torch.cuda.current_stream(self.inner.device)
+            side = torch.cuda.Stream(device=self.inner.device)
+            side.wait_stream(cur)
+            g = torch.cuda.CUDAGraph()
+            # thread-local: the process group's watchdog thread may poll CUDA events while this thread captures
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                self._segment(TA)
+            cur.wait_stream(side)
+            self._graphs[TA] = g
+        g.replay()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         cfg, inner, R = self.cfg, self.inner, self.world
@@ -117,26 +171,18 @@ class EPMoELayer:
         lib = _lib.load()
         p = ops._ptr
         with torch.cuda.device(inner.device):
-            x_all = gather_tokens(x, R, self.group)  # (R*T, d)
-            TA = x_all.shape[0]
-            inner.route(x_all)  # replicated: weights/indices of all R*T tokens (the full-E plan is unused)
-            li = self.local_idx[:TA * K]
-            torch.sub(inner.indices[:TA].reshape(-1), self.lo, out=li)  # ids outside [0, n_local) are dropped
-            st = ops._stream()
-            _lib.check(lib.zmoe_build_plan(None, K, p(li), TA * K, 1, self.n_local, p(self.local_plan),
-                                           self.local_plan.numel() * 4, st))
-            qm = ops.qmode_code(cfg.mode)
-            W = inner.p
+            TA = R * T
+            if R > 1 and x.is_cuda:
+                dist.all_gather_into_tensor(self.x_all[:TA], x.contiguous(), group=self.group)
+            else:
+                self.x_all[:TA].copy_(gather_tokens(x, R, self.group))
+            self._run_segment(TA)
             y = inner.y[:TA * K]
-            y.zero_()
-            _lib.check(lib.zmoe_gather_qmm_swiglu(p(x_all), TA, x_all.stride(0), p(W["gate_w"]), p(W["gate_s"]),
-                                                  p(W["gate_b"]), p(W["up_w"]), p(W["up_s"]), p(W["up_b"]),
-                                                  self.n_local, cfg.d_ff, cfg.d_model, inner.gs, qm,
-                                                  p(self.local_plan), TA * K, TA, p(inner.h), inner.swiglu, st))
-            _lib.check(lib.zmoe_gather_qmm(p(inner.h), TA * K, cfg.d_ff, p(W["down_w"]), p(W["down_s"]),
-                                           p(W["down_b"]), self.n_local, cfg.d_model, cfg.d_ff, inner.gs, qm,
-                                           p(self.local_plan), TA * K, TA, 1, p(y), st))
-            y_mine = exchange_slot_rows(y, R, self.group)  # (T*K, d): complete rows of this rank's tokens
+            if R > 1 and y.is_cuda:
+                y_mine = self.y_mine[:T * K]
+                dist.reduce_scatter_tensor(y_mine, y, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                y_mine = exchange_slot_rows(y, R, self.group)  # (T*K, d): complete rows of this rank's tokens
             w_mine = inner.weights[self.rank * T:(self.rank + 1) * T] if R > 1 else inner.weights[:T]
             residual = None
             if cfg.n_shared:
