@@ -53,8 +53,9 @@ def _args():
     ap.add_argument("--no-fused", action="store_true",
                     help="run every block as separate kernels even where the one-launch decode kernel covers it")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallel")
-    ap.add_argument("--ep-segments", action="store_true",
-                    help="N>1: replay the kernels between the two collectives of a layer from one CUDA graph")
+    ap.add_argument("--no-ep-segments", dest="ep_segments", action="store_false",
+                    help="N>1: launch the kernels between the two collectives of a layer eagerly instead of "
+                         "replaying them from one CUDA graph per layer")
     ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
 
