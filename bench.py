@@ -2,7 +2,9 @@
 
 A *step* is one batch of T decode tokens passing through L stacked MoE layers with
 distinct weights (the Qwen3-30B-A3B-shaped layer, 128 experts, top-8, 4-bit affine
-g64).  Rotating over L layers means every layer pass streams its experts from HBM:
+g64).  On one GPU every layer is ONE kernel launch (zmoe_layer_decode: router, top-k,
+gate/up + SwiGLU, down, combine) for T <= 8; larger T, mxfp4 and --no-fused take the
+separate kernels.  Rotating over L layers means every layer pass streams its experts from HBM:
 the bytes touched between two visits of the same layer exceed the 126 MB L2 several
 times over.  ``value`` = layer-tokens per second = T * L * n_gpus / step time, inputs
 resident in HBM; ``e2e`` is the same metric through the public Python call with the
@@ -11,7 +13,8 @@ token rows starting in pinned host memory and the result read back every step.
 Multi-GPU (--gpus N under torchrun): expert parallel.  Rank r owns E/N experts of every
 layer and brings its own T tokens; per layer the token rows are all-gathered, routed on
 every rank, the local experts run, and the per-slot rows are reduce-scattered back for the
-ordered combine (zmlx_b200/ep.py).  Per-GPU tokens are fixed as N grows (weak scaling);
+ordered combine (zmlx_b200/ep.py); the kernels between the two collectives are replayed from one
+CUDA graph per layer, the collectives and the combine are launched eagerly.  Per-GPU tokens are fixed as N grows (weak scaling);
 the step time is the max over ranks.  ``--replicas`` runs N independent copies instead.
 
 ``--impl reference`` times the CPU restatement of the reference's path (the compiled

@@ -187,6 +187,14 @@ int zmoe_moe_combine(const void* y, int y_dtype, const void* w, int w_dtype, int
                      void* out, int out_t, const void* residual, void* stream);
 
 /*
+ * Elementwise SwiGLU on T tensors: out[i] = silu(gate[i]) * up[i] under `swiglu_mode`.
+ * Replaces transformer.swiglu2 (src/zmlx/kernels/transformer.py:925-1005) and its GLM specialisation
+ * glm_fused_swiglu (src/zmlx/kernels/discovered/glm_fused_swiglu.py:65-90), which the patched block uses on its
+ * unfused path (src/zmlx/patch/patterns/moe_mlp.py:712-716); ZMOE_SWIGLU_PER_OP is their in-T arithmetic.
+ */
+int zmoe_swiglu(const void* gate, const void* up, long long n, int swiglu_mode, void* out, void* stream);
+
+/*
  * gather_qmm_combine_quantized: out[t] = sum_k gate[t,k] * T(act[t,k] @ W[idx[t,k]].T).
  * Replaces moe.py:2043-2174 (and the K-vectorised form moe.py:1198-1236).
  * act (T*K, Kin) T; plan built over rhs = idx (T*K pairs, lhs = identity);

@@ -71,6 +71,7 @@ SIGNATURES = {
                                 c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "zmoe_moe_combine": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p]),
+    "zmoe_swiglu": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]),
     "zmoe_gather_qmm_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                         c_int, c_void_p]),

@@ -2,7 +2,7 @@
 // contracts, plus the fused down-projection + combine entry point.
 #include <mutex>
 
-#include "common.cuh"
+#include "qmm_common.cuh"
 
 namespace zmoe {
 
@@ -108,6 +108,25 @@ int combine_launch(const void* y, int y_dtype, const void* w, int w_dtype, int T
   return check_launch(who);
 }
 
+// ---------------------------------------------------------------- elementwise SwiGLU
+// out = silu(gate) * up on T tensors of n elements (two per thread), under the rounding contracts of the fused
+// projection's epilogue.
+__global__ void __launch_bounds__(256) swiglu_kernel(const __nv_bfloat16* __restrict__ gate,
+                                                     const __nv_bfloat16* __restrict__ up, long long n, int mode,
+                                                     __nv_bfloat16* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i >= n) return;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (i + k < n) {
+      const float g = __bfloat162float(gate[i + k]), u = __bfloat162float(up[i + k]);
+      out[i + k] = __float2bfloat16_rn(mode == ZMOE_SWIGLU_CPU ? swiglu_cpu_contract(g, u) : swiglu_per_op(g, u));
+    }
+  }
+}
+
 // ---------------------------------------------------------------- allocation-free variant
 // Scratch for zmoe_gather_qmm_combine_noalloc: lives in the library image, one copy per GPU that
 // loads the library, for the life of the process.
@@ -148,6 +167,19 @@ extern "C" {
 int zmoe_moe_combine(const void* y, int y_dtype, const void* w, int w_dtype, int T, int K, int D, int mode,
                      void* out, int out_t, const void* residual, void* stream) {
   return combine_launch(y, y_dtype, w, w_dtype, T, K, D, mode, out, out_t, residual, stream, "zmoe_moe_combine");
+}
+
+int zmoe_swiglu(const void* gate, const void* up, long long n, int swiglu_mode, void* out, void* stream) {
+  ZMOE_REQUIRE(gate && up && out, ZMOE_ERR_SHAPE, "zmoe_swiglu: null pointer");
+  ZMOE_REQUIRE(n >= 0, ZMOE_ERR_SHAPE, "zmoe_swiglu: n=%lld", n);
+  ZMOE_REQUIRE(swiglu_mode == ZMOE_SWIGLU_CPU || swiglu_mode == ZMOE_SWIGLU_PER_OP, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_swiglu: swiglu_mode %d", swiglu_mode);
+  if (n == 0) return ZMOE_OK;
+  const long long blocks = (n + 511) / 512;
+  ZMOE_REQUIRE(blocks <= 0x7fffffffLL, ZMOE_ERR_UNSUPPORTED, "zmoe_swiglu: n=%lld is too large for one call", n);
+  launch_pdl(swiglu_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)gate,
+             (const __nv_bfloat16*)up, n, swiglu_mode, (__nv_bfloat16*)out);
+  return check_launch("zmoe_swiglu");
 }
 
 int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w_, const void* scales, const void* biases,

@@ -1,4 +1,4 @@
 """Hot-path kernels behind the reference's module names (``zmlx.kernels.moe``,
-``zmlx.kernels.fused_moe``)."""
+``zmlx.kernels.fused_moe``, ``zmlx.kernels.transformer.swiglu2``, ``zmlx.kernels.discovered``)."""
 
-from . import fused_moe, moe  # noqa: F401
+from . import discovered, fused_moe, moe, transformer  # noqa: F401

@@ -155,6 +155,22 @@ def combine(y: torch.Tensor, w: torch.Tensor, mode: int, *, out_t: bool = False,
     return out
 
 
+def swiglu(gate: torch.Tensor, up: torch.Tensor, *, mode: int = _lib.SWIGLU_PER_OP) -> torch.Tensor:
+    """Elementwise silu(gate) * up on bfloat16 tensors of the same shape (``zmoe_swiglu``)."""
+    dev = _need_cuda(gate, up)
+    if gate.shape != up.shape:
+        raise ValueError("swiglu2: gate and up must have the same shape")
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16:
+        raise TypeError(f"swiglu: gate and up must be bfloat16, got {gate.dtype} and {up.dtype}")
+    g, u = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(g)
+    if g.numel() == 0:
+        return out
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().zmoe_swiglu(_ptr(g), _ptr(u), g.numel(), int(mode), _ptr(out), _stream()))
+    return out
+
+
 def router_softmax_topk(logits: torch.Tensor, k: int, *, flavour: int, bias: torch.Tensor | None = None,
                         renorm: int = 0):
     dev = _need_cuda(logits, bias)
