@@ -49,3 +49,12 @@ def test_variant_agrees_with_the_default_kernels(env, name, T, mode):
     assert np.array_equal(np.asarray(rec["indices"]), idx)
     got = np.asarray(rec["out"], dtype=np.float32).reshape(want.shape)
     assert_close_rel(got, want, 2e-2, f"{name} T={T} {env}")
+
+
+def test_a_wait_that_runs_out_ends_the_launch_with_the_status_word_set():
+    """Failure detection without a GPU fault: with ZMOE_LD_TEST_WITHHOLD=1 one router logit is never published, so
+    every CTA's bounded wait for it runs out; the launch must end by itself (about a second), report it in the
+    workspace's status word and leave the CUDA context usable."""
+    rec = _child({"ZMOE_LD_TEST_WITHHOLD": "1"}, "c2", 1, "fused")
+    assert rec["status"] == 1
+    assert rec["context_usable"]

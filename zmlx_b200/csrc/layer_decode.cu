@@ -46,7 +46,7 @@ constexpr int kLdMaxTasks = kLdMaxRouted + 1;
 // a warp's share of an item is two quads anyway (d_ff < 2048), 4 for long rows, where one warp streams a whole
 // item and the bytes in flight per SM decide the bandwidth
 constexpr bool kLdBulkByDefault = false;  // the bulk-copy form of the one-token kernel
-constexpr int kLdSpinLimit = 1 << 21;  // polls of the barrier counter before a CTA gives up (~1 s)
+constexpr int kLdSpinLimit = 1 << 21;  // polls of a hand-over word or mbarrier before a CTA gives up (~1 s)
 
 struct LdBank {
   const uint32_t* w[2];
@@ -66,6 +66,7 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
+  int withhold;           // test hook: expert 0's logit is never published, so every wait for it runs out
   int pdl;                // regular launch with programmatic dependent launch instead of a cooperative one
   int tiles_per_cta;      // upper bound of the 16-column output tiles one CTA owns (sizes ybuf)
   int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
@@ -890,7 +891,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         const float sres = warp_sum(acc);
         // eight copies = one full 32-byte sector: L2 holds it whole and never has to merge it with a stale
         // copy from HBM when the other CTAs read it
-        if (lane < 8) st_relaxed_u32(p.logits + ((size_t)t * E + e) * 8 + lane, tag | float_to_bf16_bits(sres));
+        if (lane < 8 && !(p.withhold && e == 0))
+          st_relaxed_u32(p.logits + ((size_t)t * E + e) * 8 + lane, tag | float_to_bf16_bits(sres));
       }
     }
   }
@@ -1430,6 +1432,10 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   ZMOE_REQUIRE(L->launch_mode == 0 || L->launch_mode == 1, ZMOE_ERR_UNSUPPORTED,
                "zmoe_layer_decode: launch_mode %d", L->launch_mode);
   p.pdl = L->launch_mode;
+  // ZMOE_LD_TEST_WITHHOLD=1 (read once per process) makes the bounded waits run out on purpose: the kernel must
+  // end by itself with the status word set and leave the context usable
+  static const bool withhold = getenv("ZMOE_LD_TEST_WITHHOLD") != nullptr && atoi(getenv("ZMOE_LD_TEST_WITHHOLD")) != 0;
+  p.withhold = withhold ? 1 : 0;
   unsigned char* ws = (unsigned char*)workspace;
   p.sync = (int*)ws;
   p.logits = (uint32_t*)(ws + ld_ws_logits_off());
