@@ -44,6 +44,7 @@ class MoELayer:
         self.launch = launch
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
+        self._fused_ok: dict[int, bool] = {}  # token count -> whether the one-launch path covers this block
 
     # -- one-launch decode path ---------------------------------------------
     FUSED_MAX_TOKENS = 8
@@ -231,8 +232,12 @@ class MoELayer:
         if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
             x = x.contiguous()
         with torch.cuda.device(self.device):
-            if self.fused and (T in self._fused_ws or self.fused_workspace_bytes(T) > 0):
-                return self.forward_fused(x)
+            if self.fused:
+                ok = self._fused_ok.get(T)
+                if ok is None:
+                    ok = self._fused_ok[T] = self.fused_workspace_bytes(T) > 0
+                if ok:
+                    return self.forward_fused(x)
             self.route(x)
             self.experts(x)
             residual = None
