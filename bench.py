@@ -395,8 +395,8 @@ def main() -> None:
 
     if rank == 0:
         peak, peak_kind = _peaks()
-        # DRAM bytes per launch of the one-launch block at the default workload, from the ncu capture summarised in
-        # profiles/layer_decode_c2_T1_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum, mean of 4 launches)
+        # DRAM bytes per launch of the one-launch block at the default workload: mean of four launches in an ncu
+        # capture of this command at four layers (dram__bytes_read.sum + dram__bytes_write.sum)
         traffic = 21.874e6 if (one_launch and cfg.name.startswith("c2") and T == 1) else None
         achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
         line = {
@@ -420,7 +420,7 @@ def main() -> None:
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
                                   "whole block in one cooperative launch (zmoe_layer_decode)" if one_launch else
-                                  "whole layer pass (4 kernels); per-kernel figures in profiles/")},
+                                  "whole layer pass (4 kernels)")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
                     "d2h_bytes_per_step": T * cfg.d_model * 2},
             "gpu_launches": launches_per_layer * L * args.steps,

@@ -1,6 +1,6 @@
 """Expert-parallel MoE layer across the GPUs of one node (one process per GPU, NCCL).
 
-The reference has no distributed code at all (SURVEY: no collectives anywhere in the tree); this is the sharding
+The reference has no distributed code at all (no collectives anywhere in its tree); this is the sharding
 its operator surface allows: experts are independent, so rank r owns experts [r*E/R, (r+1)*E/R) and the router
 weight and shared experts are replicated.  Every rank brings its own T decode tokens (data-parallel attention
 side); one layer pass is
