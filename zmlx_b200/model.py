@@ -9,7 +9,8 @@ is plain torch ops -- float32 score/softmax arithmetic, so that a CPU restatemen
 the libzmoe kernels.  Weights are random-init: no checkpoint is involved.
 
 Command line: ``python -m zmlx_b200.model --layers 48 --prompt 4096 --new 256 --batch 1`` prints
-prefill and decode rates as one JSON line.
+prefill and decode rates as one JSON line; under ``python -m torch.distributed.run --nproc-per-node N`` the MoE
+blocks run expert-parallel over the N GPUs (every rank decodes its own batch, here the same prompt).
 """
 
 from __future__ import annotations
@@ -306,10 +307,20 @@ def _main() -> None:
         cfg = replace(cfg, n_layers=args.layers)
     if args.vocab:
         cfg = replace(cfg, vocab=args.vocab)
-    dev = torch.device("cuda", 0)
-    params = make_decoder_params(cfg, device=dev)
+    import os
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:  # under torch.distributed.run: expert-parallel MoE blocks, every rank its own sequences
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    params = make_decoder_params(cfg, device=dev)  # same seeds on every rank: one model
     model = StackedDecoder(cfg, params, max_batch=args.batch, max_seq=args.prompt + args.new,
-                           fused=not args.no_fused)
+                           fused=not args.no_fused, world=world, rank=rank)
     g = torch.Generator(device="cpu")
     g.manual_seed(5)
     prompt = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=g).to(dev)
@@ -326,15 +337,22 @@ def _main() -> None:
         torch.cuda.synchronize()
         ev0, ev1, steps = model.last_decode
         decode_s = ev0.elapsed_time(ev1) * 1e-3
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return
     print(json.dumps({
-        "model": cfg.name, "layers": cfg.n_layers, "batch": args.batch, "prompt": args.prompt, "new": args.new,
+        "model": cfg.name, "n_gpus": world, "layers": cfg.n_layers, "batch": args.batch, "prompt": args.prompt, "new": args.new,
         "one_launch_block": not args.no_fused,
         "prefill_tokens_per_s": args.batch * args.prompt / (t1 - t0),
         "cuda_graph_decode": not args.no_graph,
         "decode_tokens_per_s": args.batch * steps / max(decode_s, 1e-9),
         "decode_ms_per_step": 1e3 * decode_s / max(steps, 1),
         "decode_steps_timed": steps,
-        "first_tokens": toks[0, :8].tolist(),
+        "first_tokens": toks[0, :16].tolist(),
     }))
 
 
