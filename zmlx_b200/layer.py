@@ -45,6 +45,7 @@ class MoELayer:
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
         self._fused_ok: dict[int, bool] = {}  # token count -> whether the one-launch path covers this block
+        self._shared_plans: dict[int, torch.Tensor] = {}  # token count -> the shared expert's (constant) plan
 
     # -- one-launch decode path ---------------------------------------------
     FUSED_MAX_TOKENS = 8
@@ -209,13 +210,21 @@ class MoELayer:
         qm = ops.qmode_code(cfg.mode)
         S = self.p["shared"]
         f = cfg.d_ff * cfg.n_shared
-        _lib.check(lib.zmoe_build_plan(None, 1, p(self.zero_idx), T, 1, 1, p(self.shared_plan),
-                                       self.shared_plan.numel() * 4, st))
+        # the shared expert's plan depends on the token count only (row t -> expert 0): built once per count and
+        # kept, unless this call is being captured in a CUDA graph (a captured launch does not run now)
+        plan = self._shared_plans.get(T)
+        if plan is None:
+            capturing = torch.cuda.is_current_stream_capturing()
+            plan = self.shared_plan if capturing else torch.empty(ops.plan_bytes(T, 1) // 4, dtype=torch.int32,
+                                                                  device=self.device)
+            _lib.check(lib.zmoe_build_plan(None, 1, p(self.zero_idx), T, 1, 1, p(plan), plan.numel() * 4, st))
+            if not capturing:
+                self._shared_plans[T] = plan
         _lib.check(lib.zmoe_gather_qmm_swiglu(p(x), T, x.stride(0), p(S["gate_w"]), p(S["gate_s"]), p(S["gate_b"]),
                                               p(S["up_w"]), p(S["up_s"]), p(S["up_b"]), 1, f, cfg.d_model, self.gs,
-                                              qm, p(self.shared_plan), T, T, p(self.sh_h), _lib.SWIGLU_PER_OP, st))
+                                              qm, p(plan), T, T, p(self.sh_h), _lib.SWIGLU_PER_OP, st))
         _lib.check(lib.zmoe_gather_qmm(p(self.sh_h), T, f, p(S["down_w"]), p(S["down_s"]), p(S["down_b"]), 1,
-                                       cfg.d_model, f, self.gs, qm, p(self.shared_plan), T, T, 1, p(self.sh_y), st))
+                                       cfg.d_model, f, self.gs, qm, p(plan), T, T, 1, p(self.sh_y), st))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x (T, d_model) bfloat16 on this layer's device -> (T, d_model) bfloat16 (a view of an owned buffer)."""
