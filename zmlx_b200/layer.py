@@ -45,6 +45,7 @@ class MoELayer:
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
         self._fused_ok: dict[int, bool] = {}  # token count -> whether the one-launch path covers this block
+        self._side: torch.cuda.Stream | None = None  # second stream for the shared expert (separate-kernel path)
         self._shared_plans: dict[int, torch.Tensor] = {}  # token count -> the shared expert's (constant) plan
 
     # -- one-launch decode path ---------------------------------------------
@@ -247,12 +248,21 @@ class MoELayer:
                     ok = self._fused_ok[T] = self.fused_workspace_bytes(T) > 0
                 if ok:
                     return self.forward_fused(x)
-            self.route(x)
-            self.experts(x)
             residual = None
             if cfg.n_shared:
-                self.shared(x)
+                # the shared expert depends on x only: it runs on a side stream beside the router and the routed
+                # experts and joins before the combine (fork and join are events, so a CUDA graph captures them)
+                cur = torch.cuda.current_stream(self.device)
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=self.device)
+                self._side.wait_stream(cur)
+                with torch.cuda.stream(self._side):
+                    self.shared(x)
                 residual = self.sh_y
+            self.route(x)
+            self.experts(x)
+            if cfg.n_shared:
+                cur.wait_stream(self._side)
             _lib.check(_lib.load().zmoe_moe_combine(
                 ops._ptr(self.y), _lib.BF16, ops._ptr(self.weights), _lib.F32, T, cfg.top_k, cfg.d_model,
                 self.combine_mode, ops._ptr(self.out), 3 if cfg.family == "generic" else 1, ops._ptr(residual),
