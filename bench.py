@@ -1,24 +1,25 @@
 """MoE-layer decode benchmark (one JSON line on stdout).
 
-A *step* is one batch of T decode tokens passing through L stacked MoE layers with
-distinct weights (the Qwen3-30B-A3B-shaped layer, 128 experts, top-8, 4-bit affine
-g64).  On one GPU every layer is ONE kernel launch (zmoe_layer_decode: router, top-k,
-gate/up + SwiGLU, down, combine) for T <= 8; larger T, mxfp4 and --no-fused take the
-separate kernels.  Rotating over L layers means every layer pass streams its experts from HBM:
-the bytes touched between two visits of the same layer exceed the 126 MB L2 several
-times over.  ``value`` = layer-tokens per second = T * L * n_gpus / step time, inputs
-resident in HBM; ``e2e`` is the same metric through the public Python call with the
-token rows starting in pinned host memory and the result read back every step.
+A *step* is one batch of T decode tokens passing through L stacked MoE layers with distinct
+weights.  The default workload is the DeepSeek-V3-shaped layer (d_model 7168, 256 experts + one
+shared, top-8 with group-limited sigmoid routing, d_ff 2048, 4-bit affine g64: 227 MB of active
+weights per token) at T = 1 through L = 6 layers -- the largest configuration that fits one GPU and
+the one where bytes, not latency, decide; ``--config c2`` is the Qwen3-30B-A3B-shaped layer (22 MB
+per token, L = 24).  On one GPU every layer is ONE kernel launch (zmoe_layer_decode: router, top-k,
+gate/up + SwiGLU, down, combine, shared expert) where the block's shape allows it; larger T, mxfp4
+and --no-fused take the separate kernels.  Rotating over L layers means every layer pass streams
+its experts from HBM: the bytes touched between two visits of the same layer exceed the 126 MB L2
+many times over.  ``value`` = layer-tokens per second = T * L * n_gpus / step time (median of
+``--repeats`` timed loops of ``--steps`` steps), inputs resident in HBM; ``e2e`` is the same metric
+through the public Python call with the token rows starting in pinned host memory and the result
+read back every step.
 
-Multi-GPU (--gpus N under torchrun): expert parallel.  Rank r owns E/N experts of every
-layer and brings its own T tokens; per layer the token rows are all-gathered, routed on
-every rank, the local experts run, and the per-slot rows are reduce-scattered back for the
-ordered combine (zmlx_b200/ep.py); the kernels between the two collectives are replayed from one
-CUDA graph per layer, the collectives and the combine are launched eagerly.  Per-GPU tokens are fixed as N grows (weak scaling);
-the step time is the max over ranks.  ``--replicas`` runs N independent copies instead.
+Multi-GPU (--gpus N under torchrun): expert parallel.  Rank r owns E/N experts of every layer and
+brings its own T tokens (zmlx_b200/ep.py).  Per-GPU tokens are fixed as N grows (weak scaling); the
+step time is the max over ranks.  ``--replicas`` runs N independent copies instead.
 
-``--impl reference`` times the CPU restatement of the reference's path (the compiled
-oracle, all host threads) on a bounded sample of the same workload.
+``--impl reference`` times the CPU restatement of the reference's path (the compiled oracle, all
+host threads) on a bounded sample of the same workload.
 """
 
 from __future__ import annotations
@@ -45,9 +46,14 @@ def _args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="zmoe", choices=["zmoe", "reference"])
-    ap.add_argument("--config", default="c2")
+    ap.add_argument("--config", default="c5")
     ap.add_argument("--tokens", type=int, default=1)
-    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--layers", type=int, default=0, help="stacked layers per step (default: 6 for c5, else 24)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed loops of --steps steps; the median is reported")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="trim the routed bank to this many experts (profiling captures on a small footprint)")
+    ap.add_argument("--via-patch", action="store_true",
+                    help="drive the blocks as nn modules patched by zmlx_b200.patch.patch() instead of MoELayer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--launch", default="pdl", choices=["pdl", "cooperative"],
@@ -61,6 +67,19 @@ def _args():
                          "replaying them from one CUDA graph per layer")
     ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
+
+
+# DRAM bytes per launch of the one-launch block measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum),
+# as a ratio to the algorithmic bytes of the captured launches; the summaries that hold the figures are named.
+_TRAFFIC_RATIO = {}
+
+
+def _measured_traffic(cfg, T, one_launch, alg_bytes_per_launch):
+    rec = _TRAFFIC_RATIO.get((cfg.config_id, T)) if one_launch else None
+    if rec is None:
+        return None, None
+    ratio, source = rec
+    return ratio * alg_bytes_per_launch, source
 
 
 def _peaks():
@@ -149,7 +168,8 @@ class ClockSampler:
 
 def _cpu_baseline(cfg, tokens: int, budget_s: float = 12.0):
     """Time the compiled oracle (a port of the reference's CPU arithmetic) on a bounded sample:
-    whole layer passes of the same shape, repeated until ~budget_s of CPU work."""
+    whole layer passes of the same shape (router, routed experts, combine, shared expert), repeated
+    until ~budget_s of CPU work.  All host threads."""
     import numpy as np
     import torch
 
@@ -157,32 +177,50 @@ def _cpu_baseline(cfg, tokens: int, budget_s: float = 12.0):
     from oracle import semantics as S
     from zmlx_b200 import synthetic
 
-    small = cfg.scaled(n_experts=max(cfg.top_k * 2, 16))  # expert bank trimmed: routing still picks top_k distinct
+    F.set_num_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1: choose the count here
+    groups = max(cfg.n_group, 1)
+    keep = max(cfg.top_k * 2, 16)
+    keep = ((keep + groups - 1) // groups) * groups
+    small = cfg.scaled(n_experts=min(cfg.n_experts, keep))  # bank trimmed: routing still picks top_k distinct
     p = synthetic.make_layer(small, device="cpu")
 
     def n(t):
         if t is None:
             return None
+        if isinstance(t, dict):
+            return {k: n(v) for k, v in t.items()}
         if t.dtype == torch.bfloat16:
             return t.float().numpy()
         if t.dtype == torch.uint32:
             return t.view(torch.int32).numpy().view(np.uint32)
         return t.numpy()
 
-    pn = {k: n(v) for k, v in p.items() if k != "shared"}
+    pn = {k: n(v) for k, v in p.items()}
     x = n(synthetic.make_tokens(small, tokens))
     rw = pn["router_w"]
+    gs = 32 if small.mode == "mxfp4" else small.group_size
+    sw = "cpu" if small.mode == "affine" else "per_op"
+    zero_idx = np.zeros((tokens, 1), dtype=np.int32)
 
     def one_pass():
         logits = S.bf16(x @ rw.T)
         if small.family == "qwen3":
             idx, w = S.qwen3_gating(logits, small.top_k)
             mode = "no_fma"
-        else:
+        elif small.family == "generic":
             w, idx = S.topk_gating_softmax(logits, small.top_k)
-            mode = "t"
-        y, _ = F.experts_forward(x, idx.astype(np.int32), pn, group_size=small.group_size, mode=small.mode)
-        return S.moe_combine(y, w, mode=mode)
+            w, mode = S.bf16(w), "t"
+        else:
+            w, idx = S.deepseek_router_topk_sigmoid(logits, pn["expert_bias"], k=small.top_k, n_group=small.n_group,
+                                                    topk_group=min(small.topk_group, small.n_group))
+            w = (w * np.float32(small.routed_scaling_factor)).astype(np.float32)
+            mode = "fp32_no_fma" if small.family == "glm" else "t"
+        y, _ = F.experts_forward(x, idx.astype(np.int32), pn, group_size=gs, mode=small.mode, swiglu=sw)
+        out = S.moe_combine(y, w, mode=mode)
+        if small.n_shared:
+            ys, _ = F.experts_forward(x, zero_idx, pn["shared"], group_size=gs, mode=small.mode, swiglu="per_op")
+            out = S.bf16(S.bf16(out) + ys[:, 0, :])
+        return out
 
     one_pass()
     t0 = time.perf_counter()
@@ -193,9 +231,13 @@ def _cpu_baseline(cfg, tokens: int, budget_s: float = 12.0):
         dt = time.perf_counter() - t0
         if dt > budget_s or reps >= 2000:
             break
+    nbytes = small.algorithmic_bytes(min(small.top_k * tokens, small.n_experts), tokens)
     return {"value": tokens * reps / dt, "unit": UNIT, "cores": F.num_threads(), "kind": "port",
+            "achieved_gbs": nbytes * reps / dt / 1e9,
             "sample": f"{reps} passes of one {cfg.name}-shaped layer (expert bank trimmed to {small.n_experts}, "
-                      f"top-{small.top_k} active) at T={tokens}, compiled oracle with OpenMP, {dt:.1f} s"}
+                      f"top-{small.top_k} active" + (", one shared expert" if small.n_shared else "") +
+                      f") at T={tokens}, compiled oracle with OpenMP on {F.num_threads()} threads, {dt:.1f} s; "
+                      "a reported baseline, not a target: see roofline.frac for kernel quality"}
 
 
 def run_reference(args) -> None:
@@ -205,6 +247,8 @@ def run_reference(args) -> None:
     from zmlx_b200 import synthetic
 
     cfg = synthetic.CONFIGS[args.config]
+    if args.experts:
+        cfg = cfg.scaled(n_experts=args.experts)
     t0 = time.perf_counter()
     # steps/warmup are honoured as repetitions of a bounded sample
     base = _cpu_baseline(cfg, args.tokens, budget_s=min(20.0, 0.4 * max(args.steps, 1)))
@@ -245,6 +289,10 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
 
     cfg = synthetic.CONFIGS[args.config]
+    if args.experts:
+        cfg = cfg.scaled(n_experts=args.experts)
+    if args.layers <= 0:
+        args.layers = 6 if cfg.config_id == 5 else 24
     T, L = args.tokens, args.layers
     use_ep = world > 1 and not args.replicas
     if use_ep:
@@ -349,22 +397,26 @@ def main() -> None:
         for _ in range(max(args.warmup, 3)):
             run_step()
     barrier()
-    ev0 = torch.cuda.Event(enable_timing=True)
-    ev1 = torch.cuda.Event(enable_timing=True)
     clocks = ClockSampler(local)  # samples over both timed regions (device-timed steps, then end to end)
     clocks.__enter__()
-    with torch.cuda.stream(stream):
-        ev0.record(stream)
-        for _ in range(args.steps):
-            run_step()
-        ev1.record(stream)
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+    per_repeat = []
+    for _ in range(max(args.repeats, 1)):
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev1 = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+            for _ in range(args.steps):
+                run_step()
+            ev1.record(stream)
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        per_repeat.append(ms / args.steps)
+    ordered = sorted(per_repeat)
+    ms_per_step = ordered[len(ordered) // 2]
     value = T * L * world / (ms_per_step * 1e-3)
 
     # --- end to end: pinned host rows in, result read back, every step
@@ -392,16 +444,20 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = T * L * world / (e2e_ms / args.steps * 1e-3)
+    # a bounded wait that ran out anywhere in the timed launches voids the numbers: fail loudly
+    with torch.cuda.stream(stream):
+        for ly in layers:
+            getattr(ly, "check_status", lambda: None)()
 
     if rank == 0:
         peak, peak_kind = _peaks()
-        # DRAM bytes per launch of the one-launch block at the default workload: mean of four launches in an ncu
-        # capture of this command at four layers (dram__bytes_read.sum + dram__bytes_write.sum)
-        traffic = 21.874e6 if (one_launch and cfg.name.startswith("c2") and T == 1) else None
+        traffic, traffic_source = _measured_traffic(cfg, T, one_launch, alg_bytes_step / L)
         achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "ms_per_step_repeats": {"n": len(per_repeat), "min": ordered[0], "median": ms_per_step, "max": ordered[-1]},
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{cfg.name}: d_model={cfg.d_model}, {cfg.n_experts} experts, top-{cfg.top_k}, "
                                    f"d_ff={cfg.d_ff}, {cfg.mode} 4-bit; T={T} decode tokens per step through "
@@ -415,7 +471,8 @@ def main() -> None:
                                        + ("; kernels between the collectives replayed from per-layer CUDA graphs"
                                           if args.ep_segments else "")) if use_ep else f"replicas x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                         "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
+                         "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_launch": (alg_bytes_step / L) if one_launch else None,
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define ZMOE_ABI_VERSION 1
+#define ZMOE_ABI_VERSION 2
 
 enum zmoe_status {
   ZMOE_OK = 0,
@@ -263,22 +263,34 @@ typedef struct zmoe_layer_desc {
   const float* router_bias; /* (E) or NULL */
   zmoe_expert_bank routed;
   zmoe_expert_bank shared;  /* ignored when n_shared == 0 */
+  int32_t debug_flags;      /* 0 in production; ZMOE_DEBUG_* bits are test hooks */
+  int32_t reserved;
+  void* debug_stamps;       /* NULL in production; else 16 int64 of device memory: CTA 0 records its cycle
+                               counter at the phase boundaries (token staging, router linear, logits received,
+                               top-k, task list, gate/up done, h staged, down done, combine done) */
 } zmoe_layer_desc;
+
+/* debug_flags bit: expert 0's router logit is never published, so that every CTA's bounded wait for it runs
+   out -- the launch must end by itself with the status word set (failure detection without a GPU fault). */
+#define ZMOE_DEBUG_WITHHOLD_LOGIT 1
 
 /*
  * The whole patched block forward for a few decode tokens (src/zmlx/patch/patterns/moe_mlp.py:883-1063:
- * gate -> experts -> combine -> + shared_experts(x)) in ONE cooperative launch: router linear, the family's
+ * gate -> experts -> combine -> + shared_experts(x)) in ONE launch: router linear, the family's
  * top-k, gather_qmm_swiglu, the down projection, the ordered combine and the shared expert.  Same
  * arithmetic contracts as the separate entry points above.  Covers 4-bit affine weights with group
- * size 64, 1..8 tokens, top_k <= 8, E <= 256, d_model and d_ff multiples of 256; other shapes fail with
+ * size 64, 1..8 tokens, top_k <= 8, E <= 256, d_model and d_ff multiples of 256, packed weights 16-byte
+ * aligned, as long as the token rows fit in shared memory beside the weight stages; other shapes fail with
  * ZMOE_ERR_UNSUPPORTED (zmoe_layer_decode_workspace_bytes returns 0 for them) and take the separate calls.
+ * Both functions need the CUDA device of the call to be current (sizes depend on its SM count).
  *
  * workspace: zmoe_layer_decode_workspace_bytes(L, T) bytes, 256-byte aligned, ALL ZERO before the first
  * call, then left to the library and used with the same T (zero it again before changing T).  It starts
- * with five ints {-, -, sign-in count, status, launch count}.  CTAs hand the router logits and the
- * activated rows to each other through the workspace as tagged 32-bit words and re-read a word until it
- * carries the current launch's tag; every such wait is bounded, and one that runs out sets status to 1
- * and ends the launch with `out` undefined.  One workspace serves one stream at a time.
+ * with five ints {-, -, sign-in count, status, launch count}.  CTAs hand the router logits, the activated
+ * rows and the projected rows to each other through the workspace as tagged 32-bit words and re-read a word
+ * until it carries the current launch's tag; every such wait is bounded, and one that runs out sets status
+ * to 1 and ends the launch with `out` undefined (read it with zmoe_layer_decode_status).  One workspace
+ * serves one stream at a time.
  * x (T, d_model) T with row stride ldx; out (T, d_model) T (float for the FP32 combine modes without
  * out_flags bit 0); weights (T, top_k) float and indices (T, top_k) uint32 receive the routing when not
  * NULL.
@@ -286,6 +298,15 @@ typedef struct zmoe_layer_desc {
 size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T);
 int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
                       size_t workspace_bytes, float* weights, uint32_t* indices, void* out, void* stream);
+
+/*
+ * Status of the launches that have used `workspace`: copies the status word to the host on `stream` and WAITS
+ * for the stream (the one call of this library that synchronises; make it where the caller synchronises
+ * anyway, e.g. when it reads the block's output).  Returns ZMOE_OK, or ZMOE_ERR_TIMEOUT when a bounded wait
+ * ran out in some launch since the word was last cleared; with clear != 0 the word is zeroed again on
+ * `stream`.  No reference counterpart (the reference has no cross-CTA waits).
+ */
+int zmoe_layer_decode_status(const void* workspace, int clear, void* stream);
 
 #ifdef __cplusplus
 }

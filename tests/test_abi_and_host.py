@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/zmoe.h but not exported"
         assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
-    assert lib.zmoe_abi_version() == 1
+    assert lib.zmoe_abi_version() == _lib.ABI_VERSION
 
 
 def test_argument_errors_do_not_touch_the_gpu():

@@ -11,10 +11,12 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# ZMOE_LIB selects another build of the same ABI (e.g. one compiled with -DZMOE_LD_TIMING)
+# ZMOE_LIB selects another build of the same ABI
 LIB_PATH = os.environ.get("ZMOE_LIB") or os.path.join(_HERE, "libzmoe.so")
 
 OK = 0
+ABI_VERSION = 2
+DEBUG_WITHHOLD_LOGIT = 1
 ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 Q_AFFINE4, Q_MXFP4 = 0, 1
@@ -48,7 +50,8 @@ class LayerDesc(ctypes.Structure):
                 + [("routed_scale", c_float)]
                 + [(n, ctypes.c_int32) for n in ("n_shared", "swiglu_mode", "shared_swiglu_mode", "combine_mode",
                                                  "out_flags", "launch_mode")]
-                + [("router_w", c_void_p), ("router_bias", c_void_p), ("routed", ExpertBank), ("shared", ExpertBank)])
+                + [("router_w", c_void_p), ("router_bias", c_void_p), ("routed", ExpertBank), ("shared", ExpertBank)]
+                + [("debug_flags", ctypes.c_int32), ("reserved", ctypes.c_int32), ("debug_stamps", c_void_p)])
 
 
 # name -> (restype, argtypes); must list every symbol include/zmoe.h declares.
@@ -81,6 +84,7 @@ SIGNATURES = {
     "zmoe_layer_decode_workspace_bytes": (c_size_t, [ctypes.POINTER(LayerDesc), c_int]),
     "zmoe_layer_decode": (c_int, [ctypes.POINTER(LayerDesc), c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p,
                                   c_void_p, c_void_p, c_void_p]),
+    "zmoe_layer_decode_status": (c_int, [c_void_p, c_int, c_void_p]),
 }
 
 
@@ -110,7 +114,7 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
-        if lib.zmoe_abi_version() != 1:
+        if lib.zmoe_abi_version() != ABI_VERSION:
             raise RuntimeError("libzmoe.so ABI version mismatch; rebuild it")
         _lib = lib
     return _lib

@@ -1,52 +1,56 @@
-// One MoE block for a handful of decode tokens in ONE launch: router linear, top-k,
-// fused gate/up + SwiGLU, down projection, ordered weighted combine, shared expert.
+// One MoE block for a handful of decode tokens in ONE launch: router linear, top-k, fused gate/up + SwiGLU,
+// down projection, ordered weighted combine, shared expert.
 //
-// The separate-kernel path pays four dependent launches per block; at one token each of
-// them is a few microseconds of launch and pipeline-fill latency around ~1 us of memory
-// traffic.  Here a persistent grid of one 512-thread CTA per SM (cooperative launch, so
-// every CTA is resident) walks three phases.  There is no grid-wide barrier: what one CTA
-// produces for the others travels as tagged 32-bit "hand-over words" that a consumer
-// re-reads until they carry the current launch's tag.
+// A persistent grid of one CTA per SM.  Each CTA is 16 consumer warps (four teams of four) plus one PRODUCER
+// warp that does nothing but issue asynchronous copies (cp.async) of packed expert weights into a ring of shared-memory
+// stages (one mbarrier pair per stage).  The producer runs ahead of the math: it starts with the shared
+// expert's first tiles before the routing is known, follows the routed gate/up tiles with the down-projection
+// tiles without a pause, and so keeps >100 KB per SM in flight across every phase boundary.  There is no
+// grid-wide barrier: what one CTA produces for the others travels as tagged 32-bit "hand-over words" that a
+// consumer re-reads until they carry the current launch's tag.
 //
-//   phase 1  every CTA stages the T token rows in shared memory (they feed every gate/up
-//            tile); the router linear runs one warp per expert row across the whole grid
-//            and publishes each logit as a hand-over word;
-//   phase 2  every CTA waits for the logits and repeats the top-k of the T rows (cheap,
-//            and it spares a second exchange), derives the task list (distinct experts and
-//            their rows) in shared memory; gate/up + SwiGLU tiles (task, 16 rows) are dealt
-//            to groups of four warps across the grid; h rows are published as hand-over
-//            words.  Each warp then already streams the first packed down-projection
-//            weights: they depend on the routing only;
-//   phase 3  every CTA waits for and stages all h rows, owns 16 output columns at a time,
-//            computes them for every task (warps split tasks and K) and combines the K slots
-//            of each token in slot order under the requested rounding contract.
+//   routing   the router linear is spread over the grid (one expert row per CTA at a time, its 16 warps take
+//             one segment of the row each); logits are published as hand-over words; every CTA waits for
+//             them and repeats the top-k of the T rows (cheap, and it spares a second exchange);
+//   gate/up   items (task, 16 weight rows of gate and of up) are dealt round-robin over the grid, the shared
+//             expert's first; a team owns an item, its four warps split K; h = SwiGLU is published as
+//             hand-over words;
+//   down      items (task, 32 output columns) are cut into contiguous, equally long ranges per CTA (so a CTA
+//             needs the h rows of one or two tasks only); projected rows y are published as hand-over words;
+//   combine   64 output elements per half-warp pair anywhere in the grid: wait for the K (+ shared) words of
+//             an element, combine them in slot order under the block's rounding contract.
 //
-// The matmul core is the one of qmm.cu: packed codes go from HBM to registers with 8-byte
-// streaming loads (for one token an opt-in variant brings them to shared memory with
-// cp.async.bulk instead), become bf16 (128 + q) with a shift and a lop3, and meet the token
-// rows on the tensor cores (mma.sync m16n8k16, weights are the A operand); scale, bias and
-// the 128 offset are applied per group in fp32; spare mma columns carry other groups
-// (column multiplexing).  Every wait on another CTA is bounded: when the limit is hit the
-// CTA records it in the status word and leaves.
-#include <cstdlib>
+// The matmul core: a stage holds 32 row segments of up to 512 bytes (16 groups of 64 codes).  A lane reads
+// 8 bytes of rows g and g+8 and turns each packed word into four half2 operands with four lop3 and ONE shift:
+//     (w & 0x000F000F) | 0x64006400 = (1024 + q0, 1024 + q4)        (w & 0x00F000F0) | 0x64006400 =
+//     (1024 + 16 q1, 1024 + 16 q5), and the same on w >> 8 for q2, q6, q3, q7
+// (fp16 has ten mantissa bits, so a code at bit 4 still lands inside the mantissa of 1024).  The token rows are
+// staged in shared memory as fp16 in the matching order, the odd positions pre-divided by 16, after a
+// per-row power-of-two scale that puts the row maximum in [2^14, 2^15) (exact for every element within 2^-24
+// of the maximum; bf16 has 8 significant bits, fp16 11).  Products are exact, accumulation is fp32
+// (mma.sync m16n8k16).  The 1024 offsets, the group scale and the group bias are applied per group in fp32:
+//     sum_k x_k (q_k s + b) = s * (D - C) + b * X,   D = the mma sum, C = 1024 sum_even x + 64 sum_odd x, X = sum x.
+// Spare mma columns carry other groups (column multiplexing, see qmm.cu).  Scales and biases are read straight
+// from L1/L2 into registers one block of groups ahead.
+//
+// Every wait on another warp, CTA or copy is bounded: when the limit is hit the warp records it in the status
+// word and leaves; the producer then waits (bounded) for its copies in flight before the CTA ends.
+#include <cuda_fp16.h>
+
 #include <mutex>
 
+#include "layer_route.cuh"
 #include "qmm_common.cuh"
-#include "router_rows.cuh"
 
 namespace zmoe {
 
-constexpr int kLdThreads = 512;
-constexpr int kLdWarps = kLdThreads / 32;
-constexpr int kLdMaxT = 8;
-constexpr int kLdMaxK = 8;
-constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;      // (token, slot) rows
-constexpr int kLdMaxTasks = kLdMaxRouted + 1;
-// DPD (kernel template parameter): quads of packed weights a warp keeps in flight in the down projection: 2 when
-// a warp's share of an item is two quads anyway (d_ff < 2048), 4 for long rows, where one warp streams a whole
-// item and the bytes in flight per SM decide the bandwidth
-constexpr bool kLdBulkByDefault = false;  // the bulk-copy form of the one-token kernel
-constexpr int kLdSpinLimit = 1 << 21;  // polls of a hand-over word or mbarrier before a CTA gives up (~1 s)
+constexpr int kLdTeams = 4;                          // teams of consumer warps; a team owns one item at a time
+constexpr int kLdSegBytes = 512;                     // bytes of one weight row in one stage
+constexpr int kLdSegStride = kLdSegBytes + 32;       // == 32 mod 128: the 8-byte fragment reads of a warp hit all banks once
+constexpr int kLdSlotBytes = 32 * kLdSegStride;      // one stage: 32 row segments
+constexpr int kLdMaxDepth = 6;                       // stages per team at most
+constexpr int kLdSmemLimit = 227 * 1024;
+constexpr int kLdMaxMine = 4;                        // router rows per CTA at most (E <= 4 * grid)
 
 struct LdBank {
   const uint32_t* w[2];
@@ -66,121 +70,172 @@ struct LdParams {
   int n_shared;
   int epi, sepi;  // SwiGLU contract of routed / shared experts (1: CPU contract, 2: per-op)
   int combine_mode, out_flags;
-  int withhold;           // test hook: expert 0's logit is never published, so every wait for it runs out
-  int pdl;                // regular launch with programmatic dependent launch instead of a cooperative one
-  int tiles_per_cta;      // upper bound of the 16-column output tiles one CTA owns (sizes ybuf)
-  int bulk_off, g_slots;  // bulk-copy variant: byte offset of its shared-memory region, gate/up slots per CTA
+  int withhold;  // test hook: expert 0's logit is never published, so every wait for it runs out
+  int pdl;       // regular launch with programmatic dependent launch instead of a cooperative one
+  int hrows;     // h rows a CTA stages at most for its share of the down projection
+  int slots;     // ring stages of a CTA (dealt to the four teams)
   int* sync;         // {-, -, sign-in count, status, launch count}
   uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
   uint32_t* h;       // (rows, f) hand-over words
+  uint32_t* y;       // (rows, d) hand-over words
   float* weights;
   uint32_t* indices;
   void* out;
+  long long* stamps;  // debug: CTA 0 records its cycle counter at the phase boundaries (NULL: off)
 };
 
 struct LdMeta {
-  int n_tasks, n_routed;
+  int n_tasks, n_routed, n_h;
   int idx[kLdMaxRouted];
   float w[kLdMaxRouted];
   int rank[kLdMaxRouted];
   int task_expert[kLdMaxTasks];
   int task_cnt[kLdMaxTasks];
   unsigned char task_rows[kLdMaxTasks][kLdMaxT];
+  unsigned char hlist[kLdMaxRouted + kLdMaxT];  // staged h row -> row of the (rows, f) buffer
+  unsigned char hloc[kLdMaxRouted + kLdMaxT];   // and back
 };
 
 struct LdSmem {
-  int xs, xsum, sc, red, ybuf, route, meta, zero, total;
+  int xs, xsum, isig, rowmax, route, meta, red, flags, bars, zero, ring, total;
 };
 
 __host__ __device__ inline int ld_align16(int a) { return (a + 15) & ~15; }
 
-__host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int n_shared, int tiles_per_cta) {
+// Shared-memory carve-up, identical on host and device.  hrows and slots come from the host (ld_plan).
+__host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int hrows, int slots) {
   LdSmem m;
-  const int rtot = T * K + (n_shared ? T : 0);
   const int ngd = d / 64, ngf = f / 64;
   int a = 0;
-  m.xs = a;
-  const int xs1 = T * qmm_xs_stride(d), xs2 = rtot * qmm_xs_stride(f);
+  m.xs = a;  // token rows (gate/up), later the staged h rows (down): fp16, fragment order
+  const int xs1 = T * qmm_xs_stride(d), xs2 = hrows * qmm_xs_stride(f);
   a += ld_align16(xs1 > xs2 ? xs1 : xs2);
-  m.xsum = a;
-  const int su1 = ngd * T, su2 = ngf * rtot;
-  a += ld_align16((su1 > su2 ? su1 : su2) * 4);
-  m.sc = a;
-  const int sc1 = 4 * 4 * 16 * qmm_sc_stride(ngd);        // gate/up: 4 groups x {gate,up} x {scale,bias} x 16 rows
-  const int sc2 = kLdWarps * 2 * 16 * qmm_sc_stride(ngf);  // down: up to 16 groups x {scale,bias} x 16 rows
-  a += ld_align16(sc1 > sc2 ? sc1 : sc2);
-  m.red = a;
-  a += kLdWarps * 32 * 8 * 4;
-  m.ybuf = a;
-  a += ld_align16(tiles_per_cta * rtot * 16 * 4);  // projected rows of every output tile the CTA owns
-  m.route = a;
-  a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);  // per row: scores, logits, sort keys, group scratch, winners
+  m.xsum = a;  // per (group, row): {sum x, 1024 sum_even x + 64 sum_odd x}
+  const int su1 = ngd * T, su2 = ngf * hrows;
+  a += ld_align16((su1 > su2 ? su1 : su2) * 8);
+  const int nr = T > hrows ? T : hrows;
+  m.isig = a;  // per staged row: 1 / its power-of-two scale
+  a += ld_align16(nr * 4);
+  m.rowmax = a;
+  a += ld_align16(nr * 4);
+  m.route = a;  // per row: sort keys, scores, logits, group scratch, winners
+  a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);
   m.meta = a;
   a += ld_align16((int)sizeof(LdMeta));
-  m.zero = a;
+  m.red = a;  // K-split partial sums of the teams (and the router's segment sums before that)
+  a += kLdTeams * 3 * 32 * 8 * 4;
+  m.flags = a;  // [0] a wait ran out; [1..4] items whose partial sums a team's first warp has read;
+  a += 128;     // [8 + 3 team + w] items whose partial sums warp w+1 of the team has written
+  m.bars = a;   // full[team][stage], empty[team][stage], routing done
+  a += (2 * kLdTeams * kLdMaxDepth + 1) * 8 + 8;
+  m.zero = a;  // 32 zero bytes: the B fragment of columns that carry another group
   a += 32;
+  a = (a + 127) & ~127;
+  m.ring = a;
+  a += slots * kLdSlotBytes;
   m.total = a;
   return m;
 }
 
-// ------------------------------------------------------------------ warp-group barrier
-__device__ __forceinline__ void ld_group_sync(int gid, int wk_count) {
-  if (wk_count == 1)
-    __syncwarp();
-  else
-    asm volatile("bar.sync %0, %1;" ::"r"(gid + 1), "r"(wk_count * 32) : "memory");
+// ------------------------------------------------------------------ mbarriers and bulk copies
+__device__ __forceinline__ uint32_t ld_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ld_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-
-// ------------------------------------------------------------------ hand-over words
-// Values that one CTA produces and others consume (router logits, h rows) travel as 32-bit words
-// {launch tag : 16 | bfloat16 : 16}.  A consumer re-reads a word until its tag is the current launch's, so
-// the value and its "ready" flag arrive in one relaxed access and no grid-wide barrier is needed.  The tag
-// is 1 + (launch count mod 65535): never zero, so a zeroed workspace holds no valid word.
-__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void ld_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
+__device__ __forceinline__ bool ld_mbar_try(uint32_t bar, int parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
                : "memory");
-  return v;
+  return ok != 0;
 }
-__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// The same test, but the warp may sleep up to ~1 us inside it instead of burning issue slots.
+__device__ __forceinline__ bool ld_mbar_try_sleep(uint32_t bar, int parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity), "n"(1000)
+               : "memory");
+  return ok != 0;
+}
+// Bounded wait for a phase of an mbarrier (about a second); gives up early when another warp of the CTA has.
+__device__ __forceinline__ bool ld_mbar_wait(uint32_t bar, int parity, const volatile int* flags) {
+  if (ld_mbar_try(bar, parity)) return true;
+  for (int i = 0; i < (kLdSpinLimit >> 1); ++i) {
+    if (ld_mbar_try_sleep(bar, parity)) return true;
+    if ((i & 255) == 255 && flags[0]) return false;
+  }
+  return false;
+}
+// 16-byte asynchronous copy global -> shared (L2 only), and the arrival that fires on an mbarrier once all of
+// the thread's earlier copies have landed.
+__device__ __forceinline__ void ld_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ld_cp_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait until a flag in shared memory reaches `want`.
+__device__ __forceinline__ bool ld_flag_wait(const volatile int* flag, int want, const volatile int* flags) {
+  for (int i = 0; i < kLdSpinLimit; ++i) {
+    if (*flag >= want) return true;
+    if ((i & 1023) == 1023 && flags[0]) return false;
+  }
+  return false;
 }
 
-// Order-preserving map float -> uint32 (for finite values and infinities; -0 must be folded into +0 first).
-__device__ __forceinline__ uint32_t ld_order_key(float v) {
-  const uint32_t u = __float_as_uint(v);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+__device__ __forceinline__ void mma_f16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// codes at bits [0,4) and [16,20) -> half2 (1024 + q, 1024 + q'); codes at bits [4,8) and [20,24) -> half2
+// (1024 + 16 q, 1024 + 16 q').  One LOP3 each: (w & mask) | 0x64006400.
+__device__ __forceinline__ uint32_t deq_h_lo(uint32_t w) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(r) : "r"(w));
+  return r;
+}
+__device__ __forceinline__ uint32_t deq_h_hi(uint32_t w) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x00F000F0, 0x64006400, 0xEA;" : "=r"(r) : "r"(w));
+  return r;
+}
+
+#define LD_STAMP(i)                                                            \
+  do {                                                                         \
+    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[i] = clock64(); \
+  } while (0)
 
 // ------------------------------------------------------------------ staging of token rows
-// Rows go to shared memory with every 8-element block permuted to (0,4,1,5,2,6,3,7) -- the order in
-// which a lane's two 16-byte reads give the B fragments of four k16 steps -- plus per-group sums.
-// TAGGED: the source holds hand-over words (see below); a block is re-read until its eight tags are the
-// current launch's.  Returns false when such a wait ran out.
+// nrows rows of K8 * 8 bfloat16 values go to shared memory as fp16 in fragment order, with the per-group sums
+// the fix-up needs.  Pass 1 brings the raw rows in (TAGGED: the source holds hand-over words; a block of eight
+// is re-read until its tags are the current launch's) and finds each row's largest magnitude; pass 2 scales
+// by the row's power of two, converts and permutes in place.  Eight-element block k of a row (the codes of one
+// packed word) becomes [x0, x4, x1/16, x5/16, x2, x6, x3/16, x7/16].  All consumer threads must call this;
+// returns false when a wait ran out (every thread of the CTA sees flags[0] set after the last barrier).
 template <bool TAGGED>
-__device__ __forceinline__ bool ld_stage_rows(unsigned char* xs, int xs_stride, float* xsum, int xsum_stride,
-                                              const void* src, int ld, int nrows, int K8, uint32_t tag) {
+__device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float2* xsum, int rs, float* isig,
+                                              int* rowmax, const void* src, int ld, const unsigned char* rowlist,
+                                              int nrows, int K8, uint32_t tag, volatile int* flags, int* status) {
+  const int tid = threadIdx.x, lane = tid & 31;
   const int total = nrows * K8;
-  const int lane = threadIdx.x & 31;
-  bool good = true;
+  if (tid < nrows) rowmax[tid] = 0;
+  ld_csync();
 #pragma unroll 1
-  for (int base = (int)(threadIdx.x & ~31u); base < total; base += kLdThreads) {
+  for (int base = (int)(tid & ~31u); base < total; base += kLdConsumers) {
     const int i = base + lane;
-    const bool ok = i < total;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    int t = 0, blk = 0;
-    if (ok) {
-      t = i / K8;
-      blk = i - t * K8;
+    if (i < total) {
+      const int t = i / K8, blk = i - t * K8;
+      uint4 v;
       if (TAGGED) {
-        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)t * ld + blk * 8;
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)rowlist[t] * ld + blk * 8;
         uint4 a, b;
         int spins = 0;
         for (;;) {
@@ -189,8 +244,11 @@ __device__ __forceinline__ bool ld_stage_rows(unsigned char* xs, int xs_stride, 
           const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
                                 (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
           if (bad == 0u) break;
-          if (++spins >= kLdSpinLimit) {
-            good = false;
+          ++spins;
+          if (spins >= kLdSpinLimit || ((spins & 1023) == 1023 && flags[0])) {
+            flags[0] = 1;
+            atomicExch(status, 1);
+            a = b = make_uint4(0u, 0u, 0u, 0u);
             break;
           }
         }
@@ -201,706 +259,552 @@ __device__ __forceinline__ bool ld_stage_rows(unsigned char* xs, int xs_stride, 
       } else {
         v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + (size_t)t * ld) + blk);
       }
+      *reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16) = v;
+      // magnitudes of bfloat16 order like their low 15 bits
+      const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+      uint32_t m = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m = max(m, max(q[k] & 0x7fffu, (q[k] >> 16) & 0x7fffu));
+      atomicMax(rowmax + t, (int)m);
+    }
+  }
+  ld_csync();
+#pragma unroll 1
+  for (int base = (int)(tid & ~31u); base < total; base += kLdConsumers) {
+    const int i = base + lane;
+    const bool ok = i < total;
+    int t = 0, blk = 0;
+    float se = 0.0f, so = 0.0f;
+    if (ok) {
+      t = i / K8;
+      blk = i - t * K8;
+      const int m = rowmax[t];
+      const int e8 = m >> 7;  // biased exponent of the largest magnitude
+      int sexp = (m == 0 || e8 == 255) ? 0 : 14 - (e8 - 127);
+      sexp = max(-100, min(100, sexp));
+      const float sigma = __uint_as_float((uint32_t)(sexp + 127) << 23);
+      uint4* slot = reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16);
+      const uint4 v = *slot;
+      const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+      __half hv[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float lo = bf16_bits_to_float(q[k] & 0xffffu) * sigma;            // element 2k (even position)
+        const float hi = bf16_bits_to_float(q[k] >> 16) * sigma * 0.0625f;      // element 2k+1 (odd position)
+        hv[2 * k] = __float2half_rn(lo);
+        hv[2 * k + 1] = __float2half_rn(hi);
+        se += __half2float(hv[2 * k]);
+        so += __half2float(hv[2 * k + 1]);
+      }
+      auto pack = [&](int a, int b) {
+        return (uint32_t)__half_as_ushort(hv[a]) | ((uint32_t)__half_as_ushort(hv[b]) << 16);
+      };
       uint4 o;
-      o.x = __byte_perm(v.x, v.z, 0x5410);
-      o.y = __byte_perm(v.x, v.z, 0x7632);
-      o.z = __byte_perm(v.y, v.w, 0x5410);
-      o.w = __byte_perm(v.y, v.w, 0x7632);
-      *reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16) = o;
+      o.x = pack(0, 4);
+      o.y = pack(1, 5);
+      o.z = pack(2, 6);
+      o.w = pack(3, 7);
+      *slot = o;
+      if (blk == 0) isig[t] = __uint_as_float((uint32_t)(127 - sexp) << 23);
     }
-    float part = ((bf16_bits_to_float(v.x & 0xffffu) + bf16_bits_to_float(v.x >> 16)) +
-                  (bf16_bits_to_float(v.y & 0xffffu) + bf16_bits_to_float(v.y >> 16))) +
-                 ((bf16_bits_to_float(v.z & 0xffffu) + bf16_bits_to_float(v.z >> 16)) +
-                  (bf16_bits_to_float(v.w & 0xffffu) + bf16_bits_to_float(v.w >> 16)));
-    part += __shfl_xor_sync(0xffffffffu, part, 1);
-    part += __shfl_xor_sync(0xffffffffu, part, 2);
-    part += __shfl_xor_sync(0xffffffffu, part, 4);
-    if (ok && (lane & 7) == 0) xsum[(blk >> 3) * xsum_stride + t] = part;
+    se += __shfl_xor_sync(0xffffffffu, se, 1);
+    so += __shfl_xor_sync(0xffffffffu, so, 1);
+    se += __shfl_xor_sync(0xffffffffu, se, 2);
+    so += __shfl_xor_sync(0xffffffffu, so, 2);
+    se += __shfl_xor_sync(0xffffffffu, se, 4);
+    so += __shfl_xor_sync(0xffffffffu, so, 4);
+    if (ok && (lane & 7) == 0) xsum[(blk >> 3) * rs + t] = make_float2(fmaf(16.0f, so, se), 1024.0f * (se + so));
   }
-  return good;
+  ld_csync();
 }
 
-// ------------------------------------------------------------------ routing of the T token rows
-// Same arithmetic as the per-row router functions (softmax_topk_row / sigmoid_topk_row: the order of every
-// floating-point sum is kept, so scores, indices and weights are bit-identical).  A single warp is slow at
-// long dependent instruction sequences, so only what must be is done by one warp per row (waiting for the
-// logits, the softmax / sigmoid scores, the weights of the winners); the selection itself -- ranking every
-// score against every other one -- is spread over all threads of the CTA.
-//
-// Step 1, one warp per row: wait for the row's logits (hand-over words written by the router warps of all
-// CTAs), compute the selection scores and leave, per expert, the score, the logit and a 64-bit sort key
-// {order-preserving score : 32 | ~expert id : 32} in shared memory.  Returns false when the wait ran out.
-__device__ __forceinline__ bool ld_route_scores(const uint32_t* g_logits, uint32_t tag, int E, int family,
-                                                const float* bias, int n_group, int topk_group, float* vals,
-                                                float* lgs, uint2* keys, float* gsc /* 64 floats */, int lane,
-                                                long long* dbg = nullptr) {
-  constexpr int NJ = 8;  // values per lane: E <= 256
-  const int nj = (E + 31) >> 5;
-  {
-    uint32_t raw[NJ];
-    int spins = 0;
-    bool ok;
-    do {
-      ok = true;
+// ------------------------------------------------------------------ what a consumer warp carries around
+struct LdCtx {
+  unsigned char* smem;
+  LdMeta* meta;
+  volatile int* flags;
+  float* red;
+  uint32_t bars, ring;  // shared-space addresses
+  uint32_t tag;
+  int team, wk, lane, g, tig;
+  int depth, slot0;  // this team's stages: slot0 .. slot0 + depth - 1 of the ring
+  int use, slot;     // position in the team's stage sequence: uses of the current slot so far, the slot
+  int itn;           // items the team has finished
+  bool alive;
+};
+
+__device__ __forceinline__ uint32_t ld_full_bar(uint32_t bars, int team, int s) {
+  return bars + (team * kLdMaxDepth + s) * 8;
+}
+__device__ __forceinline__ uint32_t ld_empty_bar(uint32_t bars, int team, int s) {
+  return bars + ((kLdTeams + team) * kLdMaxDepth + s) * 8;
+}
+__device__ __forceinline__ uint32_t ld_route_bar(uint32_t bars) { return bars + 2 * kLdTeams * kLdMaxDepth * 8; }
+
+// Stream position p of a warp (four groups per chunk) -> group of the row: chunk p / 4 holds quads
+// 4 * chunk .. 4 * chunk + 3, warp wk owns quad 4 * chunk + wk.
+__device__ __forceinline__ int ld_group_of(int p, int wk) { return ((((p >> 2) << 2) + wk) << 2) + (p & 3); }
+
+// Scales and biases of the block of 8 / TT groups that starts at stream position p0: sb[m][h][0] scale,
+// [1] bias of row g + 8h of matrix m.  With one token a lane's two columns are two adjacent groups (one 32-bit
+// load brings both); otherwise both columns are the same group.
+template <int TT>
+__device__ __forceinline__ void ld_load_sb(uint32_t (&sb)[2][2][2], const __nv_bfloat16* const (&sp)[2],
+                                           const __nv_bfloat16* const (&bp)[2], int ng, int p0, int wk, int tig) {
+  const int G = ld_group_of(p0 + ((TT == 1) ? 2 * tig : (2 * tig) / TT), wk);
+#ifdef ZMOE_LD_EXP_NO_SB
+  const bool ok = false;
+#else
+  const bool ok = G < ng;
+#endif
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        raw[j] = tag;
-        if (lane + 32 * j < E) raw[j] = ld_relaxed_u32(g_logits + (size_t)(lane + 32 * j) * 8);
-        ok = ok && ((raw[j] & 0xffff0000u) == tag);
-      }
-      ok = __all_sync(0xffffffffu, ok);
-    } while (!ok && ++spins < kLdSpinLimit);
-    if (!ok) return false;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < E) lgs[lane + 32 * j] = bf16_bits_to_float(raw[j] & 0xffffu);
-    if (dbg && lane == 0) {
-      dbg[22] = clock64();
-      dbg[23] = spins;
-    }
-  }
-  // From here on the loops over a lane's values stay rolled (they run once per launch: code size matters more
-  // than overlap); every lane touches only its own entries lane, lane + 32, ... of the shared arrays.
-  if (family == 0) {
-#pragma unroll 1
-    for (int j = 0; j < nj; ++j) {
-      const int idx = lane + 32 * j;
-      if (idx < E) vals[idx] = lgs[idx];
-    }
-  } else if (family == 1) {
-    float mx = -CUDART_INF_F;
-#pragma unroll 1
-    for (int j = 0; j < nj; ++j) {
-      const int idx = lane + 32 * j;
-      if (idx < E) mx = fmaxf(mx, lgs[idx]);
-    }
-    mx = warp_max(mx);
-    float sum = 0.0f;
-#pragma unroll 1
-    for (int j = 0; j < nj; ++j) {
-      const int idx = lane + 32 * j;
-      const float e = (idx < E) ? expf(lgs[idx] - mx) : 0.0f;
-      if (idx < E) vals[idx] = e;
-      sum += e;
-    }
-    sum = warp_sum(sum);
-#pragma unroll 1
-    for (int j = 0; j < nj; ++j) {
-      const int idx = lane + 32 * j;
-      if (idx < E) {
-        float q = vals[idx] / sum;
-        if (bias) q += bias[idx];
-        vals[idx] = q;
-      }
-    }
-  } else {
-    return true;  // sigmoid family: the scores are computed by all threads (ld_sigmoid_scores)
-  }
-#pragma unroll 1
-  for (int j = 0; j < nj; ++j) {
-    const int idx = lane + 32 * j;
-    if (idx < E) keys[idx] = make_uint2(~(uint32_t)idx, ld_order_key(vals[idx] + 0.0f));  // .y is the high half
-  }
-  return true;
-}
-
-// Step 1b, sigmoid family, all threads: scores = sigmoid(logit) + bias, group-limited selection (a group's
-// score is the sum of its two largest scores; the best topk_group groups are kept, ties to the lower group;
-// the experts of the other groups are scored 0.0), then the sort keys.  Maxima and the sum of two numbers do
-// not depend on evaluation order, so the result is bit-identical to the one-warp form of sigmoid_topk_row.
-// Contains CTA-wide barriers: every thread must call it.
-__device__ __forceinline__ void ld_sigmoid_scores(int T, int E, const float* bias, int n_group, int topk_group,
-                                                  float* vals, const float* lgs, uint2* keys, float* gsc) {
-  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  for (int i = tid; i < T * E; i += kLdThreads) vals[i] = sigmoid_stable(lgs[i]) + bias[i % E];
-  if (n_group > 1) {  // uniform over the CTA
-    __syncthreads();
-    const int per = E / n_group;
-    for (int pg = wid; pg < T * n_group; pg += kLdWarps) {  // one warp per (row, group)
-      const int t = pg / n_group, grp = pg - t * n_group;
-      const float* src = vals + (size_t)t * E + grp * per;
-      float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
-      for (int j = lane; j < per; j += 32) {
-        const float x = src[j];
-        if (x > t1) {
-          t2 = t1;
-          t1 = x;
-        } else if (x > t2) {
-          t2 = x;
-        }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {  // merge the lanes' (largest, second largest) pairs
-        const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
-        const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
-        const float hi = fmaxf(t1, o1);
-        t2 = fmaxf(fminf(t1, o1), fmaxf(t2, o2));
-        t1 = hi;
-      }
-      if (lane == 0) gsc[t * 64 + grp] = t1 + t2;
-    }
-    __syncthreads();
-    if (tid < T * n_group) {
-      const int t = tid / n_group, grp = tid - t * n_group;
-      const float mine = gsc[t * 64 + grp];
-      int rank = 0;
-      for (int h = 0; h < n_group; ++h) {
-        const float o = gsc[t * 64 + h];
-        rank += (o > mine) || (o == mine && h < grp);
-      }
-      gsc[t * 64 + 32 + grp] = (rank < topk_group) ? 1.0f : 0.0f;
-    }
-    __syncthreads();
-    for (int i = tid; i < T * E; i += kLdThreads) {
-      const int t = i / E, e = i - t * E;
-      if (gsc[t * 64 + 32 + e / per] == 0.0f) vals[i] = 0.0f;
-    }
-  }
-  // each thread reads back only what it wrote itself
-  for (int i = tid; i < T * E; i += kLdThreads) keys[i] = make_uint2(~(uint32_t)(i % E), ld_order_key(vals[i] + 0.0f));
-}
-
-// Step 2, all threads: rank of every score under (score descending, expert id ascending) -- one unsigned
-// 64-bit comparison of the sort keys.  The ranks of a row are a permutation, so the experts ranked below K
-// write themselves into slot order.
-__device__ __forceinline__ void ld_rank_select(const uint2* keys, int T, int E, int K, int* sel_idx) {
-  const int pairs = T * E;
-  int P = 1;  // threads that share one score's scan
-  while (P < 32 && P * 2 * pairs <= kLdThreads) P *= 2;
-  const int lp = 31 - __clz(P);
-  const int per_pass = kLdThreads >> lp;
-  const int part = threadIdx.x & (P - 1);
-  for (int base = 0; base < pairs; base += per_pass) {
-    const int pair = base + (threadIdx.x >> lp);
-    const bool ok = pair < pairs;
-    const int t = ok ? pair / E : 0;
-    const int i = ok ? pair - t * E : 0;
-    const unsigned long long* row = reinterpret_cast<const unsigned long long*>(keys + (size_t)t * E);
-    const unsigned long long mine = row[i];
-    int rank = 0;
-#pragma unroll 4
-    for (int j = part; j < E; j += P) rank += (row[j] > mine);
-    for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-    if (ok && part == 0 && rank < K) sel_idx[t * K + rank] = i;
-  }
-}
-
-// Step 3, one warp per row: the weights of the selected experts.  Lane i < K owns slot i; sums run over the
-// slots in order 0..K-1 (every lane repeats them), as in the per-row router functions.
-__device__ __forceinline__ void ld_finish_row(const float* vals, const float* lgs, int K, int family, int renorm,
-                                              float scale, const int* sel_idx, float* w_out, int* idx_out, int lane) {
-  const int si = sel_idx[lane < K ? lane : 0];
-  const float sv = vals[si];
-  float mine;  // the slot's term of the normalising sum
-  if (family == 0)
-    mine = expf(sv - vals[sel_idx[0]]);
-  else if (family == 1)
-    mine = sv;
-  else
-    mine = sigmoid_stable(lgs[si]);
-  float sum = 0.0f;
-  for (int i = 0; i < K; ++i) sum += __shfl_sync(0xffffffffu, mine, i);
-  float w;
-  if (family == 0) {
-    w = mine / sum;
-  } else if (family == 1) {
-    const float denom = (renorm == 1) ? sum + 1e-20f : sum;
-    w = renorm ? sv / denom : sv;
-  } else {
-    const float inv = 1.0f / sum;
-    w = mine * inv;
-    if (scale != 1.0f) w = w * scale;
-  }
-  if (lane < K) {
-    w_out[lane] = w;
-    idx_out[lane] = si;
-  }
-}
-
-// ------------------------------------------------------------------ matmul core (one warp)
-template <int NMAT>
-__device__ __forceinline__ void ld_load_quad(uint2 (&buf)[4][NMAT][2], const uint32_t* (&wp)[NMAT][2]) {
-#pragma unroll
-  for (int m = 0; m < NMAT; ++m) {
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      buf[0][m][h] = ldg_stream_u2<0>(wp[m][h]);
-      buf[1][m][h] = ldg_stream_u2<32>(wp[m][h]);
-      buf[2][m][h] = ldg_stream_u2<64>(wp[m][h]);
-      buf[3][m][h] = ldg_stream_u2<96>(wp[m][h]);
-    }
-  }
-}
-
-// Starts one (expert, 16-row tile) item: the first PD quads of this warp's share of K go to registers ...
-template <int NMAT, int PD>
-__device__ __forceinline__ void ld_issue_w(uint2 (&wbuf)[PD][4][NMAT][2], const uint32_t* (&wp)[NMAT][2],
-                                           const LdBank& bank, int e, int N, int K8, int n0, int g, int tig, int wk,
-                                           int wk_count, int nq_w) {
-#pragma unroll
-  for (int m = 0; m < NMAT; ++m) {
-    const uint32_t* we = bank.w[m] + ((size_t)e * N + n0) * K8 + tig * 2 + wk * 32;
-    wp[m][0] = we + (size_t)g * K8;
-    wp[m][1] = we + (size_t)(g + 8) * K8;
-  }
-#pragma unroll
-  for (int bq = 0; bq < PD; ++bq) {
-    if (bq < nq_w) {
-      ld_load_quad<NMAT>(wbuf[bq], wp);
-#pragma unroll
-      for (int m = 0; m < NMAT; ++m) {
-        wp[m][0] += wk_count * 32;
-        wp[m][1] += wk_count * 32;
+      if (TT == 1) {
+        sb[m][h][0] = ok ? __ldg(reinterpret_cast<const uint32_t*>(sp[m] + (size_t)h * 8 * ng + G)) : 0u;
+        sb[m][h][1] = ok ? __ldg(reinterpret_cast<const uint32_t*>(bp[m] + (size_t)h * 8 * ng + G)) : 0u;
+      } else {
+        sb[m][h][0] = ok ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(sp[m] + (size_t)h * 8 * ng + G)) : 0u;
+        sb[m][h][1] = ok ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(bp[m] + (size_t)h * 8 * ng + G)) : 0u;
       }
     }
-  }
 }
 
-// ... and the tile's scales and biases to the group's shared-memory area (asynchronous copies, raw T values).
-template <int NMAT>
-__device__ __forceinline__ void ld_issue_sc(const LdBank& bank, int e, int N, int ngroups, int n0, unsigned char* sraw,
-                                            int sc_stride, int gtid, int gsize) {
-  const int cpr = ngroups >> 2;  // 8-byte chunks per row
-#pragma unroll
-  for (int arr = 0; arr < NMAT * 2; ++arr) {
-    const __nv_bfloat16* base = ((arr & 1) ? bank.b[arr >> 1] : bank.s[arr >> 1]) + ((size_t)e * N + n0) * ngroups;
-    unsigned char* dst = sraw + arr * 16 * sc_stride;
-    for (int i = gtid; i < 16 * cpr; i += gsize) {
-      const int r = i / cpr;
-      const int c = i - r * cpr;
-      cp_async_8(dst + r * sc_stride + c * 8, base + (size_t)r * ngroups + c * 4);
-    }
-  }
-}
-
-// Picks the routed or the shared bank field by field (keeps the kernel parameters out of local memory).
-__device__ __forceinline__ LdBank ld_pick(const LdBank& a, const LdBank& b, bool second) {
-  LdBank r;
-#pragma unroll
-  for (int m = 0; m < 2; ++m) {
-    r.w[m] = second ? b.w[m] : a.w[m];
-    r.s[m] = second ? b.s[m] : a.s[m];
-    r.b[m] = second ? b.b[m] : a.b[m];
-  }
-  return r;
-}
-
-// Scale, bias and the 128 offset for a block of 8/TT multiplexed groups whose first item in the warp's stream
-// is gi0.  Lane (g, tig) owns columns 2*tig and 2*tig+1; srow_c[c] is the staged row of column c's token (-1: none).
-template <int NMAT, int TT>
-__device__ __forceinline__ void ld_fixup(float (&acc)[NMAT][4], const float (&dg)[NMAT][4], const float* xsum,
-                                         int xsum_stride, const int (&srow_c)[2], const unsigned char* sraw,
-                                         int sc_stride, int wk, int wk_count, int g, int tig, int gi0, int nq_w) {
+// Scale, bias and the offsets for the block of 8 / TT multiplexed groups that starts at stream position p0.
+// Lane (g, tig) owns columns 2*tig and 2*tig+1; srow_c[c] is the staged row of column c's token (-1: none).
+template <int TT>
+__device__ __forceinline__ void ld_fixup(float (&acc)[2][4], const float (&dg)[2][2][4], const uint32_t (&sb)[2][2][2],
+                                         const float2* xsum, int rs, const int (&srow_c)[2], int ng, int p0, int wk,
+                                         int tig) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    const int col = 2 * tig + c;
-    const int gi_c = gi0 + ((TT == 8) ? 0 : col / TT);
-    const int G_c = (wk + (gi_c >> 2) * wk_count) * 4 + (gi_c & 3);
-    if ((gi_c >> 2) < nq_w) {
-      const float X = (srow_c[c] >= 0) ? xsum[G_c * xsum_stride + srow_c[c]] : 0.0f;
+    const int G = ld_group_of(p0 + ((TT == 8) ? 0 : (2 * tig + c) / TT), wk);
+    float2 xc = make_float2(0.0f, 0.0f);
+    if (G < ng && srow_c[c] >= 0) xc = xsum[G * rs + srow_c[c]];
 #pragma unroll
-      for (int m = 0; m < NMAT; ++m) {
+    for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = g + 8 * h;
-          const float sv = __bfloat162float(
-              *reinterpret_cast<const __nv_bfloat16*>(sraw + ((m * 2 + 0) * 16 + r) * sc_stride + G_c * 2));
-          const float bv = __bfloat162float(
-              *reinterpret_cast<const __nv_bfloat16*>(sraw + ((m * 2 + 1) * 16 + r) * sc_stride + G_c * 2));
-          const float cv = fmaf(-128.0f, sv, bv);
-          acc[m][h * 2 + c] = fmaf(sv, dg[m][h * 2 + c], fmaf(cv, X, acc[m][h * 2 + c]));
-        }
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t sraw = sb[m][h][0], braw = sb[m][h][1];
+        const float sv = __uint_as_float((TT == 1 && c == 1) ? (sraw & 0xffff0000u) : (sraw << 16));
+        const float bv = __uint_as_float((TT == 1 && c == 1) ? (braw & 0xffff0000u) : (braw << 16));
+        const float dsum = dg[m][0][h * 2 + c] + dg[m][1][h * 2 + c];
+        acc[m][h * 2 + c] = fmaf(sv, dsum - xc.y, fmaf(bv, xc.x, acc[m][h * 2 + c]));
       }
-    }
   }
 }
 
-// This warp's share of K for one item.  xoff is the byte offset (in shared memory) of the lane's token row
-// plus tig*32; lanes whose column carries no token of this item read the zero page.  The four k16 steps of a
-// group go to NACC independent accumulators (summed in a fixed order at the fix-up): a chain of dependent
-// mma.sync on one accumulator costs its full latency per step, and at decode sizes nothing else hides it.
-template <int NMAT, int PD, int TT, int NACC>
-__device__ __forceinline__ void ld_mainloop(float (&acc)[NMAT][4], uint2 (&wbuf)[PD][4][NMAT][2],
-                                            const uint32_t* (&wp)[NMAT][2], const unsigned char* smem, int xoff,
-                                            bool tok_ok, int zpage, int slot_g, const float* xsum, int xsum_stride,
-                                            const int (&srow_c)[2], const unsigned char* sraw, int sc_stride, int wk,
-                                            int wk_count, int nq_w, int g, int tig) {
-  static_assert(NACC == 1 || NACC == 2 || NACC == 4, "accumulators per matrix");
+// One (task, tile) item of a team: every warp walks its quad of each chunk as the producer's copies land.
+// DN = false: gate/up, matrices m = gate, up of rows n0 .. n0+15; DN = true: down, m = rows n0 + 16 m ..
+// Leaves the K-split total of the team in the first warp's acc, columns folded back onto their tokens.
+template <int TT, bool DN>
+__device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBank& bank, int e, int N, int K8,
+                                        int n0, int xoff, int zoff, bool tok_ok, int slot_g, const float2* xsum,
+                                        int rs, const int (&srow_c)[2]) {
   constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
-  float dg[NMAT][NACC][4];
-  float dsum[NMAT][4];
+  const int ng = K8 >> 3;
+  const int rb = K8 << 2;  // bytes of a weight row
+  const int nch = (rb + kLdSegBytes - 1) / kLdSegBytes;
+  const int wk = c.wk, g = c.g, tig = c.tig;
+  const __nv_bfloat16* sp[2];
+  const __nv_bfloat16* bp[2];
 #pragma unroll
-  for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
-#pragma unroll
-    for (int n = 0; n < NACC; ++n)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) dg[m][n][j] = 0.0f;
+  for (int m = 0; m < 2; ++m) {
+    const size_t row = (size_t)e * N + n0 + (DN ? m * 16 : 0) + g;
+    sp[m] = bank.s[DN ? 0 : m] + row * ng;
+    bp[m] = bank.b[DN ? 0 : m] + row * ng;
   }
-  auto fold = [&]() {
+  float dg[2][2][4];
 #pragma unroll
-    for (int m = 0; m < NMAT; ++m)
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[m][j] = 0.0f;
+      dg[m][0][j] = 0.0f;
+      dg[m][1][j] = 0.0f;
+    }
+  uint32_t sb_cur[2][2][2], sb_nxt[2][2][2];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) sb_cur[m][h][0] = sb_cur[m][h][1] = sb_nxt[m][h][0] = sb_nxt[m][h][1] = 0u;
+  if (TT > 1) ld_load_sb<TT>(sb_cur, sp, bp, ng, 0, wk, tig);
+
+  for (int ch = 0; ch < nch; ++ch) {
+    // ---- wait for the stage (every lane polls: the data was written by the copy engine)
+    const uint32_t full = ld_full_bar(c.bars, c.team, c.slot);
+    if (c.alive && !ld_mbar_wait(full, c.use & 1, c.flags)) {
+      c.alive = false;
+      c.flags[0] = 1;
+    }
+#ifdef ZMOE_LD_EXP_SKIP_MATH
+    const bool have = false;
+#else
+    const bool have = c.alive && ((ch * 4 + wk) * 128 < rb);  // the warp's quad exists in this row
+#endif
+    if (have) {
+      const uint32_t wbase = c.ring + (uint32_t)(c.slot0 + c.slot) * kLdSlotBytes + g * kLdSegStride + wk * 128 + tig * 8;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        if (NACC == 1) dsum[m][j] = dg[m][0][j];
-        if (NACC == 2) dsum[m][j] = dg[m][0][j] + dg[m][NACC - 1][j];
-        if (NACC == 4) dsum[m][j] = (dg[m][0][j] + dg[m][1 % NACC][j]) + (dg[m][2 % NACC][j] + dg[m][3 % NACC][j]);
-      }
-  };
-  for (int qi = 0; qi < nq_w; qi += PD) {
+        const int slot = (TT == 1) ? ((ch & 1) * 4 + j) : (j % GPB);
+        const int pos = ch * 4 + j;
+        if (slot == 0) {
+          if (TT == 1)
+            ld_load_sb<TT>(sb_cur, sp, bp, ng, pos, wk, tig);
+          else
+            ld_load_sb<TT>(sb_nxt, sp, bp, ng, pos + GPB, wk, tig);
+        }
+        // lanes whose column carries another group (or no token) read the zero page
+        const bool mine = tok_ok && (TT == 8 || slot_g == slot);
+        const int xa = mine ? (xoff + ((ch * 4 + wk) * 4 + j) * 128) : zoff;
+        const uint4 xb0 = *reinterpret_cast<const uint4*>(c.smem + xa);
+        const uint4 xb1 = *reinterpret_cast<const uint4*>(c.smem + xa + 16);
 #pragma unroll
-    for (int bq = 0; bq < PD; ++bq) {
-      const int quad = wk + (qi + bq) * wk_count;
-      if (qi + bq < nq_w) {  // warp-uniform
+        for (int m = 0; m < 2; ++m) {
+          uint2 wa, wb;
+          const uint32_t wa_addr = wbase + m * 16 * kLdSegStride + j * 32;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wa.x), "=r"(wa.y) : "r"(wa_addr));
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wb.x), "=r"(wb.y) : "r"(wa_addr + 8 * kLdSegStride));
+          const uint32_t wa8 = wa.x >> 8, wb8 = wb.x >> 8;
+          mma_f16_m16n8k16(dg[m][0], deq_h_lo(wa.x), deq_h_lo(wb.x), deq_h_hi(wa.x), deq_h_hi(wb.x), xb0.x, xb0.y);
+          mma_f16_m16n8k16(dg[m][1], deq_h_lo(wa8), deq_h_lo(wb8), deq_h_hi(wa8), deq_h_hi(wb8), xb0.z, xb0.w);
+          const uint32_t wc8 = wa.y >> 8, wd8 = wb.y >> 8;
+          mma_f16_m16n8k16(dg[m][0], deq_h_lo(wa.y), deq_h_lo(wb.y), deq_h_hi(wa.y), deq_h_hi(wb.y), xb1.x, xb1.y);
+          mma_f16_m16n8k16(dg[m][1], deq_h_lo(wc8), deq_h_lo(wd8), deq_h_hi(wc8), deq_h_hi(wd8), xb1.z, xb1.w);
+        }
+        if (slot == GPB - 1) {
+          ld_fixup<TT>(acc, dg, sb_cur, xsum, rs, srow_c, ng, pos - (GPB - 1), wk, tig);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int slot = (bq * 4 + j) % GPB;
-          if (slot == 0) {
+          for (int m = 0; m < 2; ++m)
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m)
+            for (int jj = 0; jj < 4; ++jj) {
+              dg[m][0][jj] = 0.0f;
+              dg[m][1][jj] = 0.0f;
+            }
+          if (TT > 1) {
 #pragma unroll
-              for (int n = 0; n < NACC; ++n)
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) dg[m][n][jj] = 0.0f;
-          }
-          const bool mine = tok_ok && (TT == 8 || slot_g == slot);
-          const int xo = mine ? (xoff + quad * 512 + j * 128) : zpage;
-          const uint4 xb0 = *reinterpret_cast<const uint4*>(smem + xo);
-          const uint4 xb1 = *reinterpret_cast<const uint4*>(smem + xo + 16);
-#pragma unroll
-          for (int m = 0; m < NMAT; ++m) {
-            const uint2 wa = wbuf[bq][j][m][0];
-            const uint2 wb = wbuf[bq][j][m][1];
-            mma_bf16_m16n8k16(dg[m][0], deq_imm<0>(wa.x), deq_imm<0>(wb.x), deq_imm<4>(wa.x), deq_imm<4>(wb.x), xb0.x,
-                              xb0.y);
-            mma_bf16_m16n8k16(dg[m][1 % NACC], deq_imm<8>(wa.x), deq_imm<8>(wb.x), deq_imm<12>(wa.x),
-                              deq_imm<12>(wb.x), xb0.z, xb0.w);
-            mma_bf16_m16n8k16(dg[m][2 % NACC], deq_imm<0>(wa.y), deq_imm<0>(wb.y), deq_imm<4>(wa.y), deq_imm<4>(wb.y),
-                              xb1.x, xb1.y);
-            mma_bf16_m16n8k16(dg[m][3 % NACC], deq_imm<8>(wa.y), deq_imm<8>(wb.y), deq_imm<12>(wa.y),
-                              deq_imm<12>(wb.y), xb1.z, xb1.w);
-          }
-          // rolling refill: the registers of the group just consumed take the same group of the quad PD steps
-          // ahead at once (keeps the bytes in flight near their maximum instead of dipping once per quad)
-          if (qi + bq + PD < nq_w) {
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
+            for (int m = 0; m < 2; ++m)
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
-                if (j == 0) wbuf[bq][0][m][h] = ldg_stream_u2<0>(wp[m][h]);
-                if (j == 1) wbuf[bq][1][m][h] = ldg_stream_u2<32>(wp[m][h]);
-                if (j == 2) wbuf[bq][2][m][h] = ldg_stream_u2<64>(wp[m][h]);
-                if (j == 3) wbuf[bq][3][m][h] = ldg_stream_u2<96>(wp[m][h]);
+                sb_cur[m][h][0] = sb_nxt[m][h][0];
+                sb_cur[m][h][1] = sb_nxt[m][h][1];
               }
-            }
-          }
-          if (slot == GPB - 1) {
-            fold();
-            ld_fixup<NMAT, TT>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig,
-                               (qi + bq) * 4 + j - (GPB - 1), nq_w);
-          }
-        }
-        if (qi + bq + PD < nq_w) {  // the refilled quad's pointers move on
-#pragma unroll
-          for (int m = 0; m < NMAT; ++m) {
-            wp[m][0] += wk_count * 32;
-            wp[m][1] += wk_count * 32;
           }
         }
       }
     }
+    // ---- hand the stage back to the producer
+    __syncwarp();
+    if (c.alive && c.lane == 0) ld_mbar_arrive(ld_empty_bar(c.bars, c.team, c.slot));
+    if (++c.slot == c.depth) {
+      c.slot = 0;
+      ++c.use;
+    }
   }
-  // an odd number of quads leaves half a block of eight multiplexed groups without its fix-up
-  if (GPB == 8 && (nq_w & 1)) {
-    fold();
-    ld_fixup<NMAT, TT>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig, (nq_w - 1) * 4,
-                       nq_w);
-  }
-}
+  // one token: an odd number of chunks leaves half a block of eight groups without its fix-up
+  if (TT == 1 && (nch & 1) && c.alive) ld_fixup<TT>(acc, dg, sb_cur, xsum, rs, srow_c, ng, (nch - 1) * 4, wk, tig);
 
-// Sums the K-split partial results of a group's warps in warp order (result in the group's first warp), then
-// folds the multiplexed columns back onto their tokens: afterwards column c < TT of the first warp holds token c.
-template <int NMAT, int TT>
-__device__ __forceinline__ void ld_reduce_fold(float (&acc)[NMAT][4], float* red, int gid, int wk, int wk_count,
-                                               int lane) {
-  const int wid = threadIdx.x >> 5;
-  if (wk_count > 1) {
-    float* mine = red + (wid * 32 + lane) * 8;
+  // ---- K-split: the partial sums of warps 1..3 go to the team's first warp in warp order
+  const int it = c.itn++;
+  if (c.alive) {
     if (wk != 0) {
+      // the first warp must have read the previous item's sums before they are overwritten
+      if (it > 0 && !ld_flag_wait(c.flags + 1 + c.team, it, c.flags)) {
+        c.alive = false;
+        c.flags[0] = 1;
+      }
+      float* mine = c.red + ((c.team * 3 + wk - 1) * 32 + c.lane) * 8;
 #pragma unroll
-      for (int m = 0; m < NMAT; ++m)
+      for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int j = 0; j < 4; ++j) mine[m * 4 + j] = acc[m][j];
-    }
-    ld_group_sync(gid, wk_count);
-    if (wk == 0) {
+      __threadfence_block();
+      __syncwarp();
+      if (c.lane == 0) c.flags[8 + c.team * 3 + wk - 1] = it + 1;
+    } else {
 #pragma unroll 1
-      for (int o = 1; o < wk_count; ++o) {
-        const float* other = red + ((wid + o) * 32 + lane) * 8;
+      for (int o = 1; o < 4; ++o) {
+        if (c.alive && !ld_flag_wait(c.flags + 8 + c.team * 3 + o - 1, it + 1, c.flags)) {
+          c.alive = false;
+          c.flags[0] = 1;
+        }
+        __threadfence_block();
+        const float* other = c.red + ((c.team * 3 + o - 1) * 32 + c.lane) * 8;
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
+        for (int m = 0; m < 2; ++m)
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[m][j] += other[m * 4 + j];
       }
-    }
-  }
-  if (wk == 0 && TT < 8) {
+      __threadfence_block();
+      __syncwarp();
+      if (c.lane == 0) c.flags[1 + c.team] = it + 1;
+      // fold the multiplexed columns back onto their tokens: afterwards column col < TT holds token col
+      if (TT < 8) {
 #pragma unroll
-    for (int m = 0; m < NMAT; ++m) {
+        for (int m = 0; m < 2; ++m)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (TT == 1) {
-          acc[m][h * 2] += acc[m][h * 2 + 1];
-          acc[m][h * 2 + 1] = 0.0f;
-        }
+          for (int h = 0; h < 2; ++h) {
+            if (TT == 1) {
+              acc[m][h * 2] += acc[m][h * 2 + 1];
+              acc[m][h * 2 + 1] = 0.0f;
+            }
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float v = acc[m][h * 2 + c];
-          if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          acc[m][h * 2 + c] = v;
-        }
+            for (int cc = 0; cc < 2; ++cc) {
+              float v = acc[m][h * 2 + cc];
+              if (TT <= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+              v += __shfl_xor_sync(0xffffffffu, v, 2);
+              acc[m][h * 2 + cc] = v;
+            }
+          }
       }
     }
   }
 }
-
-// ------------------------------------------------------------------ bulk-copy variant (one token)
-// With BULK the packed weights do not go to registers: every row of an item is one cp.async.bulk copy into a
-// padded shared-memory row (stride = row bytes + 32 == 32 mod 128: the 8-byte fragment reads of a warp hit 32
-// different banks), completion is counted on an mbarrier, and the matmul is a compact loop over shared
-// memory.  Issuing a copy never blocks the warp, so the copies of all of a CTA's items are in flight while
-// the first ones are already being consumed, and the loop body is fetched once instead of a long unrolled
-// register pipeline.  Needs 16-byte aligned tensors and rows that fit (d_model, d_ff <= 2048 or so).
-__device__ __forceinline__ uint32_t ld_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void ld_mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void ld_mbar_expect_tx(uint32_t bar, int bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool ld_mbar_try(uint32_t bar, int parity) {
-  uint32_t ok;
-  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-// Bounded wait for a phase of an mbarrier; false when it ran out.
-__device__ __forceinline__ bool ld_mbar_wait(uint32_t bar, int parity) {
-  for (int i = 0; i < kLdSpinLimit; ++i)
-    if (ld_mbar_try(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void ld_bulk_g2s(uint32_t dst, const void* src, int bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-// One token (TT = 1: eight groups share an accumulator), weights of the item in shared memory: rows m*16 + r at
-// `wslot + row * row_stride`.  The warp walks the quads wk, wk + wk_count, ...; the loop is kept rolled.
-template <int NMAT, int NACC>
-__device__ __forceinline__ void ld_smem_mainloop(float (&acc)[NMAT][4], const unsigned char* wslot, int row_stride,
-                                                 const unsigned char* smem, int xoff, int zpage, const float* xsum,
-                                                 int xsum_stride, const int (&srow_c)[2], const unsigned char* sraw,
-                                                 int sc_stride, int wk, int wk_count, int nq, int g, int tig) {
-  float dg[NMAT][NACC][4];
-  float dsum[NMAT][4];
-#pragma unroll
-  for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
-#pragma unroll
-    for (int n = 0; n < NACC; ++n)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) dg[m][n][j] = 0.0f;
-  }
-  auto fold = [&]() {
-#pragma unroll
-    for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (NACC == 1) dsum[m][j] = dg[m][0][j];
-        if (NACC == 2) dsum[m][j] = dg[m][0][j] + dg[m][NACC - 1][j];
-        if (NACC == 4) dsum[m][j] = (dg[m][0][j] + dg[m][1 % NACC][j]) + (dg[m][2 % NACC][j] + dg[m][3 % NACC][j]);
-      }
-  };
-  const int nq_w = (nq > wk) ? (nq - wk + wk_count - 1) / wk_count : 0;
-  const unsigned char* wlane = wslot + g * row_stride + tig * 8;
-  // blocks of eight groups (two of the warp's quads) share the accumulators; one fix-up per block
-#pragma unroll 1
-  for (int qb = 0; qb < nq_w; qb += 2) {
-#pragma unroll
-    for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-      for (int n = 0; n < NACC; ++n)
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) dg[m][n][jj] = 0.0f;
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      if (qb + half >= nq_w) break;
-      const int quad = wk + (qb + half) * wk_count;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const bool mine = (g == half * 4 + j);
-        const int xo = mine ? (xoff + quad * 512 + j * 128) : zpage;
-        const uint4 xb0 = *reinterpret_cast<const uint4*>(smem + xo);
-        const uint4 xb1 = *reinterpret_cast<const uint4*>(smem + xo + 16);
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-          const unsigned char* wr = wlane + m * 16 * row_stride + quad * 128 + j * 32;
-          const uint2 wa = *reinterpret_cast<const uint2*>(wr);
-          const uint2 wb = *reinterpret_cast<const uint2*>(wr + 8 * row_stride);
-          mma_bf16_m16n8k16(dg[m][0], deq_imm<0>(wa.x), deq_imm<0>(wb.x), deq_imm<4>(wa.x), deq_imm<4>(wb.x), xb0.x,
-                            xb0.y);
-          mma_bf16_m16n8k16(dg[m][1 % NACC], deq_imm<8>(wa.x), deq_imm<8>(wb.x), deq_imm<12>(wa.x), deq_imm<12>(wb.x),
-                            xb0.z, xb0.w);
-          mma_bf16_m16n8k16(dg[m][2 % NACC], deq_imm<0>(wa.y), deq_imm<0>(wb.y), deq_imm<4>(wa.y), deq_imm<4>(wb.y),
-                            xb1.x, xb1.y);
-          mma_bf16_m16n8k16(dg[m][3 % NACC], deq_imm<8>(wa.y), deq_imm<8>(wb.y), deq_imm<12>(wa.y), deq_imm<12>(wb.y),
-                            xb1.z, xb1.w);
-        }
-      }
-    }
-    fold();
-    ld_fixup<NMAT, 1>(acc, dsum, xsum, xsum_stride, srow_c, sraw, sc_stride, wk, wk_count, g, tig, qb * 4, nq_w);
-  }
-}
-
-// Debug builds (-DZMOE_LD_TIMING) record CTA 0's cycle counter at the phase boundaries in the workspace
-// header (8-byte slots from byte 64).
-#ifdef ZMOE_LD_TIMING
-#define LD_DBG_PTR \
-  ((blockIdx.x == 0 && wid == 0) ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.sync) + 64) : nullptr)
-#define LD_STAMP(i)                                                                     \
-  do {                                                                                  \
-    if (blockIdx.x == 0 && threadIdx.x == 0)                                            \
-      reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.sync) + 64)[i] = clock64(); \
-  } while (0)
-#else
-#define LD_DBG_PTR nullptr
-#define LD_STAMP(i) \
-  do {              \
-  } while (0)
-#endif
 
 // ------------------------------------------------------------------ the kernel
-template <int TT, bool BULK, int DPD>
+template <int TT>
 __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
-  static_assert(!BULK || TT == 1, "the bulk-copy variant is the one-token kernel");
-  extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ int wait_failed;  // a bounded wait on another CTA's words ran out somewhere in this CTA
+  extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int wid = tid >> 5;
+  const int T = p.T, K = p.K, E = p.E, d = p.d, f = p.f;
+  const int R = T * K;
+  const int nblocks = gridDim.x;
+  const LdSmem lay = ld_smem(T, K, E, d, f, p.hrows, p.slots);
+  volatile int* flags = reinterpret_cast<volatile int*>(smem + lay.flags);
+  LdMeta* meta = reinterpret_cast<LdMeta*>(smem + lay.meta);
+  const uint32_t bars = ld_smem_u32(smem + lay.bars);
+  const uint32_t ring = ld_smem_u32(smem + lay.ring);
+  const int ntf = f >> 4;  // gate/up tiles of 16 rows per task
+  const int ntd = d >> 5;  // down tiles of 32 rows per task
+  const int nch_gu = ((d >> 1) + kLdSegBytes - 1) / kLdSegBytes;
+  const int nch_dn = ((f >> 1) + kLdSegBytes - 1) / kLdSegBytes;
+  // stages of team t: depth_of(t) consecutive slots from slot0_of(t)
+  const int dbase = p.slots / kLdTeams, dextra = p.slots % kLdTeams;
+
+  // Router rows are constants: a consumer warp's pieces of the CTA's first two rows are requested before anything
+  // that depends on the previous kernel of the stream, so that with programmatic dependent launch their HBM
+  // latency hides behind that kernel.
+  const int nvec = d >> 3;
+  uint4 wpre[2][2];
+  if (wid < kLdWarps) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int e = blockIdx.x + nblocks * k;
+        const int i = wid * 32 + lane + 32 * kRouterSegs * r;
+        wpre[k][r] = (e < E && i < nvec) ? __ldg(reinterpret_cast<const uint4*>(p.wr + (size_t)e * d) + i)
+                                         : make_uint4(0u, 0u, 0u, 0u);
+      }
+  }
+  if (tid == 0) {
+    for (int t = 0; t < kLdTeams; ++t)
+      for (int s = 0; s < kLdMaxDepth; ++s) {
+        ld_mbar_init(ld_full_bar(bars, t, s), 32);  // one arrival per producer lane, when its copies have landed
+        ld_mbar_init(ld_empty_bar(bars, t, s), 4);
+      }
+    ld_mbar_init(ld_route_bar(bars), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (tid < 32) flags[tid] = 0;
+  if (tid < 8) reinterpret_cast<uint32_t*>(smem + lay.zero)[tid] = 0u;
+  for (int i = tid; i < kLdMaxTasks; i += kLdThreads) meta->task_cnt[i] = 0;
+  __syncthreads();
+  if (p.pdl) pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
+
+  // =================================================================== producer warp
+  if (wid == kLdWarps) {
+    int job[kLdTeams], total[kLdTeams], ngu[kLdTeams];
+#pragma unroll
+    for (int t = 0; t < kLdTeams; ++t) job[t] = total[t] = ngu[t] = 0;
+    const int K8g = d >> 3, K8d = f >> 3;
+    // issues chunk ch of one item into stage s of team t: one instruction copies one 512-byte row segment
+    // (16 bytes per lane); the stage's barrier gets one arrival per lane when that lane's copies have landed
+    auto issue = [&](int t, int s, bool dn, const LdBank& bank, int e, int n0, int ch) {
+      const int K8 = dn ? K8d : K8g;
+      const int N = dn ? d : f;
+      const int rb = K8 << 2;
+      const int bytes = min(kLdSegBytes, rb - ch * kLdSegBytes);
+      const int slot0 = t * dbase + min(t, dextra);
+      const uint32_t dst = ring + (uint32_t)(slot0 + s) * kLdSlotBytes + lane * 16;
+      const size_t off = ((size_t)e * N + n0) * rb + (size_t)ch * kLdSegBytes + lane * 16;
+      const unsigned char* src0 = reinterpret_cast<const unsigned char*>(bank.w[0]) + off;
+      const unsigned char* src1 = dn ? src0 + (size_t)16 * rb : reinterpret_cast<const unsigned char*>(bank.w[1]) + off;
+      if (lane * 16 < bytes) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) ld_cp16(dst + r * kLdSegStride, src0 + (size_t)r * rb);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) ld_cp16(dst + (16 + r) * kLdSegStride, src1 + (size_t)r * rb);
+      }
+      ld_cp_arrive(ld_full_bar(bars, t, s));
+    };
+    // the shared expert's tiles come first in the gate/up order and do not depend on the routing: when this
+    // CTA's first item is one of them, its chunks fill team 0's stages right away
+    const int depth0 = dbase + (0 < dextra ? 1 : 0);
+    if (p.n_shared && (int)blockIdx.x < ntf) {
+      const int n = min(nch_gu, depth0);
+      for (int ch = 0; ch < n; ++ch) issue(0, ch, false, p.sgu, 0, (int)blockIdx.x << 4, ch);
+      job[0] = n;
+    }
+    bool ok = ld_mbar_wait(ld_route_bar(bars), 0, flags) && flags[0] == 0;
+    if (ok) {
+      const int n_tasks = meta->n_tasks, n_routed = meta->n_routed;
+      const int items_gu = n_tasks * ntf;
+      const int nq_gu = (items_gu > (int)blockIdx.x) ? (items_gu - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
+      const long long items_dn = (long long)n_tasks * ntd;
+      const int dn_lo = (int)(items_dn * blockIdx.x / nblocks), dn_hi = (int)(items_dn * (blockIdx.x + 1) / nblocks);
+      const int nq_dn = dn_hi - dn_lo;
+#pragma unroll
+      for (int t = 0; t < kLdTeams; ++t) {
+        ngu[t] = (nq_gu > t) ? (nq_gu - 1 - t) / kLdTeams + 1 : 0;
+        const int ndn = (nq_dn > t) ? (nq_dn - 1 - t) / kLdTeams + 1 : 0;
+        total[t] = ngu[t] * nch_gu + ndn * nch_dn;
+      }
+      int idle = 0;
+      for (;;) {
+        bool left = false, moved = false;
+#pragma unroll
+        for (int t = 0; t < kLdTeams; ++t) {
+          if (job[t] < total[t]) {
+            left = true;
+            const int depth = dbase + (t < dextra ? 1 : 0);
+            const int s = job[t] % depth, use = job[t] / depth;
+            if (ld_mbar_try(ld_empty_bar(bars, t, s), (use & 1) ^ 1)) {
+              int j = job[t];
+              if (j < ngu[t] * nch_gu) {
+                const int qi = j / nch_gu, ch = j - qi * nch_gu;
+                const int i = (int)blockIdx.x + (t + kLdTeams * qi) * nblocks;
+                const int ao = i / ntf, tile = i - ao * ntf;
+                const int a = p.n_shared ? (ao == 0 ? n_routed : ao - 1) : ao;
+                const bool sh = a >= n_routed;
+                issue(t, s, false, sh ? p.sgu : p.gu, meta->task_expert[a], tile << 4, ch);
+              } else {
+                j -= ngu[t] * nch_gu;
+                const int qi = j / nch_dn, ch = j - qi * nch_dn;
+                const int i = dn_lo + t + kLdTeams * qi;
+                const int a = i / ntd, tile = i - a * ntd;
+                const bool sh = a >= n_routed;
+                issue(t, s, true, sh ? p.sdn : p.dn, meta->task_expert[a], tile << 5, ch);
+              }
+              ++job[t];
+              moved = true;
+            }
+          }
+        }
+        if (!left) break;
+        if (moved) {
+          idle = 0;
+        } else if (++idle >= kLdSpinLimit || ((idle & 1023) == 1023 && flags[0])) {
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      flags[0] = 1;
+      atomicExch(p.sync + 3, 1);
+    }
+    // copies still in flight must have landed before the CTA's shared memory goes away
+#pragma unroll
+    for (int t = 0; t < kLdTeams; ++t) {
+      const int depth = dbase + (t < dextra ? 1 : 0);
+      for (int j = max(0, job[t] - depth); j < job[t]; ++j) {
+        const uint32_t bar = ld_full_bar(bars, t, j % depth);
+        const int par = (j / depth) & 1;
+        for (int i = 0; i < kLdSpinLimit && !ld_mbar_try(bar, par); ++i) {
+        }
+      }
+    }
+    return;
+  }
+
+  // =================================================================== consumer warps
   const int g = lane >> 2;
   const int tig = lane & 3;
   const int slot_g = g / TT;
   const int tok_g = g % TT;
-
-  const int T = p.T, K = p.K, E = p.E, d = p.d, f = p.f;
-  const int R = T * K;
-  const int rtot = R + (p.n_shared ? T : 0);
-  const int ngd = d >> 6, ngf = f >> 6;
-  const LdSmem lay = ld_smem(T, K, E, d, f, p.n_shared, p.tiles_per_cta);
   unsigned char* xs = smem + lay.xs;
-  float* xsum = reinterpret_cast<float*>(smem + lay.xsum);
+  float2* xsum = reinterpret_cast<float2*>(smem + lay.xsum);
+  float* isig = reinterpret_cast<float*>(smem + lay.isig);
+  int* rowmax = reinterpret_cast<int*>(smem + lay.rowmax);
   float* red = reinterpret_cast<float*>(smem + lay.red);
-  float* ybuf = reinterpret_cast<float*>(smem + lay.ybuf);
   uint2* keys = reinterpret_cast<uint2*>(smem + lay.route);  // 8-byte aligned: the region starts 16-byte aligned
   float* vals = reinterpret_cast<float*>(keys + T * E);
   float* lgs = vals + T * E;
   float* gsc = lgs + T * E;
   int* sel_idx = reinterpret_cast<int*>(gsc + T * 64);
-  LdMeta* meta = reinterpret_cast<LdMeta*>(smem + lay.meta);
-  const int zpage = lay.zero;
-  const int nblocks = gridDim.x;
-  bool alive = true;
-  // Router rows are constants: the warp's first one is requested before anything that depends on the previous
-  // kernel of the stream, so that with programmatic dependent launch its HBM latency hides behind that kernel.
-  const int e_first = blockIdx.x + nblocks * wid;
-  uint4 wpre[8];
-#pragma unroll
-  for (int u = 0; u < 8; ++u)
-    wpre[u] = (e_first < E && lane + 32 * u < (d >> 3))
-                  ? __ldg(reinterpret_cast<const uint4*>(p.wr + (size_t)e_first * d) + lane + 32 * u)
-                  : make_uint4(0u, 0u, 0u, 0u);
-  if (p.pdl) {
-    pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
-    pdl_wait();     // nothing below may run before the previous kernel has finished and flushed
-  }
-  // launch count: every thread reads it here; the last CTA to sign in (below) bumps it for the next launch; tag of
-  // this launch's words
+
+  if (p.pdl) pdl_wait();  // nothing below may run before the previous kernel has finished and flushed
+  // launch count: every consumer thread reads it here; the last CTA to sign in (below) bumps it for the next
+  // launch; tag of this launch's words
   const int epoch = __ldcg(p.sync + 4);
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
-  if (tid == 0) wait_failed = 0;
-  // bulk-copy variant: 16 mbarriers {gate/up slot 0..3, down task 0..}, then the gate/up slots, then the down slots
-  const int rs_g = (d >> 1) + 32, rs_d = (f >> 1) + 32;  // padded row strides of the two kinds of slots
-  unsigned char* bulk = smem + p.bulk_off;
-  const uint32_t bars = ld_smem_u32(bulk);
-  unsigned char* gslots = bulk + 128;
-  unsigned char* dslots = gslots + p.g_slots * 32 * rs_g;
-  if (BULK && tid == 0) {
-    for (int i = 0; i < 4; ++i) ld_mbar_init(bars + i * 8, 32);
-    for (int i = 4; i < 16; ++i) ld_mbar_init(bars + i * 8, 16);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
 
   LD_STAMP(0);
-  // ---- phase 0: token rows -> shared memory (permuted, with group sums)
-  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, p.x, p.ldx, T, d >> 3, 0u);
-  if (tid < 8) reinterpret_cast<uint32_t*>(smem + zpage)[tid] = 0u;
-  for (int i = tid; i < kLdMaxTasks; i += kLdThreads) meta->task_cnt[i] = 0;
-
+  // ---- token rows -> shared memory (fp16, fragment order, group sums)
+  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
+                       p.sync + 3);
   LD_STAMP(1);
-  // ---- phase 1: router linear, one warp per expert row over the whole grid.  A lane's eight 16-byte pieces of
-  // the row are requested before anything is consumed (one memory round trip); the sum runs over i ascending
-  // per lane and then over the lanes, as in the stand-alone router kernels.
+  // ---- router linear: the CTA's rows blockIdx.x, blockIdx.x + grid, ...; warp w sums segment w of a row
   {
-    const int nvec = d >> 3;
-    for (int e = blockIdx.x + nblocks * wid; e < E; e += nblocks * kLdWarps) {
-      const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
+    int n_mine = 0;
+    for (int k = 0; k < kLdMaxMine; ++k) n_mine += ((int)blockIdx.x + nblocks * k < E);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int e = blockIdx.x + nblocks * k;
+      if (e < E) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
 #pragma unroll 1
+        for (int t = 0; t < T; ++t) {
+          const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx);
+          float acc = 0.0f;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int i = wid * 32 + lane + 32 * kRouterSegs * r;
+            if (i < nvec) acc = router_fma8(wpre[k][r], __ldg(xrow + i), acc);
+          }
+          for (int i = wid * 32 + lane + 64 * kRouterSegs; i < nvec; i += 32 * kRouterSegs)
+            acc = router_fma8(__ldg(wrow + i), __ldg(xrow + i), acc);
+          acc = warp_sum(acc);
+          if (lane == 0) red[(k * T + t) * kRouterSegs + wid] = acc;
+        }
+      }
+    }
+#pragma unroll 1
+    for (int k = 2; k < n_mine; ++k) {
+      const int e = blockIdx.x + nblocks * k;
+      const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
       for (int t = 0; t < T; ++t) {
         const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx);
-        float acc = 0.0f;
-#pragma unroll 1
-        for (int i0 = lane; i0 < nvec; i0 += 256) {
-          uint4 wv[8], xv[8];
-          const bool have = (e == e_first) && (i0 == lane);  // warp-uniform: the chunk requested at kernel start
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            wv[u] = have ? wpre[u] : ((i0 + 32 * u < nvec) ? __ldg(wrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u));
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            xv[u] = (i0 + 32 * u < nvec) ? __ldg(xrow + i0 + 32 * u) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-            const uint32_t xw[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              acc = fmaf(bf16_bits_to_float(ww[q] & 0xffffu), bf16_bits_to_float(xw[q] & 0xffffu), acc);
-              acc = fmaf(bf16_bits_to_float(ww[q] >> 16), bf16_bits_to_float(xw[q] >> 16), acc);
-            }
-          }
-        }
-        const float sres = warp_sum(acc);
-        // eight copies = one full 32-byte sector: L2 holds it whole and never has to merge it with a stale
-        // copy from HBM when the other CTAs read it
-        if (lane < 8 && !(p.withhold && e == 0))
-          st_relaxed_u32(p.logits + ((size_t)t * E + e) * 8 + lane, tag | float_to_bf16_bits(sres));
+        const float acc = warp_sum(router_segment_partial(wrow, xrow, nvec, wid, lane));
+        if (lane == 0) red[(k * T + t) * kRouterSegs + wid] = acc;
+      }
+    }
+    ld_csync();
+    if (tid < n_mine * T) {
+      const int k = tid / T, t = tid - k * T;
+      const int e = blockIdx.x + nblocks * k;
+      const int nseg = min(kRouterSegs, (nvec + 31) >> 5);
+      float total = 0.0f;
+      for (int s = 0; s < nseg; ++s) total += red[(k * T + t) * kRouterSegs + s];
+      // eight copies = one full 32-byte sector: L2 holds it whole and never has to merge it with a stale copy
+      // from HBM when the other CTAs read it
+      if (!(p.withhold && e == 0)) {
+        uint32_t* dst = p.logits + ((size_t)t * E + e) * 8;
+        const uint32_t word = tag | float_to_bf16_bits(total);
+        st_relaxed_v4(dst, word);
+        st_relaxed_v4(dst + 4, word);
       }
     }
   }
   LD_STAMP(2);
-  __syncthreads();  // wait_failed, the zero page and the cleared task counts are in place
-  // Launch count for the next launch.  Every thread of this CTA has read the count by now, so the CTA can sign
-  // in; the last CTA of the grid to do so bumps the count (the tags of THIS launch live in registers already)
-  // and clears the sign-in counter.  Doing it here, not at the end, keeps the atomic's round trip off the tail.
+  // Launch count for the next launch.  Every consumer thread of this CTA has read the count (they all passed
+  // the barriers above), so the CTA can sign in; the last CTA of the grid to do so bumps the count (the tags of
+  // THIS launch live in registers already) and clears the sign-in counter.
   if (tid == 0) {
     if (atomicAdd(p.sync + 2, 1) == nblocks - 1) {
       p.sync[4] = epoch + 1;
@@ -908,356 +812,291 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
 
-  {
-    // ---- phase 2a: routing of every row, repeated by every CTA (one warp per row); the logits arrive as
-    // hand-over words, so this is also where the CTA waits for the router warps of the other CTAs
-    if (wid < T) {
-      bool ok;
-      ok = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, p.n_group, p.topk_group,
-                           vals + wid * E, lgs + wid * E, keys + wid * E, gsc + wid * 64, lane, LD_DBG_PTR);
-      if (!ok && lane == 0) {
-        wait_failed = 1;
-        atomicExch(p.sync + 3, 1);
-      }
+  // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
+  // so this is also where the CTA waits for the router threads of the other CTAs
+  if (wid < T) {
+    const bool okr = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, vals + wid * E,
+                                     lgs + wid * E, keys + wid * E, lane);
+    if (!okr && lane == 0) {
+      flags[0] = 1;
+      atomicExch(p.sync + 3, 1);
     }
-    __syncthreads();
-    if (p.family == 2) {
-      ld_sigmoid_scores(T, E, p.rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
-      __syncthreads();
-    }
-    LD_STAMP(20);
-    if (wait_failed == 0) ld_rank_select(keys, T, E, K, sel_idx);
-    __syncthreads();
-    LD_STAMP(21);
-    if (wid < T && wait_failed == 0)
-      ld_finish_row(vals + wid * E, lgs + wid * E, K, p.family, p.renorm, p.scale, sel_idx + wid * K,
-                    meta->w + wid * K, meta->idx + wid * K, lane);
-    LD_STAMP(3);
-    if (T == 1) {
-      // one token: its K experts are distinct, so slot a is task a
-      if (tid < K) {  // lanes of warp 0, which has just written meta->idx
-        meta->task_expert[tid] = meta->idx[tid];
-        meta->task_cnt[tid] = 1;
-        meta->task_rows[tid][0] = (unsigned char)tid;
-      }
-      if (tid == 0) {
-        meta->n_routed = K;
-        meta->n_tasks = K + (p.n_shared ? 1 : 0);
-        if (p.n_shared) {
-          meta->task_expert[K] = 0;
-          meta->task_cnt[K] = 1;
-          meta->task_rows[K][0] = (unsigned char)R;
-        }
-      }
-    }
-    __syncthreads();
-    LD_STAMP(4);
-    alive = (wait_failed == 0);
   }
-  if (alive) {
-    if (blockIdx.x == 0 && tid < R) {
-      if (p.weights) p.weights[tid] = meta->w[tid];
-      if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
+  ld_csync();
+  LD_STAMP(3);
+  if (p.family == 2) {
+    ld_sigmoid_scores(T, E, p.rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
+    ld_csync();
+  }
+  if (flags[0] == 0) ld_rank_select(keys, T, E, K, sel_idx);
+  ld_csync();
+  LD_STAMP(4);
+  if (wid < T && flags[0] == 0)
+    ld_finish_row(vals + wid * E, lgs + wid * E, K, p.family, p.renorm, p.scale, sel_idx + wid * K, meta->w + wid * K,
+                  meta->idx + wid * K, lane);
+  if (T == 1) {
+    // one token: its K experts are distinct, so slot a is task a
+    if (tid < K) {  // lanes of warp 0: each reads back the slot it has just written itself
+      meta->task_expert[tid] = meta->idx[tid];
+      meta->task_cnt[tid] = 1;
+      meta->task_rows[tid][0] = (unsigned char)tid;
     }
-    if (TT > 1 && T > 1) {
-      // ---- phase 2b: tasks = distinct experts in order of first use; a task's rows in row order
-      if (tid < R) {
-        const int e = meta->idx[tid];
-        int rk = 0;
-        for (int r = 0; r < tid; ++r) rk += (meta->idx[r] == e);
-        meta->rank[tid] = rk;
+    if (tid == 0) {
+      meta->n_routed = K;
+      meta->n_tasks = K + (p.n_shared ? 1 : 0);
+      if (p.n_shared) {
+        meta->task_expert[K] = 0;
+        meta->task_cnt[K] = 1;
+        meta->task_rows[K][0] = (unsigned char)R;
       }
-      __syncthreads();
-      if (tid < R) {
-        const int e = meta->idx[tid];
-        int r0 = 0;
-        while (meta->idx[r0] != e) ++r0;  // first row of this expert (r0 <= tid)
-        int tk = 0;
-        for (int r = 0; r < r0; ++r) tk += (meta->rank[r] == 0);
-        const int rk = meta->rank[tid];
-        if (rk == 0) meta->task_expert[tk] = e;
-        if (rk < kLdMaxT) meta->task_rows[tk][rk] = (unsigned char)tid;
-        atomicAdd(&meta->task_cnt[tk], 1);
-      }
-      if (tid == 0) {
-        int n = 0;
-        for (int r = 0; r < R; ++r) n += (meta->rank[r] == 0);
-        meta->n_routed = n;
-        meta->n_tasks = n + (p.n_shared ? 1 : 0);
-        if (p.n_shared) {
-          meta->task_expert[n] = 0;
-          meta->task_cnt[n] = T;
-          for (int t = 0; t < T; ++t) meta->task_rows[n][t] = (unsigned char)(R + t);
-        }
-      }
-      __syncthreads();
     }
-    const int n_tasks = meta->n_tasks;
-    const int n_routed = meta->n_routed;
-    LD_STAMP(5);
+  }
+  ld_csync();
+  if (T > 1 && flags[0] == 0) {
+    // tasks = distinct experts in order of first use; a task's rows in row order
+    if (tid < R) {
+      const int e = meta->idx[tid];
+      int rk = 0;
+      for (int r = 0; r < tid; ++r) rk += (meta->idx[r] == e);
+      meta->rank[tid] = rk;
+    }
+    ld_csync();
+    if (tid < R) {
+      const int e = meta->idx[tid];
+      int r0 = 0;
+      while (meta->idx[r0] != e) ++r0;  // first row of this expert (r0 <= tid)
+      int tk = 0;
+      for (int r = 0; r < r0; ++r) tk += (meta->rank[r] == 0);
+      const int rk = meta->rank[tid];
+      if (rk == 0) meta->task_expert[tk] = e;
+      if (rk < kLdMaxT) meta->task_rows[tk][rk] = (unsigned char)tid;
+      atomicAdd(&meta->task_cnt[tk], 1);
+    }
+    if (tid == 0) {
+      int n = 0;
+      for (int r = 0; r < R; ++r) n += (meta->rank[r] == 0);
+      meta->n_routed = n;
+      meta->n_tasks = n + (p.n_shared ? 1 : 0);
+      if (p.n_shared) {
+        meta->task_expert[n] = 0;
+        meta->task_cnt[n] = T;
+        for (int t = 0; t < T; ++t) meta->task_rows[n][t] = (unsigned char)(R + t);
+      }
+    }
+    ld_csync();
+  } else if (T > 1) {
+    ld_csync();
+    ld_csync();
+  }
+  // the producer may read the task list now (it also looks at flags[0])
+  if (tid == 0) ld_mbar_arrive(ld_route_bar(bars));
+  LD_STAMP(5);
 
-    // ---- phase 2c: gate/up + SwiGLU; items (task, 16-row tile) dealt to groups of four warps over the grid
-    {
-      constexpr int WK = 4;
-      const int gid = wid >> 2, wk = wid & 3;
-      const int nq = ngd >> 2;
-      const int nq_w = (nq > wk) ? (nq - wk + WK - 1) / WK : 0;
-      const int ntiles = f >> 4;
-      const int nitems = n_tasks * ntiles;
-      const int sc_stride = qmm_sc_stride(ngd);
-      unsigned char* sraw = smem + lay.sc + gid * (4 * 16 * sc_stride);
-      const int xs_stride = qmm_xs_stride(d);
-      int gu_uses = 0;  // how often this team's slot has been filled (parity of its barrier)
-      for (int it = gid * nblocks + blockIdx.x; it < nitems; it += nblocks * 4) {
-        const int a = it / ntiles;
-        const int n0 = (it - a * ntiles) << 4;
-        const bool is_sh = a >= n_routed;
-        const LdBank bank = ld_pick(p.gu, p.sgu, is_sh);
-        const int e = meta->task_expert[a];
-        const int cnt = meta->task_cnt[a];
-        uint2 wbuf[BULK ? 1 : 2][4][2][2];
-        const uint32_t* wp[2][2];
-        if (!BULK) ld_issue_w<2, BULK ? 1 : 2>(wbuf, wp, bank, e, f, d >> 3, n0, g, tig, wk, WK, nq_w);
-        ld_group_sync(gid, WK);  // the previous item is done with the group's scale area (and weight slot)
-        if (BULK) {
-          // rows 0..15 gate, 16..31 up: eight lanes of each of the team's warps copy one row each
-          if (gu_uses > 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          if (lane < 8) {
-            const int r = wk * 8 + lane;
-            const uint32_t* src = bank.w[r >> 4] + ((size_t)e * f + n0 + (r & 15)) * (d >> 3);
-            ld_mbar_expect_tx(bars + gid * 8, d >> 1);
-            ld_bulk_g2s(ld_smem_u32(gslots + (gid * 32 + r) * rs_g), src, d >> 1, bars + gid * 8);
-          }
-        }
-        ld_issue_sc<2>(bank, e, f, ngd, n0, sraw, sc_stride, tid & 127, 128);
-        // token of a task row: routed row r belongs to token r / K, shared row R + t to token t
-        const bool tok_ok = tok_g < cnt;
-        int trow = 0;
-        if (tok_ok) {
-          const int r = meta->task_rows[a][tok_g];
-          trow = is_sh ? r - R : r / K;
-        }
-        int srow_c[2];
+  LdCtx c;
+  c.smem = smem;
+  c.meta = meta;
+  c.flags = flags;
+  c.red = red;
+  c.bars = bars;
+  c.ring = ring;
+  c.tag = tag;
+  c.team = wid >> 2;
+  c.wk = wid & 3;
+  c.lane = lane;
+  c.g = g;
+  c.tig = tig;
+  c.depth = dbase + (c.team < dextra ? 1 : 0);
+  c.slot0 = c.team * dbase + min(c.team, dextra);
+  c.use = 0;
+  c.slot = 0;
+  c.itn = 0;
+  c.alive = (flags[0] == 0);
+  const int n_tasks = c.alive ? meta->n_tasks : 0;
+  const int n_routed = c.alive ? meta->n_routed : 0;
+  if (c.alive && blockIdx.x == 0 && tid < R) {
+    if (p.weights) p.weights[tid] = meta->w[tid];
+    if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
+  }
+
+  // ---- gate/up + SwiGLU: item i = blockIdx.x + q * grid, the CTA's q-th item goes to team q % 4
+  {
+    const int items = n_tasks * ntf;
+    const int nq = (items > (int)blockIdx.x) ? (items - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
+    const int xs_stride = qmm_xs_stride(d);
+    for (int q = c.team; q < nq; q += kLdTeams) {
+      const int i = (int)blockIdx.x + q * nblocks;
+      const int ao = i / ntf, tile = i - ao * ntf;
+      const int a = p.n_shared ? (ao == 0 ? n_routed : ao - 1) : ao;
+      const bool is_sh = a >= n_routed;
+      const int n0 = tile << 4;
+      const int cnt = meta->task_cnt[a];
+      // token of a task row: routed row r belongs to token r / K, shared row R + t to token t
+      const bool tok_ok = tok_g < cnt;
+      int trow = 0;
+      if (tok_ok) {
+        const int r = meta->task_rows[a][tok_g];
+        trow = is_sh ? r - R : r / K;
+      }
+      int srow_c[2];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int sl = (2 * tig + c) % TT;
-          srow_c[c] = -1;
-          if (sl < cnt) {
-            const int r = meta->task_rows[a][sl];
-            srow_c[c] = is_sh ? r - R : r / K;
+      for (int cc = 0; cc < 2; ++cc) {
+        const int sl = (2 * tig + cc) % TT;
+        srow_c[cc] = -1;
+        if (sl < cnt) {
+          const int r = meta->task_rows[a][sl];
+          srow_c[cc] = is_sh ? r - R : r / K;
+        }
+      }
+      float acc[2][4];
+      ld_item<TT, false>(c, acc, is_sh ? p.sgu : p.gu, meta->task_expert[a], f, d >> 3, n0,
+                         lay.xs + trow * xs_stride + tig * 32, lay.zero, tok_ok, slot_g, xsum, T, srow_c);
+      if (c.alive && c.wk == 0) {
+        const int epi = is_sh ? p.sepi : p.epi;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = 2 * tig + (j & 1);
+          const bool writer = (TT == 8) || (col < TT);
+          if (writer && col < cnt) {
+            const int dst = meta->task_rows[a][col];
+            const float inv = isig[is_sh ? dst - R : dst / K];
+            const float gv = acc[0][j] * inv, uv = acc[1][j] * inv;
+            const float v = (epi == 2) ? swiglu_per_op(gv, uv) : swiglu_cpu_contract(gv, uv);
+            st_relaxed_u32(p.h + (size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
           }
         }
-        LD_STAMP(11);
-        cp_async_wait_all();
-        if (BULK && !ld_mbar_wait(bars + gid * 8, gu_uses & 1)) {
-          wait_failed = 1;
-          atomicExch(p.sync + 3, 1);
+      }
+    }
+  }
+  LD_STAMP(6);
+
+  // ---- down projection: items (task, 32 columns) in task-major order, cut into equal contiguous ranges per
+  // CTA; the CTA stages the h rows of the tasks its range touches (this is where it waits for the gate/up
+  // tiles of the other CTAs)
+  const long long items_dn = (long long)n_tasks * ntd;
+  const int dn_lo = (int)(items_dn * blockIdx.x / nblocks), dn_hi = (int)(items_dn * (blockIdx.x + 1) / nblocks);
+  ld_csync();  // every team is done with the token rows
+  if (tid == 0) {
+    int n = 0;
+    if (c.alive && dn_hi > dn_lo) {
+      for (int a = dn_lo / ntd; a <= (dn_hi - 1) / ntd; ++a)
+        for (int r = 0; r < meta->task_cnt[a] && r < kLdMaxT; ++r) {
+          const int row = meta->task_rows[a][r];
+          if (n < p.hrows) {
+            meta->hlist[n] = (unsigned char)row;
+            meta->hloc[row] = (unsigned char)n;
+          }
+          ++n;
         }
-        ++gu_uses;
-        ld_group_sync(gid, WK);
-        LD_STAMP(12);
-        float acc[2][4];
-        if (BULK)
-          ld_smem_mainloop<2, 2>(acc, gslots + gid * 32 * rs_g, rs_g, smem, lay.xs + trow * xs_stride + tig * 32,
-                                 zpage, xsum, T, srow_c, sraw, sc_stride, wk, WK, nq, g, tig);
-        else
-          ld_mainloop<2, BULK ? 1 : 2, TT, 2>(acc, wbuf, wp, smem, lay.xs + trow * xs_stride + tig * 32, tok_ok, zpage,
-                                              slot_g, xsum, T, srow_c, sraw, sc_stride, wk, WK, nq_w, g, tig);
-        LD_STAMP(13);
-        ld_reduce_fold<2, TT>(acc, red, gid, wk, WK, lane);
-        LD_STAMP(14);
-        if (wk == 0) {
-          const int epi = is_sh ? p.sepi : p.epi;
+      if (n > p.hrows) {  // cannot happen with the host's sizing; never overrun shared memory
+        flags[0] = 1;
+        atomicExch(p.sync + 3, 1);
+        n = 0;
+      }
+    }
+    meta->n_h = n;
+  }
+  ld_csync();
+  const int n_h = meta->n_h;
+  ld_stage_rows<true>(xs, qmm_xs_stride(f), xsum, p.hrows, isig, rowmax, p.h, f, meta->hlist, n_h, f >> 3, tag, flags,
+                      p.sync + 3);
+  LD_STAMP(7);
+  if (flags[0]) c.alive = false;
+  {
+    const int nq = c.alive ? dn_hi - dn_lo : 0;
+    const int xs_stride = qmm_xs_stride(f);
+    for (int q = c.team; q < nq; q += kLdTeams) {
+      const int i = dn_lo + q;
+      const int a = i / ntd, tile = i - a * ntd;
+      const bool is_sh = a >= n_routed;
+      const int n0 = tile << 5;
+      const int cnt = meta->task_cnt[a];
+      const bool tok_ok = tok_g < cnt;
+      const int srow = tok_ok ? (int)meta->hloc[meta->task_rows[a][tok_g]] : 0;
+      int srow_c[2];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int sl = (2 * tig + cc) % TT;
+        srow_c[cc] = (sl < cnt) ? (int)meta->hloc[meta->task_rows[a][sl]] : -1;
+      }
+      float acc[2][4];
+      ld_item<TT, true>(c, acc, is_sh ? p.sdn : p.dn, meta->task_expert[a], d, f >> 3, n0,
+                        lay.xs + srow * xs_stride + tig * 32, lay.zero, tok_ok, slot_g, xsum, p.hrows, srow_c);
+      if (c.alive && c.wk == 0) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int col = 2 * tig + (j & 1);
             const bool writer = (TT == 8) || (col < TT);
             if (writer && col < cnt) {
-              const float v = (epi == 2) ? swiglu_per_op(acc[0][j], acc[1][j]) : swiglu_cpu_contract(acc[0][j], acc[1][j]);
               const int dst = meta->task_rows[a][col];
-              st_relaxed_u32(p.h + (size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
+              const float v = acc[m][j] * isig[meta->hloc[dst]];
+              st_relaxed_u32(p.y + (size_t)dst * d + n0 + m * 16 + g + ((j >> 1) ? 8 : 0),
+                             tag | float_to_bf16_bits(v));
             }
           }
-        }
-      }
-    }
-
-    LD_STAMP(6);
-    // ---- phase 3 set-up.  The CTA owns the 16-column output tiles blockIdx.x, blockIdx.x + grid, ...; an item
-    // is (tile, task).  The register-pipelined form takes all of its tiles as one batch, so that the warps have
-    // many independent items and few idle rounds; the bulk-copy form has shared-memory slots for one tile.
-    const int nqf = ngf >> 2;
-    const int ntiles_d = d >> 4;
-    const int ntile_mine = ((int)blockIdx.x < ntiles_d) ? (ntiles_d - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
-    const int tb = BULK ? 1 : ntile_mine;  // tiles per batch
-    int wkc = 1;  // warps that split K for one item
-    {
-      const int items = (tb < ntile_mine ? tb : ntile_mine) * n_tasks;
-      int best = 1 << 30;
-      for (int c = 4; c >= 1; c >>= 1) {  // ties go to the smaller split (fewer partial sums)
-        if (c > nqf) continue;
-        const int groups = kLdWarps / c;
-        // a round of items costs its quads plus a fixed latency of about four quads
-        const int cost = ((items + groups - 1) / groups) * ((nqf + c - 1) / c + 4);
-        if (cost <= best) {
-          best = cost;
-          wkc = c;
-        }
-      }
-    }
-    const int ngrp = kLdWarps / wkc;
-    const int gid = wid / wkc, wk = wid % wkc;
-    const int nq_w = (nqf > wk) ? (nqf - wk + wkc - 1) / wkc : 0;
-    const int sc_stride = qmm_sc_stride(ngf);
-    unsigned char* sraw = smem + lay.sc + gid * (2 * 16 * sc_stride);
-    const int gtid = tid - gid * wkc * 32;
-    const int nb0 = tb < ntile_mine ? tb : ntile_mine;  // tiles of the first batch
-    const int pre_tl = gid / n_tasks, pre_a = gid - pre_tl * n_tasks;  // the group's first item
-    const int pre_n0 = ((int)blockIdx.x + pre_tl * nblocks) << 4;
-
-    uint2 wbuf[BULK ? 1 : DPD][4][1][2];
-    const uint32_t* wp[1][2];
-    // the first item's packed weights and scales depend on the routing only: stream them before waiting for h
-    const bool pre = gid < nb0 * n_tasks;
-    if (BULK) {
-      // all tasks of the CTA's first tile: warp a copies the 16 rows of task a into down slot a
-      if ((int)blockIdx.x < ntiles_d && wid < n_tasks && lane < 16) {
-        const LdBank bank = ld_pick(p.dn, p.sdn, wid >= n_routed);
-        const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + (blockIdx.x << 4) + lane) * (f >> 3);
-        ld_mbar_expect_tx(bars + (4 + wid) * 8, f >> 1);
-        ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
-      }
-    } else if (pre) {
-      ld_issue_w<1, BULK ? 1 : DPD>(wbuf, wp, ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a],
-                                          d, f >> 3, pre_n0, g, tig, wk, wkc, nq_w);
-    }
-    __syncthreads();  // every group of this CTA is done with the gate/up scale areas, which the next copies reuse
-    if (pre)
-      ld_issue_sc<1>(ld_pick(p.dn, p.sdn, pre_a >= n_routed), meta->task_expert[pre_a], d, ngf, pre_n0, sraw,
-                     sc_stride, gtid, wkc * 32);
-    LD_STAMP(7);
-    {
-      // ---- phase 3: stage every h row (hand-over words: this is where the CTA waits for the gate/up tiles of
-      // the other CTAs), then 16 output columns at a time: all tasks, then the combine
-      const int xs_stride = qmm_xs_stride(f);
-      const bool good = ld_stage_rows<true>(xs, xs_stride, xsum, rtot, p.h, f, rtot, f >> 3, tag);
-      if (!good) {
-        wait_failed = 1;
-        atomicExch(p.sync + 3, 1);
-      }
-      __syncthreads();
-      LD_STAMP(9);
-      alive = (wait_failed == 0);
-    }
-    if (alive) {
-      const int xs_stride = qmm_xs_stride(f);
-      int d_uses = 0;  // how often the down slots have been filled (parity of their barriers)
-      for (int b0 = 0; b0 < ntile_mine; b0 += tb, ++d_uses) {
-        const int nb = (tb < ntile_mine - b0) ? tb : ntile_mine - b0;  // tiles of this batch
-        if (BULK && d_uses > 0) {
-          // the previous tile ended with a CTA-wide barrier: every slot is free again
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          if (wid < n_tasks && lane < 16) {
-            const LdBank bank = ld_pick(p.dn, p.sdn, wid >= n_routed);
-            const int n0b = ((int)blockIdx.x + b0 * nblocks) << 4;
-            const uint32_t* src = bank.w[0] + ((size_t)meta->task_expert[wid] * d + n0b + lane) * (f >> 3);
-            ld_mbar_expect_tx(bars + (4 + wid) * 8, f >> 1);
-            ld_bulk_g2s(ld_smem_u32(dslots + (wid * 16 + lane) * rs_d), src, f >> 1, bars + (4 + wid) * 8);
-          }
-        }
-        for (int item = gid; item < nb * n_tasks; item += ngrp) {
-          const int tl = item / n_tasks;
-          const int a = item - tl * n_tasks;
-          const int n0 = ((int)blockIdx.x + (b0 + tl) * nblocks) << 4;
-          const bool is_sh = a >= n_routed;
-          const int cnt = meta->task_cnt[a];
-          if (!(pre && b0 == 0 && item == gid)) {
-            const LdBank bank = ld_pick(p.dn, p.sdn, is_sh);
-            if (!BULK)
-              ld_issue_w<1, BULK ? 1 : DPD>(wbuf, wp, bank, meta->task_expert[a], d, f >> 3, n0, g, tig, wk, wkc,
-                                                  nq_w);
-            ld_group_sync(gid, wkc);  // the previous item is done with the group's scale area
-            ld_issue_sc<1>(bank, meta->task_expert[a], d, ngf, n0, sraw, sc_stride, gtid, wkc * 32);
-          }
-          const bool tok_ok = tok_g < cnt;
-          const int srow = tok_ok ? meta->task_rows[a][tok_g] : 0;
-          int srow_c[2];
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int sl = (2 * tig + c) % TT;
-            srow_c[c] = (sl < cnt) ? (int)meta->task_rows[a][sl] : -1;
-          }
-          LD_STAMP(15);
-          cp_async_wait_all();
-          if (BULK && !ld_mbar_wait(bars + (4 + a) * 8, d_uses & 1)) {
-            wait_failed = 1;  // the results of this launch are void; the status word says so
-            atomicExch(p.sync + 3, 1);
-          }
-          ld_group_sync(gid, wkc);
-          LD_STAMP(16);
-          float acc[1][4];
-          if (BULK)
-            ld_smem_mainloop<1, 4>(acc, dslots + a * 16 * rs_d, rs_d, smem, lay.xs + srow * xs_stride + tig * 32, zpage,
-                                   xsum, rtot, srow_c, sraw, sc_stride, wk, wkc, nqf, g, tig);
-          else
-            ld_mainloop<1, BULK ? 1 : DPD, TT, 4>(acc, wbuf, wp, smem, lay.xs + srow * xs_stride + tig * 32, tok_ok,
-                                                        zpage, slot_g, xsum, rtot, srow_c, sraw, sc_stride, wk, wkc,
-                                                        nq_w, g, tig);
-          LD_STAMP(17);
-          ld_reduce_fold<1, TT>(acc, red, gid, wk, wkc, lane);
-          LD_STAMP(18);
-          if (wk == 0) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = 2 * tig + (j & 1);
-              const bool writer = (TT == 8) || (col < TT);
-              if (writer && col < cnt)
-                ybuf[(tl * rtot + (int)meta->task_rows[a][col]) * 16 + g + ((j >> 1) ? 8 : 0)] = acc[0][j];
-            }
-          }
-        }
-        __syncthreads();
-        LD_STAMP(19);
-        // ordered combine: thread (tile, token, column) walks the K slots; projected values are rounded to T
-        // first, as the separate-kernel path stores them
-        for (int idx = tid; idx < nb * T * 16; idx += kLdThreads) {
-          const int tl = idx / (T * 16);
-          const int t = (idx - tl * T * 16) >> 4, n = idx & 15;
-          const float* yb = ybuf + tl * rtot * 16;
-          const int mode = p.combine_mode;
-          float a0 = 0.0f;
-#pragma unroll 1
-          for (int i = 0; i < K; ++i) {
-            float wi = meta->w[t * K + i];
-            if (p.out_flags & 2) wi = round_bf16(wi);
-            const float v0 = round_bf16(yb[(t * K + i) * 16 + n]);
-            if (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_T) {
-              a0 = fmaf(wi, v0, a0);
-            } else if (mode == ZMOE_COMBINE_FP32_NO_FMA || mode == ZMOE_COMBINE_NO_FMA) {
-              a0 = __fadd_rn(a0, __fmul_rn(wi, v0));
-            } else if (mode == ZMOE_COMBINE_EXACT) {
-              wi = round_bf16(wi);
-              a0 = round_bf16(__fadd_rn(a0, round_bf16(__fmul_rn(wi, v0))));
-            } else {
-              a0 = round_bf16(__fadd_rn(a0, __fmul_rn(wi, v0)));
-            }
-          }
-          const size_t oo = (size_t)t * d + (((int)blockIdx.x + (b0 + tl) * nblocks) << 4) + n;
-          const bool fp32_mode = (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_FP32_NO_FMA);
-          if (fp32_mode && !(p.out_flags & 1)) {
-            reinterpret_cast<float*>(p.out)[oo] = a0;
-          } else {
-            a0 = round_bf16(a0);
-            if (p.n_shared) a0 = __fadd_rn(a0, round_bf16(yb[(R + t) * 16 + n]));
-            reinterpret_cast<__nv_bfloat16*>(p.out)[oo] = __float2bfloat16_rn(a0);
-          }
-        }
-        __syncthreads();
       }
     }
   }
+  LD_STAMP(8);
 
-  LD_STAMP(10);
+  // ---- ordered combine: 64 output elements per unit, units dealt over the grid; a thread waits for the K
+  // (+ shared) projected values of its element (rounded to T, as the separate-kernel path stores them)
+  if (flags[0] == 0) {
+    const int units = (T * d) >> 6;
+    const int mode = p.combine_mode;
+    for (int u = (int)blockIdx.x + nblocks * (tid >> 6); u < units; u += nblocks * (kLdConsumers >> 6)) {
+      const int o = (u << 6) + (tid & 63);
+      const int t = o / d, n = o - t * d;
+      uint32_t yw[kLdMaxK + 1];
+      int spins = 0;
+      bool okc;
+      do {
+        okc = true;
+#pragma unroll
+        for (int i = 0; i < kLdMaxK + 1; ++i) {
+          yw[i] = tag;
+          if (i < K) yw[i] = ld_relaxed_u32(p.y + (size_t)(t * K + i) * d + n);
+          if (i == kLdMaxK && p.n_shared) yw[i] = ld_relaxed_u32(p.y + (size_t)(R + t) * d + n);
+          okc = okc && ((yw[i] & 0xffff0000u) == tag);
+        }
+        ++spins;
+      } while (!okc && spins < kLdSpinLimit && !((spins & 1023) == 1023 && flags[0]));
+      if (!okc) {
+        flags[0] = 1;
+        atomicExch(p.sync + 3, 1);
+        break;
+      }
+      float a0 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kLdMaxK; ++i) {
+        if (i < K) {
+          float wi = meta->w[t * K + i];
+          if (p.out_flags & 2) wi = round_bf16(wi);
+          const float v0 = bf16_bits_to_float(yw[i] & 0xffffu);
+          if (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_T) {
+            a0 = fmaf(wi, v0, a0);
+          } else if (mode == ZMOE_COMBINE_FP32_NO_FMA || mode == ZMOE_COMBINE_NO_FMA) {
+            a0 = __fadd_rn(a0, __fmul_rn(wi, v0));
+          } else if (mode == ZMOE_COMBINE_EXACT) {
+            wi = round_bf16(wi);
+            a0 = round_bf16(__fadd_rn(a0, round_bf16(__fmul_rn(wi, v0))));
+          } else {
+            a0 = round_bf16(__fadd_rn(a0, __fmul_rn(wi, v0)));
+          }
+        }
+      }
+      const bool fp32_mode = (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_FP32_NO_FMA);
+      if (fp32_mode && !(p.out_flags & 1)) {
+        reinterpret_cast<float*>(p.out)[o] = a0;
+      } else {
+        a0 = round_bf16(a0);
+        if (p.n_shared) a0 = __fadd_rn(a0, bf16_bits_to_float(yw[kLdMaxK] & 0xffffu));
+        reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(a0);
+      }
+    }
+  }
+  LD_STAMP(9);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1283,19 +1122,36 @@ static int ld_sm_count(int* out) {
   return ZMOE_OK;
 }
 
-// Output tiles per CTA that the shared-memory layout provides for: right for grids of 128 CTAs or more.
-static int ld_tiles_assumed(int d_model) { return (d_model / 16 + 127) / 128; }
+struct LdPlan {
+  int hrows, slots;
+  LdSmem lay;
+};
 
-// Why a block shape cannot take the one-launch path (nullptr: it can).
-static const char* ld_unsupported(const zmoe_layer_desc* L, int T) {
+// Sizes that depend on the grid: the h rows one CTA's share of the down projection can touch, and how many
+// ring stages fit beside everything else.  Returns why the shape cannot take the one-launch path (nullptr: it can).
+static const char* ld_plan(const zmoe_layer_desc* L, int T, int sms, LdPlan* out) {
   if (L->qmode != ZMOE_Q_AFFINE4 || L->group_size != 64) return "needs 4-bit affine weights with group size 64";
   if (T < 1 || T > kLdMaxT) return "takes 1..8 tokens";
   if (L->top_k < 1 || L->top_k > kLdMaxK) return "takes top_k <= 8";
   if (L->E < L->top_k || L->E > 256) return "takes at most 256 experts";
   if (L->d_model % 256 != 0 || L->d_ff % 256 != 0) return "needs d_model and d_ff to be multiples of 256";
   if (L->n_shared < 0 || L->n_shared > 1) return "takes at most one shared expert";
-  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared, ld_tiles_assumed(L->d_model));
-  if (lay.total > 220 * 1024) return "needs more shared memory than an SM has";
+  if (sms * kLdMaxMine < L->E) return "needs a GPU with more SMs for this many experts";
+  const int rtot = T * L->top_k + (L->n_shared ? T : 0);
+  int routed_max = T * L->top_k;
+  if (routed_max > L->E) routed_max = L->E;
+  const long long items = (long long)(routed_max + (L->n_shared ? 1 : 0)) * (L->d_model / 32);
+  const int per_cta = (int)((items + sms - 1) / sms);
+  const int span = per_cta > 0 ? (per_cta - 1) / (L->d_model / 32) + 2 : 1;  // tasks a contiguous range can touch
+  int hrows = span * T;
+  if (hrows > rtot) hrows = rtot;
+  const LdSmem fixed = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, hrows, 0);
+  int slots = (kLdSmemLimit - fixed.total) / kLdSlotBytes;
+  if (slots > kLdTeams * kLdMaxDepth) slots = kLdTeams * kLdMaxDepth;
+  if (slots < 2 * kLdTeams) return "needs more shared memory than an SM has";
+  out->hrows = hrows;
+  out->slots = slots;
+  out->lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, hrows, slots);
   return nullptr;
 }
 
@@ -1303,10 +1159,14 @@ static size_t ld_ws_logits_off() { return 256; }
 static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
   return (ld_ws_logits_off() + (size_t)T * L->E * 32 + 255) & ~(size_t)255;
 }
+static size_t ld_ws_y_off(const zmoe_layer_desc* L, int T) {
+  const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
+  return (ld_ws_h_off(L, T) + rows * L->d_ff * 4 + 255) & ~(size_t)255;
+}
 
-template <int TT, bool BULK, int DPD>
+template <int TT>
 static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = layer_decode_kernel<TT, BULK, DPD>;
+  auto kern = layer_decode_kernel<TT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
@@ -1339,15 +1199,40 @@ using namespace zmoe;
 extern "C" {
 
 size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T) {
-  if (!L || ld_unsupported(L, T)) return 0;
+  if (!L) return 0;
+  int sms = 0;
+  if (ld_sm_count(&sms) != ZMOE_OK) return 0;
+  LdPlan plan;
+  if (ld_plan(L, T, sms, &plan)) return 0;
   const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
-  return ld_ws_h_off(L, T) + rows * L->d_ff * 4;
+  return ld_ws_y_off(L, T) + rows * L->d_model * 4;
+}
+
+int zmoe_layer_decode_status(const void* workspace, int clear, void* stream) {
+  ZMOE_REQUIRE(workspace != nullptr, ZMOE_ERR_SHAPE, "zmoe_layer_decode_status: null workspace");
+  cudaStream_t st = (cudaStream_t)stream;
+  int word = 0;
+  int* dev = (int*)workspace + 3;
+  cudaError_t e = cudaMemcpyAsync(&word, dev, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode_status: %s", cudaGetErrorString(e));
+  if (word == 0) return ZMOE_OK;
+  if (clear) {
+    e = cudaMemsetAsync(dev, 0, sizeof(int), st);
+    if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode_status: %s", cudaGetErrorString(e));
+  }
+  return fail(ZMOE_ERR_TIMEOUT,
+              "zmoe_layer_decode: a bounded wait ran out in an earlier launch on this workspace (its output is void)");
 }
 
 int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
                       size_t workspace_bytes, float* weights, uint32_t* indices, void* out, void* stream) {
   ZMOE_REQUIRE(L && x && workspace && out, ZMOE_ERR_SHAPE, "zmoe_layer_decode: null pointer");
-  const char* why = ld_unsupported(L, T);
+  int sms = 0;
+  int rc = ld_sm_count(&sms);
+  if (rc != ZMOE_OK) return rc;
+  LdPlan plan;
+  const char* why = ld_plan(L, T, sms, &plan);
   ZMOE_REQUIRE(why == nullptr, ZMOE_ERR_UNSUPPORTED, "zmoe_layer_decode: the one-launch path %s", why);
   ZMOE_REQUIRE(L->router_w && L->routed.gate_w && L->routed.gate_scales && L->routed.gate_biases && L->routed.up_w &&
                    L->routed.up_scales && L->routed.up_biases && L->routed.down_w && L->routed.down_scales &&
@@ -1385,16 +1270,21 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   const zmoe_expert_bank* banks[2] = {&L->routed, L->n_shared ? &L->shared : nullptr};
   for (int i = 0; i < 2; ++i) {
     if (!banks[i]) continue;
-    const void* ptrs[9] = {banks[i]->gate_w,    banks[i]->gate_scales, banks[i]->gate_biases,
-                           banks[i]->up_w,      banks[i]->up_scales,   banks[i]->up_biases,
-                           banks[i]->down_w,    banks[i]->down_scales, banks[i]->down_biases};
-    for (int j = 0; j < 9; ++j)
-      ZMOE_REQUIRE(((uintptr_t)ptrs[j] % 8) == 0, ZMOE_ERR_ALIGN,
-                   "zmoe_layer_decode: packed weights, scales and biases must be 8-byte aligned");
+    const void* wptr[3] = {banks[i]->gate_w, banks[i]->up_w, banks[i]->down_w};
+    for (int j = 0; j < 3; ++j)
+      ZMOE_REQUIRE(((uintptr_t)wptr[j] % 16) == 0, ZMOE_ERR_ALIGN,
+                   "zmoe_layer_decode: packed weights must be 16-byte aligned (they are fetched by bulk copies)");
+    const void* sptr[6] = {banks[i]->gate_scales, banks[i]->gate_biases, banks[i]->up_scales,
+                           banks[i]->up_biases,   banks[i]->down_scales, banks[i]->down_biases};
+    for (int j = 0; j < 6; ++j)
+      ZMOE_REQUIRE(((uintptr_t)sptr[j] % 8) == 0, ZMOE_ERR_ALIGN,
+                   "zmoe_layer_decode: scales and biases must be 8-byte aligned");
   }
   const size_t need = zmoe_layer_decode_workspace_bytes(L, T);
   ZMOE_REQUIRE(workspace_bytes >= need, ZMOE_ERR_WORKSPACE, "zmoe_layer_decode: workspace of %zu bytes, need %zu",
                workspace_bytes, need);
+  ZMOE_REQUIRE(L->launch_mode == 0 || L->launch_mode == 1, ZMOE_ERR_UNSUPPORTED,
+               "zmoe_layer_decode: launch_mode %d", L->launch_mode);
 
   LdParams p;
   p.x = (const __nv_bfloat16*)x;
@@ -1429,66 +1319,26 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.sepi = L->shared_swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : 2;
   p.combine_mode = L->combine_mode;
   p.out_flags = L->out_flags;
-  ZMOE_REQUIRE(L->launch_mode == 0 || L->launch_mode == 1, ZMOE_ERR_UNSUPPORTED,
-               "zmoe_layer_decode: launch_mode %d", L->launch_mode);
   p.pdl = L->launch_mode;
-  // ZMOE_LD_TEST_WITHHOLD=1 (read once per process) makes the bounded waits run out on purpose: the kernel must
-  // end by itself with the status word set and leave the context usable
-  static const bool withhold = getenv("ZMOE_LD_TEST_WITHHOLD") != nullptr && atoi(getenv("ZMOE_LD_TEST_WITHHOLD")) != 0;
-  p.withhold = withhold ? 1 : 0;
+  p.withhold = (L->debug_flags & ZMOE_DEBUG_WITHHOLD_LOGIT) ? 1 : 0;
+  p.stamps = (long long*)L->debug_stamps;
+  p.hrows = plan.hrows;
+  p.slots = plan.slots;
   unsigned char* ws = (unsigned char*)workspace;
   p.sync = (int*)ws;
   p.logits = (uint32_t*)(ws + ld_ws_logits_off());
   p.h = (uint32_t*)(ws + ld_ws_h_off(L, T));
+  p.y = (uint32_t*)(ws + ld_ws_y_off(L, T));
   p.weights = weights;
   p.indices = indices;
   p.out = out;
 
-  int sms = 0;
-  int rc = ld_sm_count(&sms);
-  if (rc != ZMOE_OK) return rc;
-  p.tiles_per_cta = ld_tiles_assumed(L->d_model);
-  ZMOE_REQUIRE((L->d_model / 16 + sms - 1) / sms <= p.tiles_per_cta, ZMOE_ERR_UNSUPPORTED,
-               "zmoe_layer_decode: this GPU has %d SMs, the one-launch path is laid out for 128 or more", sms);
-  const LdSmem lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, L->n_shared, p.tiles_per_cta);
   cudaStream_t st = (cudaStream_t)stream;
-  p.bulk_off = 0;
-  p.g_slots = 0;
-  if (T == 1) {
-    // bulk-copy variant: every tensor 16-byte aligned and its shared-memory slots fit beside the rest
-    // ZMOE_LD_BULK=1 / ZMOE_LD_NO_BULK=1 force the choice (read once per process)
-    static const bool force_on = getenv("ZMOE_LD_BULK") != nullptr && atoi(getenv("ZMOE_LD_BULK")) != 0;
-    static const bool force_off = getenv("ZMOE_LD_NO_BULK") != nullptr && atoi(getenv("ZMOE_LD_NO_BULK")) != 0;
-    const bool no_bulk = force_off || !(force_on || kLdBulkByDefault);
-    bool aligned = true;
-    for (int i = 0; i < 2; ++i) {
-      if (!banks[i]) continue;
-      const void* wptr[3] = {banks[i]->gate_w, banks[i]->up_w, banks[i]->down_w};
-      for (int j = 0; j < 3; ++j) aligned = aligned && (((uintptr_t)wptr[j] % 16) == 0);
-    }
-    const int n_tasks = L->top_k + (L->n_shared ? 1 : 0);
-    const int items = n_tasks * (L->d_ff / 16);
-    int g_slots = (items + sms - 1) / sms;
-    if (g_slots > 4) g_slots = 4;
-    const int rs_g = L->d_model / 2 + 32, rs_d = L->d_ff / 2 + 32;
-    const int bulk_off = (lay.total + 127) & ~127;
-    const size_t total = (size_t)bulk_off + 128 + (size_t)g_slots * 32 * rs_g + (size_t)n_tasks * 16 * rs_d;
-    if (!no_bulk && aligned && n_tasks <= 12 && total <= 220 * 1024) {
-      p.bulk_off = bulk_off;
-      p.g_slots = g_slots;
-      return ld_launch<1, true, 2>(p, sms, total, st);
-    }
-    if (L->d_ff >= 2048) return ld_launch<1, false, 4>(p, sms, lay.total, st);
-    return ld_launch<1, false, 2>(p, sms, lay.total, st);
-  }
-  if (L->d_ff >= 2048) {
-    if (T <= 2) return ld_launch<2, false, 4>(p, sms, lay.total, st);
-    if (T <= 4) return ld_launch<4, false, 4>(p, sms, lay.total, st);
-    return ld_launch<8, false, 4>(p, sms, lay.total, st);
-  }
-  if (T <= 2) return ld_launch<2, false, 2>(p, sms, lay.total, st);
-  if (T <= 4) return ld_launch<4, false, 2>(p, sms, lay.total, st);
-  return ld_launch<8, false, 2>(p, sms, lay.total, st);
+  const size_t smem_bytes = (size_t)plan.lay.total;
+  if (T == 1) return ld_launch<1>(p, sms, smem_bytes, st);
+  if (T <= 2) return ld_launch<2>(p, sms, smem_bytes, st);
+  if (T <= 4) return ld_launch<4>(p, sms, smem_bytes, st);
+  return ld_launch<8>(p, sms, smem_bytes, st);
 }
 
 }  // extern "C"

@@ -21,14 +21,10 @@
 //
 // The kernel is HBM-bound by design: per weight it issues ~0.9 integer ops and
 // 1/256 of an mma, independent of the number of tokens (up to 8*NT per pass).
-#include <cstdlib>
-
 #include "qmm_common.cuh"
 
 namespace zmoe {
 
-// Persistent bulk-copy pipelined variant (qmm_stream.cu); returns 1 when the shape is outside its fast path.
-int qmm_stream_launch(const QmmParams& p, int nmat, int rows_hint, cudaStream_t st);
 // mxfp4 weights (qmm_mxfp4.cu).
 int qmm_mxfp4_launch(QmmParams p, int nmat, int rows_hint, int max_groups, cudaStream_t st, const char* who);
 
@@ -536,14 +532,6 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
     int mg = rows < E ? rows : E;
     if (mg > 65535) mg = 65535;
     return qmm_mxfp4_launch(p, nmat, rows_hint, mg, (cudaStream_t)stream, who);
-  }
-  // The shared-memory pipelined kernel is opt-in (ZMOE_STREAM=1): the register-pipelined kernel below is
-  // as fast or faster at decode sizes.
-  static const bool use_stream = getenv("ZMOE_STREAM") != nullptr && atoi(getenv("ZMOE_STREAM")) != 0;
-  if (use_stream) {
-    p.rs = 0;
-    const int rc = qmm_stream_launch(p, nmat, rows_hint, (cudaStream_t)stream);
-    if (rc != 1) return rc;  // 1: shape outside the pipelined kernel's fast path
   }
   QmmChoice c = choose_config(p.ngroups, rows_hint);
   // keep the staged token rows within ~96 KB so that several CTAs share an SM

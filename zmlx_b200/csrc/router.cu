@@ -5,6 +5,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "layer_route.cuh"
 #include "plan.cuh"
 #include "router_rows.cuh"
 
@@ -43,8 +44,9 @@ __global__ void __launch_bounds__(128) sigmoid_topk_kernel(const void* __restric
                         sm + (size_t)wid * (2 * E + 64 + 2 * kMaxK));
 }
 
-// Router linear.  One warp per (expert, token tile of 8): 16-byte loads of the
-// expert's weight row, the token rows come from L1/L2.
+// Router linear.  One warp per (expert, token tile of 8): 16-byte loads of the expert's weight row, the
+// token rows come from L1/L2.  The order of the sum is the segmented one of router_logit_warp, which the
+// one-launch decode block shares: both give the same logit bit for bit.
 __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ wr, int T, int E,
                                                             int d, void* __restrict__ logits, int out_dtype) {
@@ -54,42 +56,12 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16*
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
   const int t0 = blockIdx.y * 8;
-  float acc[8];
-#pragma unroll
-  for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
   const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * d);
   const int nvec = d >> 3;
-  for (int i = lane; i < nvec; i += 32) {
-    uint4 wv = __ldg(wrow + i);
-    float wf[8];
-    wf[0] = bf16_bits_to_float(wv.x & 0xffffu);
-    wf[1] = bf16_bits_to_float(wv.x >> 16);
-    wf[2] = bf16_bits_to_float(wv.y & 0xffffu);
-    wf[3] = bf16_bits_to_float(wv.y >> 16);
-    wf[4] = bf16_bits_to_float(wv.z & 0xffffu);
-    wf[5] = bf16_bits_to_float(wv.z >> 16);
-    wf[6] = bf16_bits_to_float(wv.w & 0xffffu);
-    wf[7] = bf16_bits_to_float(wv.w >> 16);
-#pragma unroll
-    for (int t = 0; t < 8; ++t) {
-      if (t0 + t < T) {
-        uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + t) * d) + i);
-        acc[t] = fmaf(wf[0], bf16_bits_to_float(xv.x & 0xffffu), acc[t]);
-        acc[t] = fmaf(wf[1], bf16_bits_to_float(xv.x >> 16), acc[t]);
-        acc[t] = fmaf(wf[2], bf16_bits_to_float(xv.y & 0xffffu), acc[t]);
-        acc[t] = fmaf(wf[3], bf16_bits_to_float(xv.y >> 16), acc[t]);
-        acc[t] = fmaf(wf[4], bf16_bits_to_float(xv.z & 0xffffu), acc[t]);
-        acc[t] = fmaf(wf[5], bf16_bits_to_float(xv.z >> 16), acc[t]);
-        acc[t] = fmaf(wf[6], bf16_bits_to_float(xv.w & 0xffffu), acc[t]);
-        acc[t] = fmaf(wf[7], bf16_bits_to_float(xv.w >> 16), acc[t]);
-      }
-    }
-  }
-#pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    float s = warp_sum(acc[t]);
-    if (lane == 0 && t0 + t < T) {
-      size_t o = (size_t)(t0 + t) * E + e;
+  for (int t = t0; t < min(T, t0 + 8); ++t) {
+    const float s = router_logit_warp(wrow, reinterpret_cast<const uint4*>(x + (size_t)t * d), nvec, lane);
+    if (lane == 0) {
+      const size_t o = (size_t)t * E + e;
       if (out_dtype == ZMOE_F32)
         reinterpret_cast<float*>(logits)[o] = s;
       else
@@ -125,37 +97,14 @@ __global__ void __launch_bounds__(128) route_fused_kernel(const RouteParams p) {
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int T = p.T, E = p.E, d = p.d;
-  // ---- phase 1: one warp per expert row, token tiles of 8
+  // ---- phase 1: one warp per expert row (summation order of router_logit_warp)
   const int e = blockIdx.x * 4 + wid;
   if (e < E) {
     const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
     const int nvec = d >> 3;
-    for (int t0 = 0; t0 < T; t0 += 8) {
-      float acc[8];
-#pragma unroll
-      for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
-#pragma unroll 8
-      for (int i = lane; i < nvec; i += 32) {
-        const uint4 wv = __ldg(wrow + i);
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          if (t0 + t < T) {
-            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)(t0 + t) * d) + i);
-            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              acc[t] = fmaf(bf16_bits_to_float(ww[q] & 0xffffu), bf16_bits_to_float(xw[q] & 0xffffu), acc[t]);
-              acc[t] = fmaf(bf16_bits_to_float(ww[q] >> 16), bf16_bits_to_float(xw[q] >> 16), acc[t]);
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float sres = warp_sum(acc[t]);
-        if (lane == 0 && t0 + t < T) p.logits[(size_t)(t0 + t) * E + e] = __float2bfloat16_rn(sres);
-      }
+    for (int t = 0; t < T; ++t) {
+      const float sres = router_logit_warp(wrow, reinterpret_cast<const uint4*>(p.x + (size_t)t * d), nvec, lane);
+      if (lane == 0) p.logits[(size_t)t * E + e] = __float2bfloat16_rn(sres);
     }
   }
   // ---- last CTA done?

@@ -6,6 +6,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "layer_route.cuh"
 
 namespace zmoe {
 
@@ -25,25 +26,30 @@ __device__ __forceinline__ float load_logit(const void* p, int dtype, size_t i) 
 template <int VPL>
 __device__ __forceinline__ void warp_topk_masked(float (&v)[VPL], int E, int K, int lane, float* sel_val,
                                                  int* sel_idx, float* scratch) {
-  float* vals = scratch;
+  // ranking runs on order-preserving integer keys (ld_order_key): a total order even when a row holds NaN
+  // (NaN ranks below every number), so the ranks are always a permutation and every slot gets written
+  uint32_t* keys = reinterpret_cast<uint32_t*>(scratch);
   float* out_v = scratch + E;
   int* out_i = reinterpret_cast<int*>(scratch + E + kMaxK);
   __syncwarp();
+  uint32_t kv[VPL];
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     const int idx = lane + 32 * j;
-    if (idx < E) vals[idx] = v[j];
+    kv[j] = ld_order_key(v[j] + 0.0f);
+    if (idx < E) keys[idx] = kv[j];
   }
+  if (lane < K) out_i[lane] = 0;
   __syncwarp();
   int rank[VPL];
 #pragma unroll
   for (int j = 0; j < VPL; ++j) rank[j] = 0;
   for (int o = 0; o < E; ++o) {
-    const float ov = vals[o];  // broadcast read
+    const uint32_t ok = keys[o];  // broadcast read
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const int idx = lane + 32 * j;
-      rank[j] += (ov > v[j]) || (ov == v[j] && o < idx);
+      rank[j] += (ok > kv[j]) || (ok == kv[j] && o < idx);
     }
   }
 #pragma unroll
@@ -57,7 +63,7 @@ __device__ __forceinline__ void warp_topk_masked(float (&v)[VPL], int E, int K, 
   __syncwarp();
   for (int r = 0; r < K; ++r) {
     sel_val[r] = out_v[r];
-    sel_idx[r] = out_i[r];
+    sel_idx[r] = min(max(out_i[r], 0), E - 1);
   }
 }
 

@@ -23,7 +23,8 @@ class MoELayer:
     """Packed weights of one MoE layer plus the buffers of its forward pass."""
 
     def __init__(self, cfg: MoEConfig, params: dict, *, max_tokens: int = 64, combine: str | None = None,
-                 swiglu: str | None = None, fused: bool = True, launch: str = "cooperative"):
+                 swiglu: str | None = None, fused: bool = True, launch: str = "cooperative",
+                 debug_withhold_logit: bool = False):
         self.cfg = cfg
         self.p = params
         dev = params["gate_w"].device
@@ -42,6 +43,9 @@ class MoELayer:
         # 'pdl': the one-launch block as a regular launch that is set up while the previous kernel still runs
         # (saves the launch gap in a chain of blocks); only when this stream has the GPU to itself
         self.launch = launch
+        # test hook of the one-launch block: one router logit is never published, so its bounded waits run out
+        self._debug_flags = _lib.DEBUG_WITHHOLD_LOGIT if debug_withhold_logit else 0
+        self._stamps: torch.Tensor | None = None
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
         self._fused_ok: dict[int, bool] = {}  # token count -> whether the one-launch path covers this block
@@ -65,6 +69,8 @@ class MoELayer:
         d.combine_mode = self.combine_mode
         d.out_flags = 3 if cfg.family == "generic" else 1
         d.launch_mode = 1 if self.launch == "pdl" else 0
+        d.debug_flags = self._debug_flags
+        d.debug_stamps = self._stamps.data_ptr() if self._stamps is not None else None
         d.router_w = W["router_w"].data_ptr()
         d.router_bias = bias.data_ptr() if bias is not None else None
 
@@ -116,9 +122,25 @@ class MoELayer:
         return (words & 0xFFFF).to(torch.int16).view(torch.bfloat16).view(T, E)
 
     def fused_status(self, T: int) -> int:
-        """The status word of the T-token workspace: non-zero after a bounded grid-barrier wait ran out."""
+        """The status word of the T-token workspace: non-zero after a bounded wait of the one-launch block ran out."""
         ws = self._fused_ws.get(T)
         return 0 if ws is None else int(ws[:16].view(torch.int32)[3].item())
+
+    def check_status(self) -> None:
+        """Raise ``ZmoeError(ERR_TIMEOUT)`` if a bounded wait ran out in any one-launch pass since the last check
+        (the output of that pass is void).  Synchronises the current stream: call it where the caller waits for
+        results anyway (end of a decode step, end of a timed region)."""
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            for ws in self._fused_ws.values():
+                _lib.check(lib.zmoe_layer_decode_status(ops._ptr(ws), 1, ops._stream()))
+
+    def enable_stamps(self) -> torch.Tensor:
+        """Debug: make CTA 0 of the one-launch block record its cycle counter at the phase boundaries; returns the
+        16 int64 it writes (see ``zmoe_layer_desc.debug_stamps``)."""
+        self._stamps = torch.zeros(16, dtype=torch.int64, device=self.device)
+        self._desc = self._describe()
+        return self._stamps
 
     def _alloc(self, T: int) -> None:
         cfg, dev = self.cfg, self.device
