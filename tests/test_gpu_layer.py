@@ -5,9 +5,8 @@ import numpy as np
 import pytest
 import torch
 
-from oracle import fast as F
 from oracle import semantics as S
-from tests.helpers import assert_close_rel, t2n
+from tests.helpers import assert_close_rel, oracle_layer as _oracle_layer, t2n
 from zmlx_b200 import synthetic
 from zmlx_b200.layer import MoELayer
 
@@ -21,57 +20,6 @@ def _layer(name):
         cfg = synthetic.CONFIGS[name]
         _LAYERS[name] = (cfg, synthetic.make_layer(cfg, device=DEV))
     return _LAYERS[name]
-
-
-def _subset(params, experts):
-    """Copy only the selected experts to the host (the oracle touches nothing else)."""
-    sel = torch.as_tensor(experts, device=DEV, dtype=torch.int64)
-    out = {}
-    for k in ("gate", "up", "down"):
-        out[f"{k}_w"] = t2n(params[f"{k}_w"].view(torch.int32)[sel]).view(np.uint32)
-        out[f"{k}_s"] = t2n(params[f"{k}_s"][sel])
-        out[f"{k}_b"] = None if params[f"{k}_b"] is None else t2n(params[f"{k}_b"][sel])
-    return out
-
-
-def _oracle_layer(cfg, params, x, logits, idx_gpu):
-    """The oracle's recipe with the compiled matmuls; routing is recomputed by the oracle from the
-    kernel's own bf16 logits and must match the kernel's indices exactly."""
-    xn, ln = t2n(x), t2n(logits)
-    bias = None if params["expert_bias"] is None else t2n(params["expert_bias"])
-    if cfg.family == "generic":
-        w, idx = S.topk_gating_softmax(ln, cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
-        w = S.bf16(w)
-        cmode = "t"
-    elif cfg.family == "qwen3":
-        idx, w = S.qwen3_gating(ln, cfg.top_k, norm_topk_prob=cfg.norm_topk_prob)
-        cmode = "no_fma"
-    else:
-        w, idx = S.deepseek_router_topk_sigmoid(ln, bias, k=cfg.top_k, n_group=cfg.n_group,
-                                                topk_group=cfg.topk_group)
-        w = (w * np.float32(cfg.routed_scaling_factor)).astype(np.float32)
-        cmode = "fp32_no_fma" if cfg.family == "glm" else "t"
-    np.testing.assert_array_equal(t2n(idx_gpu).view(np.uint32), idx)  # expert indices bit-exact
-    experts = np.unique(idx)
-    remap = np.searchsorted(experts, idx).astype(np.int32)
-    sub = _subset(params, experts)
-    gs = 32 if cfg.mode == "mxfp4" else cfg.group_size
-    y, _ = F.experts_forward(xn, remap, sub, group_size=gs, mode=cfg.mode,
-                             swiglu="cpu" if cfg.mode == "affine" else "per_op")
-    out = S.moe_combine(y, w, mode=cmode)
-    if cmode == "fp32_no_fma":
-        out = S.bf16(out)
-    if cfg.n_shared:
-        sh = {}
-        for k, v in params["shared"].items():
-            if v is None:
-                sh[k] = None
-            elif k.endswith("_w"):
-                sh[k] = t2n(v.view(torch.int32)).view(np.uint32)[0]
-            else:
-                sh[k] = t2n(v)[0]
-        out = S.bf16(out + S.shared_expert_mlp(xn, sh, group_size=gs, mode=cfg.mode))
-    return out, w
 
 
 # fused: the one-launch path (zmoe_layer_decode) takes the block; otherwise the separate kernels do

@@ -43,3 +43,54 @@ def test_patched_block_matches_oracle_and_unpatched(base, family):
     assert_close_rel(t2n(y), t2n(y_ref_torch), 3e-2, "patched vs unpatched torch block")
     unpatch(m)
     assert torch.equal(blk(x), y_ref_torch)
+
+
+@pytest.mark.parametrize("name,T", [("c2", 1), ("c2", 4), ("c5", 1)])
+def test_patched_block_is_one_launch_and_matches_the_oracle(name, T):
+    """patch(model) must reach the one-launch kernel: the workspace's launch counter advances by exactly one per
+    call of the patched block, and the result follows the oracle's recipe for the block's family."""
+    from tests.helpers import oracle_layer
+
+    cfg = synthetic.CONFIGS[name]
+    p = synthetic.make_layer(cfg, device=DEV)
+    blk = znn.block_from_params(cfg, p)
+    m = _Model(blk)
+    patch(m)
+    fast = blk._zmlx_fast_layer
+    assert fast is not None, "the moe_mlp pattern did not build the fused layer for a supported block"
+    x = synthetic.make_tokens(cfg, T, device="cpu").reshape(1, T, cfg.d_model).to(DEV)
+    y0 = blk(x)  # the first call creates the workspace
+    before = fast.launch_count(T)
+    y = blk(x)
+    torch.cuda.synchronize()
+    assert fast.launch_count(T) == before + 1, "a patched call must be exactly one zmoe_layer_decode launch"
+    fast.check_status()
+    assert y.data_ptr() != y0.data_ptr() and torch.equal(y, y0)  # fresh result tensors, same bits
+    ref, _ = oracle_layer(cfg, p, x.reshape(T, -1), fast.router_logits(T), fast.indices[:T])
+    assert_close_rel(t2n(y).reshape(T, -1), ref, 2e-2, f"patched {name} block T={T} vs oracle")
+    unpatch(m)
+    assert not hasattr(blk, "_zmlx_fast_layer")
+
+
+def test_deepseek_router_pattern_fires_on_a_256_expert_gate():
+    """The opt-in deepseek_router pattern (reference: src/zmlx/patch/patterns/deepseek_router.py:76-120) rewrites
+    MoEGate for 256 experts with k = 8: indices int32 in canonical order, weights = normalised affinities * scale."""
+    cfg = synthetic.CONFIGS["c5"]
+    g = torch.Generator(device="cpu").manual_seed(5)
+    wr = (torch.randn((cfg.n_experts, 512), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    bias = (torch.randn((cfg.n_experts,), generator=g) * 0.01).to(DEV)
+    gate = znn.MoEGate(wr, bias, top_k=8, n_group=8, topk_group=4, routed_scaling_factor=2.5)
+    m = _Model(gate)
+    x = torch.randn((3, 5, 512), generator=g).to(torch.bfloat16).to(DEV)
+    idx_ref, w_ref = gate(x)
+    patch(m, patterns=["deepseek_router"])
+    assert m._zmlx_patch_result.patched_count == 1
+    idx, w = gate(x)
+    assert idx.dtype == torch.int32 and w.dtype == torch.float32, "the fused router did not run"
+    logits = t2n(x.reshape(15, -1) @ wr.T)
+    w_o, idx_o = S.deepseek_router_topk_sigmoid(logits, t2n(bias), k=8, n_group=8, topk_group=4)
+    np.testing.assert_array_equal(t2n(idx).reshape(15, 8).view(np.uint32), idx_o)
+    np.testing.assert_allclose(t2n(w).reshape(15, 8), w_o * np.float32(2.5), rtol=5e-6, atol=1e-7)
+    # the unpatched gate picks the same experts (as sets: torch.topk orders ties differently)
+    assert np.array_equal(np.sort(t2n(idx_ref).reshape(15, 8), -1), np.sort(t2n(idx).reshape(15, 8), -1))
+    unpatch(m)

@@ -107,3 +107,16 @@ def test_swiglu_contracts_differ_only_in_rounding():
     exact = g / (1 + np.exp(-g.astype(np.float64))) * u
     assert np.abs(a - exact).max() <= 2 ** -8 * np.abs(exact).max()
     assert np.abs(b - exact).max() <= 4 * 2 ** -8 * np.abs(exact).max()
+
+
+def test_nan_scores_rank_below_every_number():
+    """Pinned tie/NaN rule of the canonical order: NaN scores come last, among themselves by ascending id
+    (what a stable descending argsort gives); the GPU routers use the same total order."""
+    import numpy as np
+
+    from oracle import semantics as S
+
+    row = np.array([[0.5, np.nan, -np.inf, 2.0, np.nan, 0.5]], dtype=np.float32)
+    np.testing.assert_array_equal(S._topk_desc_stable(row, 6), [[3, 0, 5, 2, 1, 4]])
+    _, idx = S.topk_gating_softmax(np.full((1, 8), np.nan, dtype=np.float32), 3)
+    np.testing.assert_array_equal(idx, [[0, 1, 2]])

@@ -9,9 +9,12 @@ data (the built-in scratch keeps the first call's rows), and expects bit-identic
 
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
+from oracle import semantics as S
+from tests.helpers import t2n
 from zmlx_b200 import _lib, ops, quant
 
 pytestmark = pytest.mark.gpu
@@ -50,11 +53,24 @@ def test_noalloc_matches_caller_scratch_twice_in_a_row():
         tensors = _case(seed, T, K, E, d_in, d_out)
         scratch = torch.empty((T * K, d_out), dtype=torch.bfloat16, device=DEV)
         want = _run("zmoe_gather_qmm_combine", tensors, T, K, E, d_in, d_out, scratch=scratch)
+        if seed == 2:  # the array's address is cached by now: the call itself must not change free memory at all
+            plan = ops.build_plan(tensors[5], E)  # (allocations of the test harness happen before the probe)
+            del plan
         free_before = torch.cuda.mem_get_info()[0]
         got = _run("zmoe_gather_qmm_combine_noalloc", tensors, T, K, E, d_in, d_out)
-        assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)  # nothing allocated by the call
+        free_after = torch.cuda.mem_get_info()[0]
+        assert free_after >= free_before - (1 << 20)  # nothing allocated by the call (torch's own pool aside)
         assert torch.isfinite(got).all()
         assert torch.equal(got, want)
+        # and the entry point's own evidence against the CPU oracle: the projections are rounded to T (bfloat16)
+        # on both sides before the float32 combine, so a last-bit flip of one projection moves the sum by a
+        # bf16 ulp of that term -- the bound is the one for bf16 activations, 2e-2 of the tensor's scale
+        w, s_, b, act, gate, idx = tensors
+        ref = S.gather_qmm_combine_quantized(t2n(act).reshape(T, K, d_in), t2n(w.view(torch.int32)).view(np.uint32),
+                                             t2n(s_), t2n(b), t2n(gate), t2n(idx).reshape(T, K), group_size=64,
+                                             combine="fp32_no_fma")
+        err = np.abs(t2n(got) - ref).max() / max(float(np.sqrt((ref ** 2).mean())), 1e-30)
+        assert err <= 2e-2, f"no-alloc entry vs oracle: {err:.3g} of rms"
     # a smaller call after a larger one: stale rows beyond the used part must not leak in
     tensors = _case(3, 2, 2, 8, 256, 512)
     scratch = torch.empty((4, 512), dtype=torch.bfloat16, device=DEV)

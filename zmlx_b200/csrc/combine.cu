@@ -139,7 +139,7 @@ static void* g_scratch_ptr[kMaxDevices] = {};
 
 // Device address of the array on the CURRENT device.  In host code the symbol itself is only a
 // stand-in; the real address comes from cudaGetSymbolAddress, asked once per device.
-static int static_scratch_for_current_device(void** out) {
+static int static_scratch_for_current_device(void** out, cudaStream_t stream) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine_noalloc: cudaGetDevice: %s",
@@ -148,6 +148,16 @@ static int static_scratch_for_current_device(void** out) {
     return fail(ZMOE_ERR_UNSUPPORTED, "zmoe_gather_qmm_combine_noalloc: device ordinal %d beyond %d", dev, kMaxDevices);
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (g_scratch_ptr[dev] == nullptr) {
+    // the one-time address query is not a stream operation: inside a capture it would invalidate the capture,
+    // so refuse instead and ask for a first call outside of it
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(stream, &cap);
+    if (e != cudaSuccess)
+      return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine_noalloc: cudaStreamIsCapturing: %s", cudaGetErrorString(e));
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(ZMOE_ERR_UNSUPPORTED,
+                  "zmoe_gather_qmm_combine_noalloc: the first call on a device looks up the built-in scratch and "
+                  "cannot run inside a stream capture; call it once outside the capture first");
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess || ptr == nullptr)
@@ -210,7 +220,7 @@ int zmoe_gather_qmm_combine_noalloc(const void* act, int ldx, const uint32_t* w_
                "holds %zu (use zmoe_gather_qmm_combine with caller scratch for larger calls)",
                (size_t)T * K * N, need, (size_t)kStaticScratchBytes);
   void* scratch = nullptr;
-  int rc = static_scratch_for_current_device(&scratch);
+  int rc = static_scratch_for_current_device(&scratch, (cudaStream_t)stream);
   if (rc != ZMOE_OK) return rc;
   if (T == 0) return ZMOE_OK;
   // the array keeps the previous call's rows: rows whose expert id the plan dropped are never written by the

@@ -2,7 +2,7 @@
 // down projection, ordered weighted combine, shared expert.
 //
 // A persistent grid of one CTA per SM.  Each CTA is 16 consumer warps (four teams of four) plus one PRODUCER
-// warp that does nothing but issue asynchronous copies (cp.async) of packed expert weights into a ring of shared-memory
+// warp per team that does nothing but issue asynchronous copies (cp.async) of packed expert weights into a ring of shared-memory
 // stages (one mbarrier pair per stage).  The producer runs ahead of the math: it starts with the shared
 // expert's first tiles before the routing is known, follows the routed gate/up tiles with the down-projection
 // tiles without a pause, and so keeps >100 KB per SM in flight across every phase boundary.  There is no
@@ -47,7 +47,9 @@ namespace zmoe {
 constexpr int kLdTeams = 4;                          // teams of consumer warps; a team owns one item at a time
 constexpr int kLdSegBytes = 512;                     // bytes of one weight row in one stage
 constexpr int kLdSegStride = kLdSegBytes + 32;       // == 32 mod 128: the 8-byte fragment reads of a warp hit all banks once
-constexpr int kLdSlotBytes = 32 * kLdSegStride;      // one stage: 32 row segments
+constexpr int kLdScOff = 32 * kLdSegStride;          // after the 32 row segments of a stage: their scales and biases,
+constexpr int kLdScBytes = 2048;                     // [scale | bias][matrix][row 0..15][16 groups] bfloat16
+constexpr int kLdSlotBytes = kLdScOff + kLdScBytes;  // one stage
 constexpr int kLdMaxDepth = 6;                       // stages per team at most
 constexpr int kLdSmemLimit = 227 * 1024;
 constexpr int kLdMaxMine = 4;                        // router rows per CTA at most (E <= 4 * grid)
@@ -153,28 +155,45 @@ __device__ __forceinline__ bool ld_mbar_try(uint32_t bar, int parity) {
                : "memory");
   return ok != 0;
 }
-// The same test, but the warp may sleep up to ~1 us inside it instead of burning issue slots.
+// The same test, but the hardware may suspend the warp inside it for a while (no issue slots burnt).
 __device__ __forceinline__ bool ld_mbar_try_sleep(uint32_t bar, int parity) {
   uint32_t ok;
-  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                : "=r"(ok)
-               : "r"(bar), "r"(parity), "n"(1000)
+               : "r"(bar), "r"(parity)
                : "memory");
   return ok != 0;
 }
-// Bounded wait for a phase of an mbarrier (about a second); gives up early when another warp of the CTA has.
+__device__ __forceinline__ unsigned long long ld_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr unsigned long long kLdWaitNs = 1000000000ull;  // a wait that lasts a second has run out
+// Bounded wait for a phase of an mbarrier; gives up early when another warp of the CTA has.
 __device__ __forceinline__ bool ld_mbar_wait(uint32_t bar, int parity, const volatile int* flags) {
   if (ld_mbar_try(bar, parity)) return true;
-  for (int i = 0; i < (kLdSpinLimit >> 1); ++i) {
+  const unsigned long long t0 = ld_now_ns();
+  for (;;) {
     if (ld_mbar_try_sleep(bar, parity)) return true;
-    if ((i & 255) == 255 && flags[0]) return false;
+    if (flags[0] || ld_now_ns() - t0 > kLdWaitNs) return false;
   }
-  return false;
 }
 // 16-byte asynchronous copy global -> shared (L2 only), and the arrival that fires on an mbarrier once all of
 // the thread's earlier copies have landed.
-__device__ __forceinline__ void ld_cp16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+// The packed weights are read once: they are marked "evict first" in L2 so that they do not push out what is
+// re-read there (token rows, router logits, the hand-over words).
+__device__ __forceinline__ unsigned long long ld_policy_evict_first() {
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void ld_cp16(uint32_t dst, const void* src, unsigned long long pol) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol)
+               : "memory");
+}
+__device__ __forceinline__ void ld_cp8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void ld_cp_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -206,6 +225,21 @@ __device__ __forceinline__ uint32_t deq_h_hi(uint32_t w) {
   uint32_t r;
   asm("lop3.b32 %0, %1, 0x00F000F0, 0x64006400, 0xEA;" : "=r"(r) : "r"(w));
   return r;
+}
+
+template <int OFF>
+__device__ __forceinline__ uint2 ld_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 ld_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
 }
 
 #define LD_STAMP(i)                                                            \
@@ -345,30 +379,23 @@ __device__ __forceinline__ uint32_t ld_route_bar(uint32_t bars) { return bars + 
 // 4 * chunk .. 4 * chunk + 3, warp wk owns quad 4 * chunk + wk.
 __device__ __forceinline__ int ld_group_of(int p, int wk) { return ((((p >> 2) << 2) + wk) << 2) + (p & 3); }
 
-// Scales and biases of the block of 8 / TT groups that starts at stream position p0: sb[m][h][0] scale,
-// [1] bias of row g + 8h of matrix m.  With one token a lane's two columns are two adjacent groups (one 32-bit
-// load brings both); otherwise both columns are the same group.
+// Scales and biases of a lane's column(s) from the stage's copy: sb[m][h][0] scale, [1] bias of row g + 8h of
+// matrix m, for local group `gl` of the chunk (0..15).  With one token a lane's two columns are two adjacent
+// groups (one 32-bit read brings both); otherwise both columns are the same group.
 template <int TT>
-__device__ __forceinline__ void ld_load_sb(uint32_t (&sb)[2][2][2], const __nv_bfloat16* const (&sp)[2],
-                                           const __nv_bfloat16* const (&bp)[2], int ng, int p0, int wk, int tig) {
-  const int G = ld_group_of(p0 + ((TT == 1) ? 2 * tig : (2 * tig) / TT), wk);
-#ifdef ZMOE_LD_EXP_NO_SB
-  const bool ok = false;
-#else
-  const bool ok = G < ng;
-#endif
+__device__ __forceinline__ void ld_load_sb(uint32_t (&sb)[2][2][2], uint32_t sc, int g, int gl) {
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (TT == 1) {
-        sb[m][h][0] = ok ? __ldg(reinterpret_cast<const uint32_t*>(sp[m] + (size_t)h * 8 * ng + G)) : 0u;
-        sb[m][h][1] = ok ? __ldg(reinterpret_cast<const uint32_t*>(bp[m] + (size_t)h * 8 * ng + G)) : 0u;
-      } else {
-        sb[m][h][0] = ok ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(sp[m] + (size_t)h * 8 * ng + G)) : 0u;
-        sb[m][h][1] = ok ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(bp[m] + (size_t)h * 8 * ng + G)) : 0u;
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int arr = 0; arr < 2; ++arr) {
+        const uint32_t addr = sc + (uint32_t)(((arr * 2 + m) * 16 + g + 8 * h) * 32 + gl * 2);
+        if (TT == 1)
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sb[m][h][arr]) : "r"(addr));
+        else
+          asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sb[m][h][arr]) : "r"(addr));
       }
-    }
 }
 
 // Scale, bias and the offsets for the block of 8 / TT multiplexed groups that starts at stream position p0.
@@ -399,22 +426,14 @@ __device__ __forceinline__ void ld_fixup(float (&acc)[2][4], const float (&dg)[2
 // DN = false: gate/up, matrices m = gate, up of rows n0 .. n0+15; DN = true: down, m = rows n0 + 16 m ..
 // Leaves the K-split total of the team in the first warp's acc, columns folded back onto their tokens.
 template <int TT, bool DN>
-__device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBank& bank, int e, int N, int K8,
-                                        int n0, int xoff, int zoff, bool tok_ok, int slot_g, const float2* xsum,
-                                        int rs, const int (&srow_c)[2]) {
+__device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, uint32_t xaddr, uint32_t zaddr,
+                                        bool tok_ok, int slot_g, const float2* xsum, int rs,
+                                        const int (&srow_c)[2]) {
   constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
   const int ng = K8 >> 3;
   const int rb = K8 << 2;  // bytes of a weight row
   const int nch = (rb + kLdSegBytes - 1) / kLdSegBytes;
   const int wk = c.wk, g = c.g, tig = c.tig;
-  const __nv_bfloat16* sp[2];
-  const __nv_bfloat16* bp[2];
-#pragma unroll
-  for (int m = 0; m < 2; ++m) {
-    const size_t row = (size_t)e * N + n0 + (DN ? m * 16 : 0) + g;
-    sp[m] = bank.s[DN ? 0 : m] + row * ng;
-    bp[m] = bank.b[DN ? 0 : m] + row * ng;
-  }
   float dg[2][2][4];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
@@ -424,13 +443,13 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBa
       dg[m][0][j] = 0.0f;
       dg[m][1][j] = 0.0f;
     }
-  uint32_t sb_cur[2][2][2], sb_nxt[2][2][2];
+  uint32_t sb[2][2][2];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) sb_cur[m][h][0] = sb_cur[m][h][1] = sb_nxt[m][h][0] = sb_nxt[m][h][1] = 0u;
-  if (TT > 1) ld_load_sb<TT>(sb_cur, sp, bp, ng, 0, wk, tig);
+    for (int h = 0; h < 2; ++h) sb[m][h][0] = sb[m][h][1] = 0u;
 
+#pragma unroll 1
   for (int ch = 0; ch < nch; ++ch) {
     // ---- wait for the stage (every lane polls: the data was written by the copy engine)
     const uint32_t full = ld_full_bar(c.bars, c.team, c.slot);
@@ -438,34 +457,31 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBa
       c.alive = false;
       c.flags[0] = 1;
     }
-#ifdef ZMOE_LD_EXP_SKIP_MATH
-    const bool have = false;
-#else
     const bool have = c.alive && ((ch * 4 + wk) * 128 < rb);  // the warp's quad exists in this row
-#endif
     if (have) {
-      const uint32_t wbase = c.ring + (uint32_t)(c.slot0 + c.slot) * kLdSlotBytes + g * kLdSegStride + wk * 128 + tig * 8;
+      const uint32_t stage = c.ring + (uint32_t)(c.slot0 + c.slot) * kLdSlotBytes;
+      const uint32_t wbase = stage + g * kLdSegStride + wk * 128 + tig * 8;
+      // one token: a block of eight groups spans two chunks; a lane's columns are groups of the first chunk
+      // (tig 0, 1) or of the second (tig 2, 3), and their scales are read while that chunk's stage is held
+      if (TT == 1 && (tig >> 1) == (ch & 1)) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * 4 + ((2 * tig) & 3));
+      const uint32_t xchunk = xaddr + (uint32_t)(ch * 4 + wk) * 512;
+      const int jm = g - (ch & 1) * 4;  // one token: the group of this chunk that the lane's column carries
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int slot = (TT == 1) ? ((ch & 1) * 4 + j) : (j % GPB);
         const int pos = ch * 4 + j;
-        if (slot == 0) {
-          if (TT == 1)
-            ld_load_sb<TT>(sb_cur, sp, bp, ng, pos, wk, tig);
-          else
-            ld_load_sb<TT>(sb_nxt, sp, bp, ng, pos + GPB, wk, tig);
-        }
+        if (TT > 1 && slot == 0) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * 4 + j + (2 * tig) / TT);
         // lanes whose column carries another group (or no token) read the zero page
-        const bool mine = tok_ok && (TT == 8 || slot_g == slot);
-        const int xa = mine ? (xoff + ((ch * 4 + wk) * 4 + j) * 128) : zoff;
-        const uint4 xb0 = *reinterpret_cast<const uint4*>(c.smem + xa);
-        const uint4 xb1 = *reinterpret_cast<const uint4*>(c.smem + xa + 16);
+        const bool mine = (TT == 1) ? (j == jm) : (tok_ok && (TT == 8 || slot_g == slot));
+        const uint32_t xa = mine ? xchunk + j * 128 : zaddr;
+        const uint4 xb0 = ld_lds128<0>(xa);
+        const uint4 xb1 = ld_lds128<16>(xa);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          uint2 wa, wb;
-          const uint32_t wa_addr = wbase + m * 16 * kLdSegStride + j * 32;
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wa.x), "=r"(wa.y) : "r"(wa_addr));
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wb.x), "=r"(wb.y) : "r"(wa_addr + 8 * kLdSegStride));
+          const uint2 wa = (m == 0) ? (j == 0 ? ld_lds64<0>(wbase) : j == 1 ? ld_lds64<32>(wbase) : j == 2 ? ld_lds64<64>(wbase) : ld_lds64<96>(wbase))
+                                    : (j == 0 ? ld_lds64<16 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<16 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<16 * kLdSegStride + 64>(wbase) : ld_lds64<16 * kLdSegStride + 96>(wbase));
+          const uint2 wb = (m == 0) ? (j == 0 ? ld_lds64<8 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<8 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<8 * kLdSegStride + 64>(wbase) : ld_lds64<8 * kLdSegStride + 96>(wbase))
+                                    : (j == 0 ? ld_lds64<24 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<24 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<24 * kLdSegStride + 64>(wbase) : ld_lds64<24 * kLdSegStride + 96>(wbase));
           const uint32_t wa8 = wa.x >> 8, wb8 = wb.x >> 8;
           mma_f16_m16n8k16(dg[m][0], deq_h_lo(wa.x), deq_h_lo(wb.x), deq_h_hi(wa.x), deq_h_hi(wb.x), xb0.x, xb0.y);
           mma_f16_m16n8k16(dg[m][1], deq_h_lo(wa8), deq_h_lo(wb8), deq_h_hi(wa8), deq_h_hi(wb8), xb0.z, xb0.w);
@@ -474,7 +490,7 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBa
           mma_f16_m16n8k16(dg[m][1], deq_h_lo(wc8), deq_h_lo(wd8), deq_h_hi(wc8), deq_h_hi(wd8), xb1.z, xb1.w);
         }
         if (slot == GPB - 1) {
-          ld_fixup<TT>(acc, dg, sb_cur, xsum, rs, srow_c, ng, pos - (GPB - 1), wk, tig);
+          ld_fixup<TT>(acc, dg, sb, xsum, rs, srow_c, ng, pos - (GPB - 1), wk, tig);
 #pragma unroll
           for (int m = 0; m < 2; ++m)
 #pragma unroll
@@ -482,15 +498,6 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBa
               dg[m][0][jj] = 0.0f;
               dg[m][1][jj] = 0.0f;
             }
-          if (TT > 1) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m)
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                sb_cur[m][h][0] = sb_nxt[m][h][0];
-                sb_cur[m][h][1] = sb_nxt[m][h][1];
-              }
-          }
         }
       }
     }
@@ -503,7 +510,7 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], const LdBa
     }
   }
   // one token: an odd number of chunks leaves half a block of eight groups without its fix-up
-  if (TT == 1 && (nch & 1) && c.alive) ld_fixup<TT>(acc, dg, sb_cur, xsum, rs, srow_c, ng, (nch - 1) * 4, wk, tig);
+  if (TT == 1 && (nch & 1) && c.alive) ld_fixup<TT>(acc, dg, sb, xsum, rs, srow_c, ng, (nch - 1) * 4, wk, tig);
 
   // ---- K-split: the partial sums of warps 1..3 go to the team's first warp in warp order
   const int it = c.itn++;
@@ -577,6 +584,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   LdMeta* meta = reinterpret_cast<LdMeta*>(smem + lay.meta);
   const uint32_t bars = ld_smem_u32(smem + lay.bars);
   const uint32_t ring = ld_smem_u32(smem + lay.ring);
+  const uint32_t smem_base = ld_smem_u32(smem);
   const int ntf = f >> 4;  // gate/up tiles of 16 rows per task
   const int ntd = d >> 5;  // down tiles of 32 rows per task
   const int nch_gu = ((d >> 1) + kLdSegBytes - 1) / kLdSegBytes;
@@ -617,106 +625,111 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   if (p.pdl) pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
 
   // =================================================================== producer warp
-  if (wid == kLdWarps) {
-    int job[kLdTeams], total[kLdTeams], ngu[kLdTeams];
-#pragma unroll
-    for (int t = 0; t < kLdTeams; ++t) job[t] = total[t] = ngu[t] = 0;
+  if (wid >= kLdWarps) {
+    // producer warp of team t: walks the team's stage sequence (its gate/up items chunk by chunk, then its
+    // down-projection items) and fills a stage as soon as the team has handed it back
+    const int t = wid - kLdWarps;
+    const int depth = dbase + (t < dextra ? 1 : 0);
+    const int slot0 = t * dbase + min(t, dextra);
     const int K8g = d >> 3, K8d = f >> 3;
-    // issues chunk ch of one item into stage s of team t: one instruction copies one 512-byte row segment
-    // (16 bytes per lane); the stage's barrier gets one arrival per lane when that lane's copies have landed
-    auto issue = [&](int t, int s, bool dn, const LdBank& bank, int e, int n0, int ch) {
+    const unsigned long long pol = ld_policy_evict_first();
+    // The shared expert's tiles come first in the gate/up order and do not depend on the routing: when this
+    // CTA's first item is one of them, team 0's producer copies its chunks before the routing is known.
+    int total = (t == 0 && p.n_shared && (int)blockIdx.x < ntf) ? nch_gu : 0;
+    const int free_jobs = total;  // stages that need no task list
+    int ngu = 1, n_routed = 0, dn_lo = 0;
+    bool ok = true;
+    int j = 0;
+    for (;; ++j) {
+      if (j == free_jobs) {
+        // from here on the task list is needed
+        ok = ld_mbar_wait(ld_route_bar(bars), 0, flags) && flags[0] == 0;
+        if (!ok) break;
+        const int n_tasks = meta->n_tasks;
+        n_routed = meta->n_routed;
+        const int items_gu = n_tasks * ntf;
+        const int nq_gu = (items_gu > (int)blockIdx.x) ? (items_gu - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
+        const long long items_dn = (long long)n_tasks * ntd;
+        dn_lo = (int)(items_dn * blockIdx.x / nblocks);
+        const int nq_dn = (int)(items_dn * (blockIdx.x + 1) / nblocks) - dn_lo;
+        ngu = (nq_gu > t) ? (nq_gu - 1 - t) / kLdTeams + 1 : 0;
+        const int ndn = (nq_dn > t) ? (nq_dn - 1 - t) / kLdTeams + 1 : 0;
+        total = ngu * nch_gu + ndn * nch_dn;
+      }
+      if (j >= total) break;
+      const int s = j % depth, use = j / depth;
+      ok = ld_mbar_wait(ld_empty_bar(bars, t, s), (use & 1) ^ 1, flags);
+      if (!ok) break;
+      // ---- which chunk of which item
+      const bool dn = j >= ngu * nch_gu;
+      int ch, e, n0;
+      bool sh;
+      if (!dn) {
+        const int qi = j / nch_gu;
+        ch = j - qi * nch_gu;
+        const int i = (int)blockIdx.x + (t + kLdTeams * qi) * nblocks;
+        const int ao = i / ntf;
+        sh = p.n_shared && ao == 0;
+        e = sh ? 0 : meta->task_expert[ao - (p.n_shared ? 1 : 0)];
+        n0 = (i - ao * ntf) << 4;
+      } else {
+        const int jj = j - ngu * nch_gu;
+        const int qi = jj / nch_dn;
+        ch = jj - qi * nch_dn;
+        const int i = dn_lo + t + kLdTeams * qi;
+        const int a = i / ntd;
+        sh = a >= n_routed;
+        e = meta->task_expert[a];
+        n0 = (i - a * ntd) << 5;
+      }
+      // ---- the copies: one instruction moves one 512-byte row segment (16 bytes per lane), eight more move the
+      // rows' scales and biases (8 bytes per lane); the stage's barrier gets one arrival per lane when that
+      // lane's copies have landed
+      const LdBank& bank = dn ? (sh ? p.sdn : p.dn) : (sh ? p.sgu : p.gu);
       const int K8 = dn ? K8d : K8g;
       const int N = dn ? d : f;
-      const int rb = K8 << 2;
+      const int rb = K8 << 2, ng = K8 >> 3;
       const int bytes = min(kLdSegBytes, rb - ch * kLdSegBytes);
-      const int slot0 = t * dbase + min(t, dextra);
-      const uint32_t dst = ring + (uint32_t)(slot0 + s) * kLdSlotBytes + lane * 16;
-      const size_t off = ((size_t)e * N + n0) * rb + (size_t)ch * kLdSegBytes + lane * 16;
-      const unsigned char* src0 = reinterpret_cast<const unsigned char*>(bank.w[0]) + off;
-      const unsigned char* src1 = dn ? src0 + (size_t)16 * rb : reinterpret_cast<const unsigned char*>(bank.w[1]) + off;
-      if (lane * 16 < bytes) {
+      const uint32_t stage = ring + (uint32_t)(slot0 + s) * kLdSlotBytes;
+      const size_t row0 = (size_t)e * N + n0;
+      {
+        const uint32_t dst = stage + lane * 16;
+        const size_t off = row0 * rb + (size_t)ch * kLdSegBytes + lane * 16;
+        const unsigned char* src0 = reinterpret_cast<const unsigned char*>(bank.w[0]) + off;
+        const unsigned char* src1 =
+            dn ? src0 + (size_t)16 * rb : reinterpret_cast<const unsigned char*>(bank.w[1]) + off;
+        if (lane * 16 < bytes) {
 #pragma unroll
-        for (int r = 0; r < 16; ++r) ld_cp16(dst + r * kLdSegStride, src0 + (size_t)r * rb);
+          for (int r = 0; r < 16; ++r) ld_cp16(dst + r * kLdSegStride, src0 + (size_t)r * rb, pol);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) ld_cp16(dst + (16 + r) * kLdSegStride, src1 + (size_t)r * rb);
+          for (int r = 0; r < 16; ++r) ld_cp16(dst + (16 + r) * kLdSegStride, src1 + (size_t)r * rb, pol);
+        }
       }
-      ld_cp_arrive(ld_full_bar(bars, t, s));
-    };
-    // the shared expert's tiles come first in the gate/up order and do not depend on the routing: when this
-    // CTA's first item is one of them, its chunks fill team 0's stages right away
-    const int depth0 = dbase + (0 < dextra ? 1 : 0);
-    if (p.n_shared && (int)blockIdx.x < ntf) {
-      const int n = min(nch_gu, depth0);
-      for (int ch = 0; ch < n; ++ch) issue(0, ch, false, p.sgu, 0, (int)blockIdx.x << 4, ch);
-      job[0] = n;
-    }
-    bool ok = ld_mbar_wait(ld_route_bar(bars), 0, flags) && flags[0] == 0;
-    if (ok) {
-      const int n_tasks = meta->n_tasks, n_routed = meta->n_routed;
-      const int items_gu = n_tasks * ntf;
-      const int nq_gu = (items_gu > (int)blockIdx.x) ? (items_gu - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
-      const long long items_dn = (long long)n_tasks * ntd;
-      const int dn_lo = (int)(items_dn * blockIdx.x / nblocks), dn_hi = (int)(items_dn * (blockIdx.x + 1) / nblocks);
-      const int nq_dn = dn_hi - dn_lo;
+      {
+        const int part = lane & 3, srow = lane >> 2;
+        if (part * 4 < (bytes >> 5)) {
+          const uint32_t dst = stage + kLdScOff + srow * 32 + part * 8;
+          const size_t off = (row0 + srow) * ng + ch * 16 + part * 4;  // elements
 #pragma unroll
-      for (int t = 0; t < kLdTeams; ++t) {
-        ngu[t] = (nq_gu > t) ? (nq_gu - 1 - t) / kLdTeams + 1 : 0;
-        const int ndn = (nq_dn > t) ? (nq_dn - 1 - t) / kLdTeams + 1 : 0;
-        total[t] = ngu[t] * nch_gu + ndn * nch_dn;
-      }
-      int idle = 0;
-      for (;;) {
-        bool left = false, moved = false;
-#pragma unroll
-        for (int t = 0; t < kLdTeams; ++t) {
-          if (job[t] < total[t]) {
-            left = true;
-            const int depth = dbase + (t < dextra ? 1 : 0);
-            const int s = job[t] % depth, use = job[t] / depth;
-            if (ld_mbar_try(ld_empty_bar(bars, t, s), (use & 1) ^ 1)) {
-              int j = job[t];
-              if (j < ngu[t] * nch_gu) {
-                const int qi = j / nch_gu, ch = j - qi * nch_gu;
-                const int i = (int)blockIdx.x + (t + kLdTeams * qi) * nblocks;
-                const int ao = i / ntf, tile = i - ao * ntf;
-                const int a = p.n_shared ? (ao == 0 ? n_routed : ao - 1) : ao;
-                const bool sh = a >= n_routed;
-                issue(t, s, false, sh ? p.sgu : p.gu, meta->task_expert[a], tile << 4, ch);
-              } else {
-                j -= ngu[t] * nch_gu;
-                const int qi = j / nch_dn, ch = j - qi * nch_dn;
-                const int i = dn_lo + t + kLdTeams * qi;
-                const int a = i / ntd, tile = i - a * ntd;
-                const bool sh = a >= n_routed;
-                issue(t, s, true, sh ? p.sdn : p.dn, meta->task_expert[a], tile << 5, ch);
-              }
-              ++job[t];
-              moved = true;
-            }
+          for (int it = 0; it < 8; ++it) {
+            const int m = (it >> 1) & 1;
+            const __nv_bfloat16* base = ((it >> 2) ? bank.b : bank.s)[dn ? 0 : m];
+            ld_cp8(dst + ((it >> 1) * 16 + (it & 1) * 8) * 32,
+                   base + off + (size_t)((dn ? m * 16 : 0) + (it & 1) * 8) * ng);
           }
         }
-        if (!left) break;
-        if (moved) {
-          idle = 0;
-        } else if (++idle >= kLdSpinLimit || ((idle & 1023) == 1023 && flags[0])) {
-          ok = false;
-          break;
-        }
       }
+      ld_cp_arrive(ld_full_bar(bars, t, s));
     }
     if (!ok && lane == 0) {
       flags[0] = 1;
       atomicExch(p.sync + 3, 1);
     }
     // copies still in flight must have landed before the CTA's shared memory goes away
-#pragma unroll
-    for (int t = 0; t < kLdTeams; ++t) {
-      const int depth = dbase + (t < dextra ? 1 : 0);
-      for (int j = max(0, job[t] - depth); j < job[t]; ++j) {
-        const uint32_t bar = ld_full_bar(bars, t, j % depth);
-        const int par = (j / depth) & 1;
-        for (int i = 0; i < kLdSpinLimit && !ld_mbar_try(bar, par); ++i) {
-        }
+    for (int k = max(0, j - depth); k < j; ++k) {
+      const uint32_t bar = ld_full_bar(bars, t, k % depth);
+      const int par = (k / depth) & 1;
+      for (int i = 0; i < kLdSpinLimit && !ld_mbar_try(bar, par); ++i) {
       }
     }
     return;
@@ -745,10 +758,6 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
 
   LD_STAMP(0);
-  // ---- token rows -> shared memory (fp16, fragment order, group sums)
-  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
-                       p.sync + 3);
-  LD_STAMP(1);
   // ---- router linear: the CTA's rows blockIdx.x, blockIdx.x + grid, ...; warp w sums segment w of a row
   {
     int n_mine = 0;
@@ -801,7 +810,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       }
     }
   }
-  LD_STAMP(2);
+  LD_STAMP(1);
   // Launch count for the next launch.  Every consumer thread of this CTA has read the count (they all passed
   // the barriers above), so the CTA can sign in; the last CTA of the grid to do so bumps the count (the tags of
   // THIS launch live in registers already) and clears the sign-in counter.
@@ -812,6 +821,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
 
+  // ---- token rows -> shared memory (fp16, fragment order, group sums), while the logits travel
+  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
+                       p.sync + 3);
+  LD_STAMP(2);
   // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
   // so this is also where the CTA waits for the router threads of the other CTAs
   if (wid < T) {
@@ -828,7 +841,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     ld_sigmoid_scores(T, E, p.rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
     ld_csync();
   }
-  if (flags[0] == 0) ld_rank_select(keys, T, E, K, sel_idx);
+  ld_topk_select(keys, T, E, K, reinterpret_cast<uint32_t*>(red), reinterpret_cast<int*>(red) + T * 64, sel_idx);
   ld_csync();
   LD_STAMP(4);
   if (wid < T && flags[0] == 0)
@@ -923,6 +936,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     const int items = n_tasks * ntf;
     const int nq = (items > (int)blockIdx.x) ? (items - 1 - (int)blockIdx.x) / nblocks + 1 : 0;
     const int xs_stride = qmm_xs_stride(d);
+#pragma unroll 1
     for (int q = c.team; q < nq; q += kLdTeams) {
       const int i = (int)blockIdx.x + q * nblocks;
       const int ao = i / ntf, tile = i - ao * ntf;
@@ -948,8 +962,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         }
       }
       float acc[2][4];
-      ld_item<TT, false>(c, acc, is_sh ? p.sgu : p.gu, meta->task_expert[a], f, d >> 3, n0,
-                         lay.xs + trow * xs_stride + tig * 32, lay.zero, tok_ok, slot_g, xsum, T, srow_c);
+      ld_item<TT, false>(c, acc, d >> 3, smem_base + lay.xs + trow * xs_stride + tig * 32, smem_base + lay.zero, tok_ok, slot_g, xsum, T,
+                         srow_c);
       if (c.alive && c.wk == 0) {
         const int epi = is_sh ? p.sepi : p.epi;
 #pragma unroll
@@ -1004,10 +1018,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   {
     const int nq = c.alive ? dn_hi - dn_lo : 0;
     const int xs_stride = qmm_xs_stride(f);
+#pragma unroll 1
     for (int q = c.team; q < nq; q += kLdTeams) {
       const int i = dn_lo + q;
       const int a = i / ntd, tile = i - a * ntd;
-      const bool is_sh = a >= n_routed;
       const int n0 = tile << 5;
       const int cnt = meta->task_cnt[a];
       const bool tok_ok = tok_g < cnt;
@@ -1019,8 +1033,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         srow_c[cc] = (sl < cnt) ? (int)meta->hloc[meta->task_rows[a][sl]] : -1;
       }
       float acc[2][4];
-      ld_item<TT, true>(c, acc, is_sh ? p.sdn : p.dn, meta->task_expert[a], d, f >> 3, n0,
-                        lay.xs + srow * xs_stride + tig * 32, lay.zero, tok_ok, slot_g, xsum, p.hrows, srow_c);
+      ld_item<TT, true>(c, acc, f >> 3, smem_base + lay.xs + srow * xs_stride + tig * 32, smem_base + lay.zero, tok_ok, slot_g, xsum, p.hrows,
+                        srow_c);
       if (c.alive && c.wk == 0) {
 #pragma unroll
         for (int m = 0; m < 2; ++m)

@@ -11,7 +11,7 @@ namespace zmoe {
 
 constexpr int kLdConsumers = 512;              // threads that compute (16 warps)
 constexpr int kLdWarps = kLdConsumers / 32;    // consumer warps
-constexpr int kLdThreads = kLdConsumers + 32;  // plus one producer warp that only issues bulk copies
+constexpr int kLdThreads = kLdConsumers + 128;  // plus four producer warps (one per team) that only issue copies
 constexpr int kLdMaxT = 8;
 constexpr int kLdMaxK = 8;
 constexpr int kLdMaxRouted = kLdMaxT * kLdMaxK;  // (token, slot) rows
@@ -226,28 +226,61 @@ __device__ __forceinline__ void ld_sigmoid_scores(int T, int E, const float* bia
     keys[i] = make_uint2(~(uint32_t)(i % E), ld_order_key(vals[i] + 0.0f));
 }
 
-// Step 2, all consumer threads: rank of every score under (score descending, expert id ascending) -- one
-// unsigned 64-bit comparison of the sort keys.  The ranks of a row are a permutation, so the experts ranked
-// below K write themselves into slot order.
-__device__ __forceinline__ void ld_rank_select(const uint2* keys, int T, int E, int K, int* sel_idx) {
-  const int pairs = T * E;
-  int P = 1;  // threads that share one score's scan
-  while (P < 32 && P * 2 * pairs <= kLdConsumers) P *= 2;
-  const int lp = 31 - __clz(P);
-  const int per_pass = kLdConsumers >> lp;
-  const int part = threadIdx.x & (P - 1);
-  for (int base = 0; base < pairs; base += per_pass) {
-    const int pair = base + (threadIdx.x >> lp);
-    const bool ok = pair < pairs;
-    const int t = ok ? pair / E : 0;
-    const int i = ok ? pair - t * E : 0;
-    const unsigned long long* row = reinterpret_cast<const unsigned long long*>(keys + (size_t)t * E);
-    const unsigned long long mine = row[i];
-    int rank = 0;
-#pragma unroll 4
-    for (int j = part; j < E; j += P) rank += (row[j] > mine);
-    for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-    if (ok && part == 0 && rank < K) sel_idx[t * K + rank] = i;
+// Step 2, the selection under (score descending, expert id ascending), in two rounds of warp arg-max so that no
+// thread walks more than a handful of dependent instructions per winner:
+//   (a) one warp per 32 consecutive experts of a row picks its own K best, best first.  A round = one
+//       redux.sync.max over the lanes' order keys, a ballot of the lanes that hold the maximum, and the lowest
+//       such lane (= the lowest expert id among equals) leaves the race;
+//   (b) one warp per row picks the K best of the (E / 32) * 8 candidates the same way.  Candidate c = 8 * w + r is
+//       warp w's r-th pick: among equal scores a smaller c is a smaller expert id (ids grow with w, and a warp
+//       emits equal scores in ascending id order), so "lowest candidate among equals" is the canonical tie rule.
+// The result equals ranking every score against every other one.  cand_key / cand_idx hold 64 entries per row.
+// Contains a consumer-wide barrier: every consumer thread must call it.
+__device__ __forceinline__ void ld_topk_select(const uint2* keys, int T, int E, int K, uint32_t* cand_key,
+                                               int* cand_idx, int* sel_idx) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nw = (E + 31) >> 5;  // <= 8
+  for (int task = wid; task < T * nw; task += kLdWarps) {
+    const int t = task / nw, w = task - t * nw;
+    const int i = w * 32 + lane;
+    bool live = i < E;
+    const uint32_t key = live ? keys[(size_t)t * E + i].y : 0u;
+#pragma unroll 1
+    for (int r = 0; r < kLdMaxK; ++r) {
+      const uint32_t mx = __reduce_max_sync(0xffffffffu, live ? key : 0u);
+      const uint32_t ball = __ballot_sync(0xffffffffu, live && key == mx);
+      const int src = __ffs(ball) - 1;  // -1: the warp has run out of experts
+      if (lane == 0) {
+        cand_key[t * 64 + w * 8 + r] = mx;
+        cand_idx[t * 64 + w * 8 + r] = (r < K && src >= 0) ? w * 32 + src : -1;
+      }
+      if (lane == src) live = false;
+    }
+  }
+  ld_csync();
+  if (wid < T) {
+    const int t = wid;
+    const int nc = nw * 8;
+    const int i0 = cand_idx[t * 64 + lane];
+    const int i1 = (lane + 32 < nc) ? cand_idx[t * 64 + lane + 32] : -1;
+    bool v0 = lane < nc && i0 >= 0, v1 = i1 >= 0;
+    const uint32_t k0 = cand_key[t * 64 + lane], k1 = (lane + 32 < nc) ? cand_key[t * 64 + lane + 32] : 0u;
+#pragma unroll 1
+    for (int r = 0; r < K; ++r) {
+      const uint32_t m0 = v0 ? k0 : 0u, m1 = v1 ? k1 : 0u;
+      const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m0, m1));
+      const uint32_t b0 = __ballot_sync(0xffffffffu, v0 && k0 == mx);
+      const uint32_t b1 = __ballot_sync(0xffffffffu, v1 && k1 == mx);
+      const int src = b0 ? __ffs(b0) - 1 : __ffs(b1) - 1;
+      const int won = __shfl_sync(0xffffffffu, b0 ? i0 : i1, src < 0 ? 0 : src);
+      if (lane == 0) sel_idx[t * K + r] = (src >= 0 && won >= 0) ? won : 0;
+      if (lane == src) {
+        if (b0)
+          v0 = false;
+        else
+          v1 = false;
+      }
+    }
   }
 }
 

@@ -92,9 +92,10 @@ class MoELayer:
             return 0
         return int(_lib.load().zmoe_layer_decode_workspace_bytes(ctypes.byref(self._desc), T))
 
-    def forward_fused(self, x: torch.Tensor) -> torch.Tensor:
-        """The whole block in one cooperative launch (``zmoe_layer_decode``); raises if the shape is outside it."""
+    def forward_fused(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The whole block in one launch (``zmoe_layer_decode``); raises if the shape is outside it."""
         T = x.shape[0]
+        dst = self.out if out is None else out
         ws = self._fused_ws.get(T)
         if ws is None:
             if torch.cuda.is_current_stream_capturing():
@@ -108,8 +109,13 @@ class MoELayer:
             self._fused_ws[T] = ws
         p = ops._ptr
         _lib.check(_lib.load().zmoe_layer_decode(ctypes.byref(self._desc), p(x), x.stride(0), T, p(ws), ws.numel(),
-                                                 p(self.weights), p(self.indices), p(self.out), ops._stream()))
-        return self.out[:T]
+                                                 p(self.weights), p(self.indices), p(dst), ops._stream()))
+        return dst[:T]
+
+    def launch_count(self, T: int) -> int:
+        """How many one-launch passes the T-token workspace has seen (the kernel's own launch counter)."""
+        ws = self._fused_ws.get(T)
+        return 0 if ws is None else int(ws[:32].view(torch.int32)[4].item())
 
     def router_logits(self, T: int) -> torch.Tensor:
         """The (T, E) bf16 router logits of the last forward pass over T tokens (whichever path ran it)."""
@@ -249,8 +255,9 @@ class MoELayer:
         _lib.check(lib.zmoe_gather_qmm(p(self.sh_h), T, f, p(S["down_w"]), p(S["down_s"]), p(S["down_b"]), 1,
                                        cfg.d_model, f, self.gs, qm, p(plan), T, T, 1, p(self.sh_y), st))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x (T, d_model) bfloat16 on this layer's device -> (T, d_model) bfloat16 (a view of an owned buffer)."""
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x (T, d_model) bfloat16 on this layer's device -> (T, d_model) bfloat16: ``out`` when given (contiguous,
+        at least T rows), else a view of a buffer the layer owns and overwrites on its next call."""
         cfg = self.cfg
         if x.dtype != torch.bfloat16 or x.ndim != 2 or x.shape[1] != cfg.d_model:
             raise ValueError(f"expected (T, {cfg.d_model}) bfloat16 activations, got {tuple(x.shape)} {x.dtype}")
@@ -269,7 +276,7 @@ class MoELayer:
                 if ok is None:
                     ok = self._fused_ok[T] = self.fused_workspace_bytes(T) > 0
                 if ok:
-                    return self.forward_fused(x)
+                    return self.forward_fused(x, out)
             residual = None
             if cfg.n_shared:
                 # the shared expert depends on x only: it runs on a side stream beside the router and the routed
@@ -285,10 +292,11 @@ class MoELayer:
             self.experts(x)
             if cfg.n_shared:
                 cur.wait_stream(self._side)
+            dst = self.out if out is None else out
             _lib.check(_lib.load().zmoe_moe_combine(
                 ops._ptr(self.y), _lib.BF16, ops._ptr(self.weights), _lib.F32, T, cfg.top_k, cfg.d_model,
-                self.combine_mode, ops._ptr(self.out), 3 if cfg.family == "generic" else 1, ops._ptr(residual),
+                self.combine_mode, ops._ptr(dst), 3 if cfg.family == "generic" else 1, ops._ptr(residual),
                 ops._stream()))
-        return self.out[:T]
+        return dst[:T]
 
     __call__ = forward

@@ -118,6 +118,7 @@ def unpatch(model: nn.Module) -> nn.Module:
             m.__class__ = orig
             m.__dict__.pop("_zmlx_original_call", None)
         m.__dict__.pop("_zmlx_original_switch_call", None)
+        m.__dict__.pop("_zmlx_fast_layer", None)
     if hasattr(model, "_zmlx_patch_result"):
         del model._zmlx_patch_result
     return model

@@ -1,10 +1,17 @@
 """MoE block pattern: reproduce each family's gating, run the experts through the fused kernels, combine.
 
 Mirrors src/zmlx/patch/patterns/moe_mlp.py (matching :773-785, apply :787-881, patched call :883-1063) for torch
-modules.  Differences from the reference, all of them about Metal performance guards rather than semantics:
-the fused SwiGLU path is on for every family by default (the reference keeps Qwen opt-in, :835-841) and has no
-token-count cap unless ``moe_fused_swiglu_max_tokens`` is given (the reference caps at 1 because its Metal kernel
-re-reads an expert per row, :296-298).  The environment variables that select *semantics* keep their names.
+modules.  What is captured at patch time (:787-881: the gate attribute, the expert bank, k, the family, the
+combine mode) is turned into one ``MoELayer`` over the module's own tensors, so that a patched block is ONE
+launch (``zmoe_layer_decode``: router linear, top-k, gate/up + SwiGLU, down, combine, shared expert) for up to
+eight tokens and the plan-once separate kernels beyond that; the call order of :883-1063 (gate -> experts ->
+combine -> + shared_experts(x)) is what those kernels implement.  Blocks the kernels do not cover (an unknown
+gate, 8-bit banks, a custom activation) keep the op-by-op path below, which calls the same operator surface as
+the reference.  Differences from the reference, all of them about Metal performance guards rather than
+semantics: the fused SwiGLU path is on for every family by default (the reference keeps Qwen opt-in, :835-841)
+and has no token-count cap unless ``moe_fused_swiglu_max_tokens`` is given (the reference caps at 1 because its
+Metal kernel re-reads an expert per row, :296-298).  The environment variables that select *semantics* keep
+their names; ``ZMLX_MOE_FAST_LAYER=0`` forces the op-by-op path.
 """
 
 from __future__ import annotations
@@ -27,6 +34,7 @@ _QWEN_FUSED_SWIGLU_ENV = "ZMLX_QWEN_FUSED_SWIGLU"
 _GLM_FUSED_DOWNPROJ_COMBINE_ENV = "ZMLX_GLM_FUSED_DOWNPROJ_COMBINE"
 _QWEN_FUSED_DOWNPROJ_COMBINE_ENV = "ZMLX_QWEN_FUSED_DOWNPROJ_COMBINE"
 _QWEN_FUSED_ROUTER_TOPK_ENV = "ZMLX_QWEN_FUSED_ROUTER_TOPK"
+_FAST_LAYER_ENV = "ZMLX_MOE_FAST_LAYER"
 
 
 def _combined_name(mod: Any) -> str:
@@ -159,6 +167,97 @@ def _fused_switch_mlp_call(switch_mlp: Any, x: torch.Tensor, indices: torch.Tens
     return proj.reshape(lead + (k, proj.shape[-1]))
 
 
+def _bank_params(bank: Any, prefix: str = "") -> dict | None:
+    """The packed tensors of a SwitchGLU-style bank in ``MoELayer``'s naming; None when it is not a 4-bit bank."""
+    out = {}
+    for name in ("gate", "up", "down"):
+        proj = getattr(bank, f"{name}_proj", None)
+        if proj is None or not _is_quantized_switch_linear(proj) or int(proj.bits) != 4:
+            return None
+        if getattr(proj, "bias", None) is not None:
+            return None
+        out[f"{name}_w"], out[f"{name}_s"], out[f"{name}_b"] = proj.weight, proj.scales, proj.get("biases")
+    return out
+
+
+def _build_fast_layer(module: Any, switch_mlp: Any, gate_attr: str, k: int, *, is_qwen3: bool, is_glm: bool,
+                      is_gpt_oss: bool, glm_combine_mode: str, qwen_combine_mode: str):
+    """One ``MoELayer`` over the module's tensors (what moe_mlp.py:787-881 captures at patch time), or None when
+    the block is outside what the kernels cover.  Nothing is copied: the layer points at the module's buffers."""
+    from ...layer import MoELayer
+    from ...synthetic import MoEConfig
+
+    if not _env_flag(_FAST_LAYER_ENV, True) or is_gpt_oss or not _is_standard_swiglu_activation(switch_mlp):
+        return None
+    routed = _bank_params(switch_mlp)
+    if routed is None:
+        return None
+    gp = switch_mlp.gate_proj
+    mode = getattr(gp, "mode", "affine")
+    gs = int(gp.group_size)
+    if (mode, gs) not in (("affine", 64), ("mxfp4", 32)):
+        return None
+    if any(getattr(getattr(switch_mlp, f"{n}_proj"), "mode", "affine") != mode
+           or int(getattr(switch_mlp, f"{n}_proj").group_size) != gs for n in ("up", "down")):
+        return None
+    gate = getattr(module, gate_attr)
+    gw = getattr(gate, "weight", None)
+    if gw is None or gw.ndim != 2 or gw.dtype != torch.bfloat16 or not gw.is_cuda:
+        return None
+    if getattr(gate, "bias", None) is not None:
+        return None
+    E, f, d = int(gp.weight.shape[0]), int(gp.weight.shape[1]), int(gp.weight.shape[2]) * 8
+    if tuple(gw.shape) != (E, d):
+        return None
+    sigmoid_gate = all(hasattr(gate, a) for a in ("e_score_correction_bias", "n_group", "topk_group",
+                                                   "routed_scaling_factor"))
+    params = dict(routed)
+    params["router_w"] = gw
+    n_group = topk_group = 1
+    scaling = 1.0
+    norm = bool(getattr(module, "norm_topk_prob", False))
+    combine = None
+    if sigmoid_gate:
+        if not bool(getattr(gate, "norm_topk_prob", True)):
+            return None  # the kernels normalise the selected affinities, as the reference's fused router does
+        family = "glm" if is_glm else "deepseek"
+        params["expert_bias"] = gate.e_score_correction_bias.to(torch.float32)
+        n_group, topk_group = int(gate.n_group), int(gate.topk_group)
+        scaling = float(gate.routed_scaling_factor)
+        if is_glm:
+            combine = {"fp32": "fp32", "exact": "exact"}.get(glm_combine_mode, "fp32_no_fma")
+    elif isinstance(gate, nn.Linear):
+        if is_qwen3:
+            family = "qwen3"
+            # "off" = (y * scores[..., None]).sum(-2): multiply, then sum == the no-FMA contract
+            combine = {"fp32": "fp32", "fp32_no_fma": "fp32_no_fma", "exact": "exact"}.get(qwen_combine_mode, "no_fma")
+            if qwen_combine_mode in ("fp32", "fp32_no_fma"):
+                return None  # those return float32 rows (moe_mlp.py:1029-1040): left to the op-by-op path
+        else:
+            family = "generic"
+            bias = getattr(module, "expert_bias", None)
+            params["expert_bias"] = None if bias is None else bias.to(torch.float32)
+    else:
+        return None
+    params.setdefault("expert_bias", None)
+    shared_mod = getattr(module, "shared_experts", None)
+    n_shared = 0
+    params["shared"] = None
+    if shared_mod is not None:
+        sh = _bank_params(shared_mod)
+        if sh is None or tuple(sh["gate_w"].shape) != (1, f, d // 8):
+            return None
+        params["shared"] = sh
+        n_shared = 1
+    cfg = MoEConfig(name=f"patched-{module.__class__.__name__}", config_id=0, d_model=d, n_experts=E, top_k=int(k),
+                    d_ff=f, family=family, mode=mode, group_size=gs, n_shared=n_shared, n_group=n_group,
+                    topk_group=topk_group, routed_scaling_factor=scaling, norm_topk_prob=norm)
+    try:
+        return MoELayer(cfg, params, max_tokens=8, combine=combine)
+    except Exception:
+        return None
+
+
 class _MoEMLPPattern:
     @property
     def name(self) -> str:
@@ -197,12 +296,26 @@ class _MoEMLPPattern:
         max_tokens = config.moe_fused_swiglu_max_tokens
         glm_combine_mode = _glm_combine_mode()
         qwen_combine_mode = _qwen_combine_mode()
+        fast = None
+        if use_fused_swiglu:
+            fast = _build_fast_layer(module, switch_mlp, gate_attr, num_experts_per_tok, is_qwen3=is_qwen3,
+                                     is_glm=is_glm, is_gpt_oss=is_gpt_oss, glm_combine_mode=glm_combine_mode,
+                                     qwen_combine_mode=qwen_combine_mode)
+        module._zmlx_fast_layer = fast
         if config.verbose:
             gp = switch_mlp.gate_proj
             print(f"  [moe_mlp] fused SwiGLU={'on' if use_fused_swiglu else 'off'} "
-                  f"(bits={getattr(gp, 'bits', '?')}, gs={getattr(gp, 'group_size', '?')})")
+                  f"(bits={getattr(gp, 'bits', '?')}, gs={getattr(gp, 'group_size', '?')}), "
+                  f"one-launch block={'on' if fast is not None else 'off'}")
 
         def patched_call(self_mod: Any, x: Any) -> Any:
+            if fast is not None and x.dtype == torch.bfloat16 and x.is_cuda:
+                tokens = x.numel() // x.shape[-1]
+                if _should_fuse_swiglu_tokens(tokens, max_tokens):
+                    x2 = x.reshape(tokens, x.shape[-1])
+                    out = torch.empty_like(x2)  # a fresh result, as every operator of the reference returns
+                    fast.forward(x2, out=out)
+                    return out.reshape(x.shape)
             shared = getattr(self_mod, "shared_experts", None)
             indices, gate_weights = _gating(self_mod, x, gate_attr, num_experts_per_tok, is_qwen3=is_qwen3,
                                             is_gpt_oss=is_gpt_oss)
