@@ -38,6 +38,7 @@
 #include <cuda_fp16.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "layer_route.cuh"
 #include "qmm_common.cuh"
@@ -45,12 +46,21 @@
 namespace zmoe {
 
 constexpr int kLdTeams = 4;                          // teams of consumer warps; a team owns one item at a time
-constexpr int kLdSegBytes = 512;                     // bytes of one weight row in one stage
+#ifndef ZMOE_LD_SEG_BYTES
+#define ZMOE_LD_SEG_BYTES 512
+#endif
+constexpr int kLdSegBytes = ZMOE_LD_SEG_BYTES;       // bytes of one weight row in one stage (256 or 512).  A team holds
+                                                     // one stage while it computes, so smaller stages leave more of
+                                                     // the ring in flight
+constexpr int kLdSegGroups = kLdSegBytes / 32;       // groups of 64 codes of a row in one stage
+constexpr int kLdGW = kLdSegGroups / 4;              // ... of which each warp of the team takes this many
 constexpr int kLdSegStride = kLdSegBytes + 32;       // == 32 mod 128: the 8-byte fragment reads of a warp hit all banks once
 constexpr int kLdScOff = 32 * kLdSegStride;          // after the 32 row segments of a stage: their scales and biases,
-constexpr int kLdScBytes = 2048;                     // [scale | bias][matrix][row 0..15][16 groups] bfloat16
+constexpr int kLdScRow = kLdSegGroups * 2;           // [scale | bias][matrix][row 0..15][groups of the stage] bfloat16
+constexpr int kLdScBytes = 64 * kLdScRow;
 constexpr int kLdSlotBytes = kLdScOff + kLdScBytes;  // one stage
-constexpr int kLdMaxDepth = 6;                       // stages per team at most
+static_assert(kLdSegBytes == 256 || kLdSegBytes == 512, "stage geometry");
+constexpr int kLdMaxDepth = 8;                       // stages per team at most
 constexpr int kLdSmemLimit = 227 * 1024;
 constexpr int kLdMaxMine = 4;                        // router rows per CTA at most (E <= 4 * grid)
 
@@ -99,7 +109,7 @@ struct LdMeta {
 };
 
 struct LdSmem {
-  int xs, xsum, isig, rowmax, route, meta, red, flags, bars, zero, ring, total;
+  int xs, xsum, isig, rowmax, route, rbias, meta, red, flags, bars, zero, ring, total;
 };
 
 __host__ __device__ inline int ld_align16(int a) { return (a + 15) & ~15; }
@@ -122,6 +132,8 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   a += ld_align16(nr * 4);
   m.route = a;  // per row: sort keys, scores, logits, group scratch, winners
   a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);
+  m.rbias = a;  // the router's selection bias (a constant: copied in before the dependency wait)
+  a += ld_align16(E * 4);
   m.meta = a;
   a += ld_align16((int)sizeof(LdMeta));
   m.red = a;  // K-split partial sums of the teams (and the router's segment sums before that)
@@ -242,6 +254,10 @@ __device__ __forceinline__ uint4 ld_lds128(uint32_t addr) {
   return v;
 }
 
+#define LD_STAMP_NS(i)                                                                         \
+  do {                                                                                         \
+    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[i] = (long long)ld_now_ns(); \
+  } while (0)
 #define LD_STAMP(i)                                                            \
   do {                                                                         \
     if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[i] = clock64(); \
@@ -265,8 +281,11 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
 #pragma unroll 1
   for (int base = (int)(tid & ~31u); base < total; base += kLdConsumers) {
     const int i = base + lane;
+    int t = -1;
+    uint32_t m = 0;
     if (i < total) {
-      const int t = i / K8, blk = i - t * K8;
+      t = i / K8;
+      const int blk = i - t * K8;
       uint4 v;
       if (TAGGED) {
         const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)rowlist[t] * ld + blk * 8;
@@ -296,9 +315,15 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
       *reinterpret_cast<uint4*>(xs + t * xs_stride + blk * 16) = v;
       // magnitudes of bfloat16 order like their low 15 bits
       const uint32_t q[4] = {v.x, v.y, v.z, v.w};
-      uint32_t m = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) m = max(m, max(q[k] & 0x7fffu, (q[k] >> 16) & 0x7fffu));
+    }
+    // one shared-memory atomic per warp when the warp sits inside one row (the common case), else one per lane
+    const int t0 = __shfl_sync(0xffffffffu, t, 0);
+    if (__all_sync(0xffffffffu, t == t0 || t < 0)) {
+      m = __reduce_max_sync(0xffffffffu, m);
+      if (lane == 0 && t0 >= 0) atomicMax(rowmax + t0, (int)m);
+    } else if (t >= 0) {
       atomicMax(rowmax + t, (int)m);
     }
   }
@@ -375,12 +400,14 @@ __device__ __forceinline__ uint32_t ld_empty_bar(uint32_t bars, int team, int s)
 }
 __device__ __forceinline__ uint32_t ld_route_bar(uint32_t bars) { return bars + 2 * kLdTeams * kLdMaxDepth * 8; }
 
-// Stream position p of a warp (four groups per chunk) -> group of the row: chunk p / 4 holds quads
-// 4 * chunk .. 4 * chunk + 3, warp wk owns quad 4 * chunk + wk.
-__device__ __forceinline__ int ld_group_of(int p, int wk) { return ((((p >> 2) << 2) + wk) << 2) + (p & 3); }
+// Stream position p of a warp (kLdGW groups per chunk) -> group of the row: chunk p / kLdGW holds groups
+// kLdSegGroups * chunk .., warp wk owns kLdGW consecutive ones of them.
+__device__ __forceinline__ int ld_group_of(int p, int wk) {
+  return (p / kLdGW) * kLdSegGroups + wk * kLdGW + (p % kLdGW);
+}
 
 // Scales and biases of a lane's column(s) from the stage's copy: sb[m][h][0] scale, [1] bias of row g + 8h of
-// matrix m, for local group `gl` of the chunk (0..15).  With one token a lane's two columns are two adjacent
+// matrix m, for local group `gl` of the chunk.  With one token a lane's two columns are two adjacent
 // groups (one 32-bit read brings both); otherwise both columns are the same group.
 template <int TT>
 __device__ __forceinline__ void ld_load_sb(uint32_t (&sb)[2][2][2], uint32_t sc, int g, int gl) {
@@ -390,7 +417,7 @@ __device__ __forceinline__ void ld_load_sb(uint32_t (&sb)[2][2][2], uint32_t sc,
     for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int arr = 0; arr < 2; ++arr) {
-        const uint32_t addr = sc + (uint32_t)(((arr * 2 + m) * 16 + g + 8 * h) * 32 + gl * 2);
+        const uint32_t addr = sc + (uint32_t)(((arr * 2 + m) * 16 + g + 8 * h) * kLdScRow + gl * 2);
         if (TT == 1)
           asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sb[m][h][arr]) : "r"(addr));
         else
@@ -448,6 +475,7 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
   for (int m = 0; m < 2; ++m)
 #pragma unroll
     for (int h = 0; h < 2; ++h) sb[m][h][0] = sb[m][h][1] = 0u;
+  int open_p0 = -1;  // first stream position of a block of multiplexed groups that still awaits its fix-up
 
 #pragma unroll 1
   for (int ch = 0; ch < nch; ++ch) {
@@ -457,31 +485,30 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
       c.alive = false;
       c.flags[0] = 1;
     }
-    const bool have = c.alive && ((ch * 4 + wk) * 128 < rb);  // the warp's quad exists in this row
+    const bool have = c.alive && ((ch * kLdSegGroups + wk * kLdGW) * 32 < rb);  // the warp's groups exist in this row
     if (have) {
       const uint32_t stage = c.ring + (uint32_t)(c.slot0 + c.slot) * kLdSlotBytes;
-      const uint32_t wbase = stage + g * kLdSegStride + wk * 128 + tig * 8;
-      // one token: a block of eight groups spans two chunks; a lane's columns are groups of the first chunk
-      // (tig 0, 1) or of the second (tig 2, 3), and their scales are read while that chunk's stage is held
-      if (TT == 1 && (tig >> 1) == (ch & 1)) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * 4 + ((2 * tig) & 3));
-      const uint32_t xchunk = xaddr + (uint32_t)(ch * 4 + wk) * 512;
-      const int jm = g - (ch & 1) * 4;  // one token: the group of this chunk that the lane's column carries
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int slot = (TT == 1) ? ((ch & 1) * 4 + j) : (j % GPB);
-        const int pos = ch * 4 + j;
-        if (TT > 1 && slot == 0) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * 4 + j + (2 * tig) / TT);
+      const uint32_t wbase = stage + g * kLdSegStride + wk * (kLdGW * 32) + tig * 8;
+      const uint32_t xchunk = xaddr + (uint32_t)(ch * kLdSegGroups + wk * kLdGW) * 128;
+      // slot (position inside the block of GPB multiplexed groups) of the chunk's first group
+      const int slot0 = (GPB > kLdGW) ? (ch % (GPB / kLdGW > 0 ? GPB / kLdGW : 1)) * kLdGW : 0;
+      // the slot of the lane's own column(s): its scales and biases are read while that group's stage is held
+      const int qlane = (TT == 1) ? 2 * tig : ((TT == 8) ? 0 : (2 * tig) / TT);
+      auto group = [&](auto jc) {
+        constexpr int j = decltype(jc)::value;
+        const int slot = (GPB > kLdGW) ? slot0 + j : (j % GPB);
+        const int pos = ch * kLdGW + j;
+        if (slot == qlane) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * kLdGW + j);
         // lanes whose column carries another group (or no token) read the zero page
-        const bool mine = (TT == 1) ? (j == jm) : (tok_ok && (TT == 8 || slot_g == slot));
+        const bool mine = tok_ok && (TT == 8 || slot_g == slot);
         const uint32_t xa = mine ? xchunk + j * 128 : zaddr;
         const uint4 xb0 = ld_lds128<0>(xa);
         const uint4 xb1 = ld_lds128<16>(xa);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          const uint2 wa = (m == 0) ? (j == 0 ? ld_lds64<0>(wbase) : j == 1 ? ld_lds64<32>(wbase) : j == 2 ? ld_lds64<64>(wbase) : ld_lds64<96>(wbase))
-                                    : (j == 0 ? ld_lds64<16 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<16 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<16 * kLdSegStride + 64>(wbase) : ld_lds64<16 * kLdSegStride + 96>(wbase));
-          const uint2 wb = (m == 0) ? (j == 0 ? ld_lds64<8 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<8 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<8 * kLdSegStride + 64>(wbase) : ld_lds64<8 * kLdSegStride + 96>(wbase))
-                                    : (j == 0 ? ld_lds64<24 * kLdSegStride>(wbase) : j == 1 ? ld_lds64<24 * kLdSegStride + 32>(wbase) : j == 2 ? ld_lds64<24 * kLdSegStride + 64>(wbase) : ld_lds64<24 * kLdSegStride + 96>(wbase));
+          const uint2 wa = (m == 0) ? ld_lds64<j * 32>(wbase) : ld_lds64<16 * kLdSegStride + j * 32>(wbase);
+          const uint2 wb = (m == 0) ? ld_lds64<8 * kLdSegStride + j * 32>(wbase)
+                                    : ld_lds64<24 * kLdSegStride + j * 32>(wbase);
           const uint32_t wa8 = wa.x >> 8, wb8 = wb.x >> 8;
           mma_f16_m16n8k16(dg[m][0], deq_h_lo(wa.x), deq_h_lo(wb.x), deq_h_hi(wa.x), deq_h_hi(wb.x), xb0.x, xb0.y);
           mma_f16_m16n8k16(dg[m][1], deq_h_lo(wa8), deq_h_lo(wb8), deq_h_hi(wa8), deq_h_hi(wb8), xb0.z, xb0.w);
@@ -498,7 +525,16 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
               dg[m][0][jj] = 0.0f;
               dg[m][1][jj] = 0.0f;
             }
+          open_p0 = -1;
+        } else {
+          open_p0 = pos - slot;
         }
+      };
+      group(std::integral_constant<int, 0>{});
+      group(std::integral_constant<int, 1>{});
+      if constexpr (kLdGW == 4) {
+        group(std::integral_constant<int, 2>{});
+        group(std::integral_constant<int, 3>{});
       }
     }
     // ---- hand the stage back to the producer
@@ -509,8 +545,9 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
       ++c.use;
     }
   }
-  // one token: an odd number of chunks leaves half a block of eight groups without its fix-up
-  if (TT == 1 && (nch & 1) && c.alive) ld_fixup<TT>(acc, dg, sb, xsum, rs, srow_c, ng, (nch - 1) * 4, wk, tig);
+  // a warp whose groups end inside a block of multiplexed groups (rows that are not a multiple of the block, or
+  // a last chunk that holds groups of the team's first warps only) still owes that block its fix-up
+  if (open_p0 >= 0 && c.alive) ld_fixup<TT>(acc, dg, sb, xsum, rs, srow_c, ng, open_p0, wk, tig);
 
   // ---- K-split: the partial sums of warps 1..3 go to the team's first warp in warp order
   const int it = c.itn++;
@@ -592,6 +629,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   // stages of team t: depth_of(t) consecutive slots from slot0_of(t)
   const int dbase = p.slots / kLdTeams, dextra = p.slots % kLdTeams;
 
+  LD_STAMP_NS(10);
   // Router rows are constants: a consumer warp's pieces of the CTA's first two rows are requested before anything
   // that depends on the previous kernel of the stream, so that with programmatic dependent launch their HBM
   // latency hides behind that kernel.
@@ -620,6 +658,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   }
   if (tid < 32) flags[tid] = 0;
   if (tid < 8) reinterpret_cast<uint32_t*>(smem + lay.zero)[tid] = 0u;
+  if (p.rbias != nullptr)
+    for (int i = tid; i < E; i += kLdThreads) reinterpret_cast<float*>(smem + lay.rbias)[i] = __ldg(p.rbias + i);
   for (int i = tid; i < kLdMaxTasks; i += kLdThreads) meta->task_cnt[i] = 0;
   __syncthreads();
   if (p.pdl) pdl_trigger();  // the next kernel of the stream may be set up now; it waits for this one to finish
@@ -693,29 +733,34 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       const uint32_t stage = ring + (uint32_t)(slot0 + s) * kLdSlotBytes;
       const size_t row0 = (size_t)e * N + n0;
       {
-        const uint32_t dst = stage + lane * 16;
-        const size_t off = row0 * rb + (size_t)ch * kLdSegBytes + lane * 16;
+        // weights: 16 bytes per lane; kLdSegBytes / 16 lanes cover one row segment
+        constexpr int LPS = kLdSegBytes / 16, SPI = 32 / LPS;  // lanes per segment, segments per instruction
+        const int piece = lane % LPS, sub = lane / LPS;
+        const uint32_t dst = stage + sub * kLdSegStride + piece * 16;
+        const size_t off = row0 * rb + (size_t)ch * kLdSegBytes + (size_t)sub * rb + piece * 16;
         const unsigned char* src0 = reinterpret_cast<const unsigned char*>(bank.w[0]) + off;
         const unsigned char* src1 =
             dn ? src0 + (size_t)16 * rb : reinterpret_cast<const unsigned char*>(bank.w[1]) + off;
-        if (lane * 16 < bytes) {
+        if (piece * 16 < bytes) {
 #pragma unroll
-          for (int r = 0; r < 16; ++r) ld_cp16(dst + r * kLdSegStride, src0 + (size_t)r * rb, pol);
+          for (int r = 0; r < 16; r += SPI) ld_cp16(dst + r * kLdSegStride, src0 + (size_t)r * rb, pol);
 #pragma unroll
-          for (int r = 0; r < 16; ++r) ld_cp16(dst + (16 + r) * kLdSegStride, src1 + (size_t)r * rb, pol);
+          for (int r = 0; r < 16; r += SPI) ld_cp16(dst + (16 + r) * kLdSegStride, src1 + (size_t)r * rb, pol);
         }
       }
       {
-        const int part = lane & 3, srow = lane >> 2;
+        // scales and biases: 8 bytes per lane; kLdScRow / 8 lanes cover the groups of one row of one tensor
+        constexpr int PPP = kLdScRow / 8, RPI = 32 / PPP;  // parts per piece, rows per instruction
+        const int part = lane % PPP, srow = lane / PPP;
         if (part * 4 < (bytes >> 5)) {
-          const uint32_t dst = stage + kLdScOff + srow * 32 + part * 8;
-          const size_t off = (row0 + srow) * ng + ch * 16 + part * 4;  // elements
+          const uint32_t dst = stage + kLdScOff + srow * kLdScRow + part * 8;
+          const size_t off = (row0 + srow) * ng + ch * kLdSegGroups + part * 4;  // elements
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int m = (it >> 1) & 1;
-            const __nv_bfloat16* base = ((it >> 2) ? bank.b : bank.s)[dn ? 0 : m];
-            ld_cp8(dst + ((it >> 1) * 16 + (it & 1) * 8) * 32,
-                   base + off + (size_t)((dn ? m * 16 : 0) + (it & 1) * 8) * ng);
+          for (int it = 0; it < 64 / RPI; ++it) {
+            const int am = (it * RPI) >> 4, r0 = (it * RPI) & 15;  // tensor (scale | bias, matrix), first row
+            const int m = am & 1;
+            const __nv_bfloat16* base = ((am >> 1) ? bank.b : bank.s)[dn ? 0 : m];
+            ld_cp8(dst + (am * 16 + r0) * kLdScRow, base + off + (size_t)((dn ? m * 16 : 0) + r0) * ng);
           }
         }
       }
@@ -750,10 +795,12 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   float* lgs = vals + T * E;
   float* gsc = lgs + T * E;
   int* sel_idx = reinterpret_cast<int*>(gsc + T * 64);
+  const float* rbias = p.rbias != nullptr ? reinterpret_cast<const float*>(smem + lay.rbias) : nullptr;
 
   if (p.pdl) pdl_wait();  // nothing below may run before the previous kernel has finished and flushed
   // launch count: every consumer thread reads it here; the last CTA to sign in (below) bumps it for the next
   // launch; tag of this launch's words
+  LD_STAMP_NS(11);
   const int epoch = __ldcg(p.sync + 4);
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
 
@@ -828,7 +875,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
   // so this is also where the CTA waits for the router threads of the other CTAs
   if (wid < T) {
-    const bool okr = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, p.rbias, vals + wid * E,
+    const bool okr = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, rbias, vals + wid * E,
                                      lgs + wid * E, keys + wid * E, lane);
     if (!okr && lane == 0) {
       flags[0] = 1;
@@ -838,10 +885,13 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   ld_csync();
   LD_STAMP(3);
   if (p.family == 2) {
-    ld_sigmoid_scores(T, E, p.rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
+    ld_sigmoid_scores(T, E, rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
     ld_csync();
   }
-  ld_topk_select(keys, T, E, K, reinterpret_cast<uint32_t*>(red), reinterpret_cast<int*>(red) + T * 64, sel_idx);
+  if (T * E <= 128)  // uniform over the CTA
+    ld_rank_select(keys, T, E, K, sel_idx);
+  else
+    ld_topk_select(keys, T, E, K, reinterpret_cast<uint32_t*>(red), reinterpret_cast<int*>(red) + T * 64, sel_idx);
   ld_csync();
   LD_STAMP(4);
   if (wid < T && flags[0] == 0)
@@ -1111,6 +1161,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
   LD_STAMP(9);
+  LD_STAMP_NS(12);
 }
 
 // ------------------------------------------------------------------ host side

@@ -226,8 +226,33 @@ __device__ __forceinline__ void ld_sigmoid_scores(int T, int E, const float* bia
     keys[i] = make_uint2(~(uint32_t)(i % E), ld_order_key(vals[i] + 0.0f));
 }
 
-// Step 2, the selection under (score descending, expert id ascending), in two rounds of warp arg-max so that no
-// thread walks more than a handful of dependent instructions per winner:
+// Step 2, small expert counts: rank of every score under (score descending, expert id ascending) by all
+// consumer threads -- one unsigned 64-bit comparison of the sort keys per pair.  The ranks of a row are a
+// permutation, so the experts ranked below K write themselves into slot order.
+__device__ __forceinline__ void ld_rank_select(const uint2* keys, int T, int E, int K, int* sel_idx) {
+  const int pairs = T * E;
+  int P = 1;  // threads that share one score's scan
+  while (P < 32 && P * 2 * pairs <= kLdConsumers) P *= 2;
+  const int lp = 31 - __clz(P);
+  const int per_pass = kLdConsumers >> lp;
+  const int part = threadIdx.x & (P - 1);
+  for (int base = 0; base < pairs; base += per_pass) {
+    const int pair = base + (threadIdx.x >> lp);
+    const bool ok = pair < pairs;
+    const int t = ok ? pair / E : 0;
+    const int i = ok ? pair - t * E : 0;
+    const unsigned long long* row = reinterpret_cast<const unsigned long long*>(keys + (size_t)t * E);
+    const unsigned long long mine = row[i];
+    int rank = 0;
+#pragma unroll 4
+    for (int j = part; j < E; j += P) rank += (row[j] > mine);
+    for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+    if (ok && part == 0 && rank < K) sel_idx[t * K + rank] = i;
+  }
+}
+
+// Step 2, large expert counts (where all-pairs ranking costs too many comparisons): the same selection in two
+// rounds of warp arg-max:
 //   (a) one warp per 32 consecutive experts of a row picks its own K best, best first.  A round = one
 //       redux.sync.max over the lanes' order keys, a ballot of the lanes that hold the maximum, and the lowest
 //       such lane (= the lowest expert id among equals) leaves the race;
