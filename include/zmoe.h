@@ -265,14 +265,23 @@ typedef struct zmoe_layer_desc {
   zmoe_expert_bank shared;  /* ignored when n_shared == 0 */
   int32_t debug_flags;      /* 0 in production; ZMOE_DEBUG_* bits are test hooks */
   int32_t reserved;
-  void* debug_stamps;       /* NULL in production; else 16 int64 of device memory: CTA 0 records its cycle
-                               counter at the phase boundaries (token staging, router linear, logits received,
+  void* debug_stamps;       /* NULL in production; else 32 int64 of device memory: CTA 0 records its cycle
+                               counter at the phase boundaries (router linear, token staging, logits received,
                                top-k, task list, gate/up done, h staged, down done, combine done) */
+  /* Expert parallel (zero / NULL when the block lives on one GPU).  E stays the router's expert count; the
+     `routed` bank holds this rank's E / ep_world experts (experts ep_rank * E / ep_world ...); router and
+     shared expert are replicated.  ep_inbox[r] is rank r's inbox as seen from THIS rank: its own buffer for
+     r == ep_rank, a peer mapping (zmoe_ep_import) otherwise. */
+  int32_t ep_world, ep_rank;
+  void* ep_inbox[8];
 } zmoe_layer_desc;
 
 /* debug_flags bit: expert 0's router logit is never published, so that every CTA's bounded wait for it runs
    out -- the launch must end by itself with the status word set (failure detection without a GPU fault). */
 #define ZMOE_DEBUG_WITHHOLD_LOGIT 1
+/* debug_flags bit: with ep_world <= 1, still send the token rows and the projected rows through ep_inbox[0]
+   (the expert-parallel data path on one GPU, for tests). */
+#define ZMOE_DEBUG_FORCE_INBOX 2
 
 /*
  * The whole patched block forward for a few decode tokens (src/zmlx/patch/patterns/moe_mlp.py:883-1063:
@@ -298,6 +307,29 @@ typedef struct zmoe_layer_desc {
 size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T);
 int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, void* workspace,
                       size_t workspace_bytes, float* weights, uint32_t* indices, void* out, void* stream);
+
+/*
+ * Expert parallel form of zmoe_layer_decode (no reference counterpart: the reference runs on one device and
+ * only disables its MoE pattern under tensor parallelism, src/zmlx/exo.py:141-151; the exchange sits where its
+ * dispatch and combine kernels are, moe.py:776-827 and :831-1127).  Every rank calls zmoe_layer_decode with
+ * its own T tokens, the same launch count on every rank.  In ONE launch per rank: the rank stores its token
+ * rows into every rank's inbox (plain peer stores of tagged words), routes all T * ep_world tokens, runs the
+ * (token, slot) rows whose expert it holds, and the down projection stores each projected row straight into
+ * the inbox of the token's home rank, which combines its own tokens' rows in slot order after a bounded wait
+ * -- bit-identical to the one-GPU order.  No collective call, nothing to synchronise on the host.  T * ep_world
+ * must not exceed 8.  Each rank owns an inbox of zmoe_layer_decode_inbox_bytes(L, T) bytes, zeroed before its
+ * first use, in memory the peers can map (zmoe_ep_alloc / zmoe_ep_export / zmoe_ep_import below, or any other
+ * peer-accessible allocation).
+ */
+size_t zmoe_layer_decode_inbox_bytes(const zmoe_layer_desc* L, int T);
+
+/* Peer-mappable device memory for the inboxes: allocate (zeroed), export a 64-byte handle, map a peer's
+   handle, and undo both.  These are set-up calls: they allocate and synchronise. */
+int zmoe_ep_alloc(size_t bytes, void** ptr);
+int zmoe_ep_free(void* ptr);
+int zmoe_ep_export(const void* ptr, void* handle64);
+int zmoe_ep_import(const void* handle64, void** ptr);
+int zmoe_ep_unmap(void* ptr);
 
 /*
  * Status of the launches that have used `workspace`: copies the status word to the host on `stream` and WAITS

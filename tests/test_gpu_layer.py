@@ -130,3 +130,18 @@ def test_router_logits_match_a_float64_matmul():
     ref = (x.double() @ params["router_w"].double().T).cpu().numpy()
     got = t2n(layer.router_logits(16))
     assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
+
+
+@pytest.mark.parametrize("name,T", [("c2", 1), ("c2", 4), ("c1", 8), ("c5", 1)])
+def test_inbox_data_path_gives_the_same_bits(name, T):
+    """The expert-parallel data path on one GPU: token rows pushed into and read from the inbox as tagged words,
+    projected rows delivered through it, both launch parities -- same arithmetic, so the same bits."""
+    cfg, params = _layer(name)
+    plain = MoELayer(cfg, params, max_tokens=8)
+    boxed = MoELayer(cfg, params, max_tokens=8, debug_force_inbox=True)
+    for step in range(4):
+        x = synthetic.make_tokens(cfg, T, step=step, device="cpu").to(DEV)
+        a, b = plain(x).clone(), boxed(x).clone()
+        assert torch.equal(a, b), f"step {step}"
+        assert torch.equal(plain.indices[:T], boxed.indices[:T]) and torch.equal(plain.weights[:T], boxed.weights[:T])
+    boxed.check_status()

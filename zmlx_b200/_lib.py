@@ -17,6 +17,7 @@ LIB_PATH = os.environ.get("ZMOE_LIB") or os.path.join(_HERE, "libzmoe.so")
 OK = 0
 ABI_VERSION = 2
 DEBUG_WITHHOLD_LOGIT = 1
+DEBUG_FORCE_INBOX = 2
 ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 Q_AFFINE4, Q_MXFP4 = 0, 1
@@ -51,7 +52,8 @@ class LayerDesc(ctypes.Structure):
                 + [(n, ctypes.c_int32) for n in ("n_shared", "swiglu_mode", "shared_swiglu_mode", "combine_mode",
                                                  "out_flags", "launch_mode")]
                 + [("router_w", c_void_p), ("router_bias", c_void_p), ("routed", ExpertBank), ("shared", ExpertBank)]
-                + [("debug_flags", ctypes.c_int32), ("reserved", ctypes.c_int32), ("debug_stamps", c_void_p)])
+                + [("debug_flags", ctypes.c_int32), ("reserved", ctypes.c_int32), ("debug_stamps", c_void_p)]
+                + [("ep_world", ctypes.c_int32), ("ep_rank", ctypes.c_int32), ("ep_inbox", c_void_p * 8)])
 
 
 # name -> (restype, argtypes); must list every symbol include/zmoe.h declares.
@@ -85,6 +87,12 @@ SIGNATURES = {
     "zmoe_layer_decode": (c_int, [ctypes.POINTER(LayerDesc), c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p,
                                   c_void_p, c_void_p, c_void_p]),
     "zmoe_layer_decode_status": (c_int, [c_void_p, c_int, c_void_p]),
+    "zmoe_layer_decode_inbox_bytes": (c_size_t, [ctypes.POINTER(LayerDesc), c_int]),
+    "zmoe_ep_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p)]),
+    "zmoe_ep_free": (c_int, [c_void_p]),
+    "zmoe_ep_export": (c_int, [c_void_p, c_void_p]),
+    "zmoe_ep_import": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "zmoe_ep_unmap": (c_int, [c_void_p]),
 }
 
 

@@ -55,6 +55,44 @@ size_t zmoe_plan_bytes(int rows, int E) {
   return plan_words(rows, E) * sizeof(int);
 }
 
+int zmoe_ep_alloc(size_t bytes, void** ptr) {
+  ZMOE_REQUIRE(ptr != nullptr && bytes > 0, ZMOE_ERR_SHAPE, "zmoe_ep_alloc: bad arguments");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_ep_alloc: %s", cudaGetErrorString(e));
+  return ZMOE_OK;
+}
+
+int zmoe_ep_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_ep_free: %s", cudaGetErrorString(e));
+  return ZMOE_OK;
+}
+
+int zmoe_ep_export(const void* ptr, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
+  ZMOE_REQUIRE(ptr != nullptr && handle64 != nullptr, ZMOE_ERR_SHAPE, "zmoe_ep_export: null pointer");
+  cudaError_t e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64), const_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_ep_export: %s", cudaGetErrorString(e));
+  return ZMOE_OK;
+}
+
+int zmoe_ep_import(const void* handle64, void** ptr) {
+  ZMOE_REQUIRE(ptr != nullptr && handle64 != nullptr, ZMOE_ERR_SHAPE, "zmoe_ep_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_ep_import: %s", cudaGetErrorString(e));
+  return ZMOE_OK;
+}
+
+int zmoe_ep_unmap(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_ep_unmap: %s", cudaGetErrorString(e));
+  return ZMOE_OK;
+}
+
 int zmoe_build_plan(const int32_t* lhs, int lhs_div, const int32_t* rhs, int P, int M, int E, void* plan,
                     size_t plan_bytes, void* stream) {
   ZMOE_REQUIRE(rhs != nullptr && plan != nullptr, ZMOE_ERR_SHAPE, "zmoe_build_plan: null pointer");

@@ -63,6 +63,7 @@ static_assert(kLdSegBytes == 256 || kLdSegBytes == 512, "stage geometry");
 constexpr int kLdMaxDepth = 8;                       // stages per team at most
 constexpr int kLdSmemLimit = 227 * 1024;
 constexpr int kLdMaxMine = 4;                        // router rows per CTA at most (E <= 4 * grid)
+constexpr int kLdMaxRanks = 8;                       // GPUs of an expert-parallel group at most
 
 struct LdBank {
   const uint32_t* w[2];
@@ -86,6 +87,12 @@ struct LdParams {
   int pdl;       // regular launch with programmatic dependent launch instead of a cooperative one
   int hrows;     // h rows a CTA stages at most for its share of the down projection
   int slots;     // ring stages of a CTA (dealt to the four teams)
+  // expert parallel: this GPU holds experts e_lo .. e_lo + e_cnt - 1 (the banks' rows 0 ..), brings T of the
+  // T * ep_world tokens and has an inbox in which every rank deposits token rows and projected rows
+  int ep_world, ep_rank, e_lo, e_cnt;
+  int use_inbox;             // token rows are read from the inbox (ep_world > 1, or the single-GPU test of that path)
+  uint32_t* inbox[kLdMaxRanks];  // every rank's inbox: [2 launch parities][T * ep_world rows][d] token words, then
+                                 // [2][T * K + T rows][d] projected-row words; NULL when there is none
   int* sync;         // {-, -, sign-in count, status, launch count}
   uint32_t* logits;  // (T, E) hand-over words, each repeated eight times (one 32-byte sector per logit)
   uint32_t* h;       // (rows, f) hand-over words
@@ -288,12 +295,12 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
       const int blk = i - t * K8;
       uint4 v;
       if (TAGGED) {
-        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)rowlist[t] * ld + blk * 8;
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(src) + (size_t)(rowlist ? rowlist[t] : t) * ld + blk * 8;
         uint4 a, b;
         int spins = 0;
         for (;;) {
-          a = ld_relaxed_v4(w32);
-          b = ld_relaxed_v4(w32 + 4);
+          a = ld_relaxed_sys_v4(w32);
+          b = ld_relaxed_sys_v4(w32 + 4);
           const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
                                 (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
           if (bad == 0u) break;
@@ -613,7 +620,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int wid = tid >> 5;
-  const int T = p.T, K = p.K, E = p.E, d = p.d, f = p.f;
+  // To tokens are this rank's own; T = To * ranks are routed here (expert parallel: every rank routes every token
+  // and computes the (token, slot) rows whose expert it holds); tok0 is the first own token
+  const int To = p.T, T = p.T * p.ep_world, tok0 = p.ep_rank * p.T;
+  const int K = p.K, E = p.E, d = p.d, f = p.f;
   const int R = T * K;
   const int nblocks = gridDim.x;
   const LdSmem lay = ld_smem(T, K, E, d, f, p.hrows, p.slots);
@@ -805,6 +815,44 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const uint32_t tag = (uint32_t)((epoch % 65535) + 1) << 16;
 
   LD_STAMP(0);
+  // inbox regions of this launch (they alternate with the launch parity, so that a rank that is one launch ahead
+  // never overwrites words a slower rank still reads)
+  const size_t xwords = (size_t)T * d, ywords = (size_t)(To * K + To) * d;
+  const size_t x_off = (size_t)(epoch & 1) * xwords, y_off = 2 * xwords + (size_t)(epoch & 1) * ywords;
+  const uint32_t* xin = p.use_inbox ? p.inbox[p.ep_rank] + x_off : nullptr;
+  uint32_t* yown = p.use_inbox ? p.inbox[p.ep_rank] + y_off : p.y;  // where this rank's projected rows arrive
+  if (p.use_inbox && (int)blockIdx.x < p.ep_world) {
+    // ---- this rank's token rows go to rank blockIdx.x's inbox as tagged words (plain peer stores)
+    uint32_t* dst = p.inbox[blockIdx.x] + x_off + (size_t)tok0 * d;
+    for (int i = tid; i < To * nvec; i += kLdConsumers) {
+      const int t = i / nvec, v = i - t * nvec;
+      const uint4 xv = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx) + v);
+      uint32_t* o = dst + (size_t)t * d + v * 8;
+      st_relaxed_sys_v4(o, make_uint4(tag | (xv.x & 0xffffu), tag | (xv.x >> 16), tag | (xv.y & 0xffffu), tag | (xv.y >> 16)));
+      st_relaxed_sys_v4(o + 4, make_uint4(tag | (xv.z & 0xffffu), tag | (xv.z >> 16), tag | (xv.w & 0xffffu), tag | (xv.w >> 16)));
+    }
+  }
+  // eight token values from wherever the tokens come from: the caller's rows, or the inbox (re-read until the
+  // words carry this launch's tag; gives zeros and flags the launch when that wait runs out)
+  auto x8 = [&](int t, int v) -> uint4 {
+    if (!p.use_inbox) return __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx) + v);
+    const uint32_t* w32 = xin + (size_t)t * d + v * 8;
+    uint4 a, b;
+    for (int spins = 0;; ++spins) {
+      a = ld_relaxed_sys_v4(w32);
+      b = ld_relaxed_sys_v4(w32 + 4);
+      const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
+                            (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
+      if (bad == 0u) break;
+      if (spins >= kLdSpinLimit || ((spins & 1023) == 1023 && flags[0])) {
+        flags[0] = 1;
+        atomicExch(p.sync + 3, 1);
+        return make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16),
+                      (b.z & 0xffffu) | (b.w << 16));
+  };
   // ---- router linear: the CTA's rows blockIdx.x, blockIdx.x + grid, ...; warp w sums segment w of a row
   {
     int n_mine = 0;
@@ -816,15 +864,14 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
 #pragma unroll 1
         for (int t = 0; t < T; ++t) {
-          const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx);
           float acc = 0.0f;
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
             const int i = wid * 32 + lane + 32 * kRouterSegs * r;
-            if (i < nvec) acc = router_fma8(wpre[k][r], __ldg(xrow + i), acc);
+            if (i < nvec) acc = router_fma8(wpre[k][r], x8(t, i), acc);
           }
           for (int i = wid * 32 + lane + 64 * kRouterSegs; i < nvec; i += 32 * kRouterSegs)
-            acc = router_fma8(__ldg(wrow + i), __ldg(xrow + i), acc);
+            acc = router_fma8(__ldg(wrow + i), x8(t, i), acc);
           acc = warp_sum(acc);
           if (lane == 0) red[(k * T + t) * kRouterSegs + wid] = acc;
         }
@@ -835,8 +882,9 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       const int e = blockIdx.x + nblocks * k;
       const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * d);
       for (int t = 0; t < T; ++t) {
-        const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx);
-        const float acc = warp_sum(router_segment_partial(wrow, xrow, nvec, wid, lane));
+        float acc = 0.0f;
+        for (int i = wid * 32 + lane; i < nvec; i += 32 * kRouterSegs) acc = router_fma8(__ldg(wrow + i), x8(t, i), acc);
+        acc = warp_sum(acc);
         if (lane == 0) red[(k * T + t) * kRouterSegs + wid] = acc;
       }
     }
@@ -869,8 +917,12 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   }
 
   // ---- token rows -> shared memory (fp16, fragment order, group sums), while the logits travel
-  ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
-                       p.sync + 3);
+  if (p.use_inbox)
+    ld_stage_rows<true>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, xin, d, nullptr, T, d >> 3, tag, flags,
+                        p.sync + 3);
+  else
+    ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
+                         p.sync + 3);
   LD_STAMP(2);
   // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
   // so this is also where the CTA waits for the router threads of the other CTAs
@@ -916,22 +968,24 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   }
   ld_csync();
   if (T > 1 && flags[0] == 0) {
-    // tasks = distinct experts in order of first use; a task's rows in row order
+    // tasks = distinct experts THIS rank holds, in order of first use; a task's rows in row order.  Rows whose
+    // expert lives on another rank are that rank's work (rank -1 marks them).
+    const int e_hi = p.e_lo + p.e_cnt;
     if (tid < R) {
       const int e = meta->idx[tid];
       int rk = 0;
       for (int r = 0; r < tid; ++r) rk += (meta->idx[r] == e);
-      meta->rank[tid] = rk;
+      meta->rank[tid] = (e >= p.e_lo && e < e_hi) ? rk : -1;
     }
     ld_csync();
-    if (tid < R) {
+    if (tid < R && meta->rank[tid] >= 0) {
       const int e = meta->idx[tid];
       int r0 = 0;
       while (meta->idx[r0] != e) ++r0;  // first row of this expert (r0 <= tid)
       int tk = 0;
       for (int r = 0; r < r0; ++r) tk += (meta->rank[r] == 0);
       const int rk = meta->rank[tid];
-      if (rk == 0) meta->task_expert[tk] = e;
+      if (rk == 0) meta->task_expert[tk] = e - p.e_lo;  // row of the rank's own banks
       if (rk < kLdMaxT) meta->task_rows[tk][rk] = (unsigned char)tid;
       atomicAdd(&meta->task_cnt[tk], 1);
     }
@@ -940,10 +994,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       for (int r = 0; r < R; ++r) n += (meta->rank[r] == 0);
       meta->n_routed = n;
       meta->n_tasks = n + (p.n_shared ? 1 : 0);
-      if (p.n_shared) {
+      if (p.n_shared) {  // the shared expert runs for the rank's own tokens
         meta->task_expert[n] = 0;
-        meta->task_cnt[n] = T;
-        for (int t = 0; t < T; ++t) meta->task_rows[n][t] = (unsigned char)(R + t);
+        meta->task_cnt[n] = To;
+        for (int t = 0; t < To; ++t) meta->task_rows[n][t] = (unsigned char)(R + t);
       }
     }
     ld_csync();
@@ -976,9 +1030,9 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   c.alive = (flags[0] == 0);
   const int n_tasks = c.alive ? meta->n_tasks : 0;
   const int n_routed = c.alive ? meta->n_routed : 0;
-  if (c.alive && blockIdx.x == 0 && tid < R) {
-    if (p.weights) p.weights[tid] = meta->w[tid];
-    if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tid];
+  if (c.alive && blockIdx.x == 0 && tid < To * K) {  // the routing of the rank's own tokens
+    if (p.weights) p.weights[tid] = meta->w[tok0 * K + tid];
+    if (p.indices) p.indices[tid] = (uint32_t)meta->idx[tok0 * K + tid];
   }
 
   // ---- gate/up + SwiGLU: item i = blockIdx.x + q * grid, the CTA's q-th item goes to team q % 4
@@ -999,7 +1053,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       int trow = 0;
       if (tok_ok) {
         const int r = meta->task_rows[a][tok_g];
-        trow = is_sh ? r - R : r / K;
+        trow = is_sh ? tok0 + r - R : r / K;
       }
       int srow_c[2];
 #pragma unroll
@@ -1008,7 +1062,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
         srow_c[cc] = -1;
         if (sl < cnt) {
           const int r = meta->task_rows[a][sl];
-          srow_c[cc] = is_sh ? r - R : r / K;
+          srow_c[cc] = is_sh ? tok0 + r - R : r / K;
         }
       }
       float acc[2][4];
@@ -1022,7 +1076,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
           const bool writer = (TT == 8) || (col < TT);
           if (writer && col < cnt) {
             const int dst = meta->task_rows[a][col];
-            const float inv = isig[is_sh ? dst - R : dst / K];
+            const float inv = isig[is_sh ? tok0 + dst - R : dst / K];
             const float gv = acc[0][j] * inv, uv = acc[1][j] * inv;
             const float v = (epi == 2) ? swiglu_per_op(gv, uv) : swiglu_cpu_contract(gv, uv);
             st_relaxed_u32(p.h + (size_t)dst * f + n0 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
@@ -1095,8 +1149,16 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
             if (writer && col < cnt) {
               const int dst = meta->task_rows[a][col];
               const float v = acc[m][j] * isig[meta->hloc[dst]];
-              st_relaxed_u32(p.y + (size_t)dst * d + n0 + m * 16 + g + ((j >> 1) ? 8 : 0),
-                             tag | float_to_bf16_bits(v));
+              // the row goes to its token's home rank: routed row of token tg, slot i -> row tl * K + i there
+              // (tl = the token's number on that rank); a shared row stays here, after the routed rows
+              uint32_t* yrow;
+              if (dst >= R) {
+                yrow = yown + (size_t)(To * K + dst - R) * d;
+              } else {
+                const int tg = dst / K, home = tg / To;
+                yrow = (p.ep_world > 1 ? p.inbox[home] + y_off : yown) + (size_t)((tg - home * To) * K + dst - tg * K) * d;
+              }
+              st_relaxed_sys_u32(yrow + n0 + m * 16 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
             }
           }
       }
@@ -1107,7 +1169,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   // ---- ordered combine: 64 output elements per unit, units dealt over the grid; a thread waits for the K
   // (+ shared) projected values of its element (rounded to T, as the separate-kernel path stores them)
   if (flags[0] == 0) {
-    const int units = (T * d) >> 6;
+    const int units = (To * d) >> 6;
     const int mode = p.combine_mode;
     for (int u = (int)blockIdx.x + nblocks * (tid >> 6); u < units; u += nblocks * (kLdConsumers >> 6)) {
       const int o = (u << 6) + (tid & 63);
@@ -1120,8 +1182,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
 #pragma unroll
         for (int i = 0; i < kLdMaxK + 1; ++i) {
           yw[i] = tag;
-          if (i < K) yw[i] = ld_relaxed_u32(p.y + (size_t)(t * K + i) * d + n);
-          if (i == kLdMaxK && p.n_shared) yw[i] = ld_relaxed_u32(p.y + (size_t)(R + t) * d + n);
+          if (i < K) yw[i] = ld_relaxed_sys_u32(yown + (size_t)(t * K + i) * d + n);
+          if (i == kLdMaxK && p.n_shared) yw[i] = ld_relaxed_sys_u32(yown + (size_t)(To * K + t) * d + n);
           okc = okc && ((yw[i] & 0xffff0000u) == tag);
         }
         ++spins;
@@ -1135,7 +1197,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
 #pragma unroll
       for (int i = 0; i < kLdMaxK; ++i) {
         if (i < K) {
-          float wi = meta->w[t * K + i];
+          float wi = meta->w[(tok0 + t) * K + i];
           if (p.out_flags & 2) wi = round_bf16(wi);
           const float v0 = bf16_bits_to_float(yw[i] & 0xffffu);
           if (mode == ZMOE_COMBINE_FP32 || mode == ZMOE_COMBINE_T) {
@@ -1194,17 +1256,24 @@ struct LdPlan {
 
 // Sizes that depend on the grid: the h rows one CTA's share of the down projection can touch, and how many
 // ring stages fit beside everything else.  Returns why the shape cannot take the one-launch path (nullptr: it can).
-static const char* ld_plan(const zmoe_layer_desc* L, int T, int sms, LdPlan* out) {
+static int ld_world(const zmoe_layer_desc* L) { return L->ep_world > 1 ? L->ep_world : 1; }
+
+// T = the rank's own tokens; the kernel routes T * ep_world of them.
+static const char* ld_plan(const zmoe_layer_desc* L, int T_own, int sms, LdPlan* out) {
+  const int world = ld_world(L);
+  if (world > kLdMaxRanks || L->ep_rank < 0 || L->ep_rank >= world) return "takes at most 8 ranks";
+  if (L->E % world != 0) return "needs the expert count to be a multiple of the rank count";
+  const int T = T_own * world;
   if (L->qmode != ZMOE_Q_AFFINE4 || L->group_size != 64) return "needs 4-bit affine weights with group size 64";
-  if (T < 1 || T > kLdMaxT) return "takes 1..8 tokens";
+  if (T_own < 1 || T > kLdMaxT) return "takes 1..8 tokens (over all ranks)";
   if (L->top_k < 1 || L->top_k > kLdMaxK) return "takes top_k <= 8";
   if (L->E < L->top_k || L->E > 256) return "takes at most 256 experts";
   if (L->d_model % 256 != 0 || L->d_ff % 256 != 0) return "needs d_model and d_ff to be multiples of 256";
   if (L->n_shared < 0 || L->n_shared > 1) return "takes at most one shared expert";
   if (sms * kLdMaxMine < L->E) return "needs a GPU with more SMs for this many experts";
-  const int rtot = T * L->top_k + (L->n_shared ? T : 0);
+  const int rtot = T * L->top_k + (L->n_shared ? T_own : 0);
   int routed_max = T * L->top_k;
-  if (routed_max > L->E) routed_max = L->E;
+  if (routed_max > L->E / world) routed_max = L->E / world;
   const long long items = (long long)(routed_max + (L->n_shared ? 1 : 0)) * (L->d_model / 32);
   const int per_cta = (int)((items + sms - 1) / sms);
   const int span = per_cta > 0 ? (per_cta - 1) / (L->d_model / 32) + 2 : 1;  // tasks a contiguous range can touch
@@ -1221,12 +1290,12 @@ static const char* ld_plan(const zmoe_layer_desc* L, int T, int sms, LdPlan* out
 }
 
 static size_t ld_ws_logits_off() { return 256; }
-static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T) {
-  return (ld_ws_logits_off() + (size_t)T * L->E * 32 + 255) & ~(size_t)255;
+static size_t ld_ws_h_off(const zmoe_layer_desc* L, int T_own) {
+  return (ld_ws_logits_off() + (size_t)T_own * ld_world(L) * L->E * 32 + 255) & ~(size_t)255;
 }
-static size_t ld_ws_y_off(const zmoe_layer_desc* L, int T) {
-  const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
-  return (ld_ws_h_off(L, T) + rows * L->d_ff * 4 + 255) & ~(size_t)255;
+static size_t ld_ws_y_off(const zmoe_layer_desc* L, int T_own) {
+  const size_t rows = (size_t)T_own * ld_world(L) * L->top_k + (L->n_shared ? T_own : 0);
+  return (ld_ws_h_off(L, T_own) + rows * L->d_ff * 4 + 255) & ~(size_t)255;
 }
 
 template <int TT>
@@ -1269,8 +1338,16 @@ size_t zmoe_layer_decode_workspace_bytes(const zmoe_layer_desc* L, int T) {
   if (ld_sm_count(&sms) != ZMOE_OK) return 0;
   LdPlan plan;
   if (ld_plan(L, T, sms, &plan)) return 0;
-  const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);
+  const size_t rows = (size_t)T * L->top_k + (L->n_shared ? T : 0);  // the rank's own projected rows
   return ld_ws_y_off(L, T) + rows * L->d_model * 4;
+}
+
+size_t zmoe_layer_decode_inbox_bytes(const zmoe_layer_desc* L, int T) {
+  if (!L || T < 1) return 0;
+  const size_t world = (size_t)ld_world(L);
+  const size_t xwords = (size_t)T * world * L->d_model;
+  const size_t ywords = ((size_t)T * L->top_k + T) * L->d_model;
+  return 2 * (xwords + ywords) * sizeof(uint32_t);
 }
 
 int zmoe_layer_decode_status(const void* workspace, int clear, void* stream) {
@@ -1389,6 +1466,18 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   p.stamps = (long long*)L->debug_stamps;
   p.hrows = plan.hrows;
   p.slots = plan.slots;
+  const int world = ld_world(L);
+  p.ep_world = world;
+  p.ep_rank = world > 1 ? L->ep_rank : 0;
+  p.e_cnt = L->E / world;
+  p.e_lo = p.ep_rank * p.e_cnt;
+  p.use_inbox = (world > 1 || (L->debug_flags & ZMOE_DEBUG_FORCE_INBOX)) ? 1 : 0;
+  for (int r = 0; r < kLdMaxRanks; ++r) p.inbox[r] = (r < world) ? (uint32_t*)L->ep_inbox[r] : nullptr;
+  if (p.use_inbox)
+    for (int r = 0; r < world; ++r)
+      ZMOE_REQUIRE(p.inbox[r] != nullptr && ((uintptr_t)p.inbox[r] % 16) == 0, ZMOE_ERR_SHAPE,
+                   "zmoe_layer_decode: ep_inbox[%d] must be a 16-byte aligned buffer of "
+                   "zmoe_layer_decode_inbox_bytes() bytes (zeroed before its first use)", r);
   unsigned char* ws = (unsigned char*)workspace;
   p.sync = (int*)ws;
   p.logits = (uint32_t*)(ws + ld_ws_logits_off());
@@ -1400,9 +1489,10 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
 
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem_bytes = (size_t)plan.lay.total;
-  if (T == 1) return ld_launch<1>(p, sms, smem_bytes, st);
-  if (T <= 2) return ld_launch<2>(p, sms, smem_bytes, st);
-  if (T <= 4) return ld_launch<4>(p, sms, smem_bytes, st);
+  const int Tt = T * world;  // rows of one task at most
+  if (Tt == 1) return ld_launch<1>(p, sms, smem_bytes, st);
+  if (Tt <= 2) return ld_launch<2>(p, sms, smem_bytes, st);
+  if (Tt <= 4) return ld_launch<4>(p, sms, smem_bytes, st);
   return ld_launch<8>(p, sms, smem_bytes, st);
 }
 

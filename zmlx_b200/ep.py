@@ -1,4 +1,9 @@
-"""Expert-parallel MoE layer across the GPUs of one node (one process per GPU, NCCL).
+"""Expert-parallel MoE layer across the GPUs of one node (one process per GPU).
+
+Two forms.  ``PeerMoELayer`` (decode, T * ranks <= 8 tokens): ONE ``zmoe_layer_decode`` launch per rank and no
+collective -- token rows and projected rows cross NVLink as plain peer stores of tagged words into the home
+rank's inbox, inside the kernel.  ``EPMoELayer`` (any token count): NCCL collectives around the separate kernels,
+described next.
 
 The reference has no distributed code at all (no collectives anywhere in its tree); this is the sharding
 its operator surface allows: experts are independent, so rank r owns experts [r*E/R, (r+1)*E/R) and the router
@@ -194,3 +199,98 @@ class EPMoELayer:
         return self.out[:T]
 
     __call__ = forward
+
+
+# ------------------------------------------------------------------ one launch per rank, peer stores
+def inbox_layout(T: int, world: int, d_model: int, top_k: int) -> dict:
+    """Word offsets inside one rank's inbox (what ``zmoe_layer_decode_inbox_bytes`` sizes): two launch parities of
+    token words (T * world rows of d_model) followed by two parities of projected-row words (T * top_k routed rows
+    and T shared-expert rows of d_model).  Row ``rank * T + t`` of the token part belongs to rank ``rank``."""
+    xwords = T * world * d_model
+    ywords = (T * top_k + T) * d_model
+    return {"x": [0, xwords], "y": [2 * xwords, 2 * xwords + ywords], "words": 2 * (xwords + ywords),
+            "bytes": 8 * (xwords + ywords)}
+
+
+def home_of_row(row: int, T: int, top_k: int) -> tuple[int, int]:
+    """(home rank, row inside the home rank's projected-row part) of routed row ``row`` = token * top_k + slot,
+    tokens numbered rank-major (rank r owns tokens r*T .. r*T+T-1)."""
+    token, slot = divmod(row, top_k)
+    home, local = divmod(token, T)
+    return home, local * top_k + slot
+
+
+def open_inboxes(nbytes: int, rank: int, world: int, group=None) -> tuple[int, list[int], list[int]]:
+    """Allocates this rank's inbox (zeroed, peer-mappable), exchanges handles with the group and maps the peers'.
+    Returns (own pointer, pointers of every rank's inbox as seen from here, the mapped peer pointers to unmap)."""
+    lib = _lib.load()
+    own = ctypes.c_void_p()
+    _lib.check(lib.zmoe_ep_alloc(nbytes, ctypes.byref(own)))
+    handle = ctypes.create_string_buffer(64)
+    _lib.check(lib.zmoe_ep_export(own, handle))
+    handles: list = [None] * world
+    dist.all_gather_object(handles, bytes(handle.raw), group=group)
+    ptrs, mapped = [], []
+    for r in range(world):
+        if r == rank:
+            ptrs.append(own.value)
+            continue
+        peer = ctypes.c_void_p()
+        _lib.check(lib.zmoe_ep_import(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)))
+        ptrs.append(peer.value)
+        mapped.append(peer.value)
+    dist.barrier(group=group)  # every inbox exists, is zero and is mapped everywhere before the first launch
+    return own.value, ptrs, mapped
+
+
+class PeerMoELayer:
+    """Expert-parallel block in one launch per rank.  ``params`` hold this rank's shard of the expert banks
+    (``shard_params``), the replicated router and shared expert.  Every rank must call ``forward`` the same number
+    of times with ``tokens`` rows: the launches of a step find each other through tags derived from the launch
+    count."""
+
+    def __init__(self, cfg: MoEConfig, params: dict, *, rank: int, world: int, tokens: int, group=None,
+                 launch: str = "cooperative"):
+        if tokens * world > MoELayer.FUSED_MAX_TOKENS:
+            raise ValueError(f"{tokens} tokens on {world} ranks exceed the {MoELayer.FUSED_MAX_TOKENS} rows of one launch")
+        self.cfg, self.rank, self.world, self.tokens, self.group = cfg, rank, world, tokens, group
+        self.lo, self.hi = expert_range(cfg.n_experts, world, rank)
+        lay = inbox_layout(tokens, world, cfg.d_model, cfg.top_k)
+        self._own, ptrs, self._mapped = open_inboxes(lay["bytes"], rank, world, group)
+        self.inner = MoELayer(cfg, params, max_tokens=tokens, launch=launch,
+                              ep={"rank": rank, "world": world, "inbox": ptrs})
+        if self.inner.fused_workspace_bytes(tokens) == 0:
+            self.close()
+            raise _lib.ZmoeError(_lib.ERR_UNSUPPORTED, "the one-launch block does not cover this shape")
+
+    @property
+    def indices(self) -> torch.Tensor:
+        return self.inner.indices
+
+    @property
+    def weights(self) -> torch.Tensor:
+        return self.inner.weights
+
+    @property
+    def out(self) -> torch.Tensor:
+        return self.inner.out
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        if x.shape[0] != self.tokens:
+            raise ValueError(f"this layer was set up for {self.tokens} tokens per rank, got {x.shape[0]}")
+        with torch.cuda.device(self.inner.device):
+            return self.inner.forward_fused(x if x.stride(1) == 1 else x.contiguous(), out)
+
+    __call__ = forward
+
+    def check_status(self) -> None:
+        self.inner.check_status()
+
+    def close(self) -> None:
+        lib = _lib.load()
+        for ptr in self._mapped:
+            lib.zmoe_ep_unmap(ctypes.c_void_p(ptr))
+        self._mapped = []
+        if self._own:
+            lib.zmoe_ep_free(ctypes.c_void_p(self._own))
+            self._own = 0

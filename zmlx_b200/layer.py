@@ -24,7 +24,7 @@ class MoELayer:
 
     def __init__(self, cfg: MoEConfig, params: dict, *, max_tokens: int = 64, combine: str | None = None,
                  swiglu: str | None = None, fused: bool = True, launch: str = "cooperative",
-                 debug_withhold_logit: bool = False):
+                 debug_withhold_logit: bool = False, debug_force_inbox: bool = False, ep: dict | None = None):
         self.cfg = cfg
         self.p = params
         dev = params["gate_w"].device
@@ -45,6 +45,12 @@ class MoELayer:
         self.launch = launch
         # test hook of the one-launch block: one router logit is never published, so its bounded waits run out
         self._debug_flags = _lib.DEBUG_WITHHOLD_LOGIT if debug_withhold_logit else 0
+        # expert parallel (zmlx_b200.ep.PeerMoELayer): {"rank", "world", "inbox": [device pointers of every rank's
+        # inbox as seen from here]}; the banks in `params` are then this rank's shard
+        self.ep = ep
+        self._inbox: torch.Tensor | None = None
+        if debug_force_inbox:  # the expert-parallel data path on one GPU (tests)
+            self._debug_flags |= _lib.DEBUG_FORCE_INBOX
         self._stamps: torch.Tensor | None = None
         self._desc = self._describe()
         self._fused_ws: dict[int, torch.Tensor] = {}
@@ -71,6 +77,12 @@ class MoELayer:
         d.launch_mode = 1 if self.launch == "pdl" else 0
         d.debug_flags = self._debug_flags
         d.debug_stamps = self._stamps.data_ptr() if self._stamps is not None else None
+        if self.ep is not None:
+            d.ep_world, d.ep_rank = int(self.ep["world"]), int(self.ep["rank"])
+            for r, ptr in enumerate(self.ep["inbox"]):
+                d.ep_inbox[r] = ptr
+        elif self._inbox is not None:
+            d.ep_inbox[0] = self._inbox.data_ptr()
         d.router_w = W["router_w"].data_ptr()
         d.router_bias = bias.data_ptr() if bias is not None else None
 
@@ -107,6 +119,10 @@ class MoELayer:
                 raise _lib.ZmoeError(_lib.ERR_UNSUPPORTED, f"no one-launch path for this block at T={T}")
             ws = torch.zeros(need, dtype=torch.uint8, device=self.device)  # the sync words start at zero
             self._fused_ws[T] = ws
+            if (self._debug_flags & _lib.DEBUG_FORCE_INBOX) and self._inbox is None:
+                nb = int(_lib.load().zmoe_layer_decode_inbox_bytes(ctypes.byref(self._desc), self.FUSED_MAX_TOKENS))
+                self._inbox = torch.zeros(nb, dtype=torch.uint8, device=self.device)
+                self._desc = self._describe()
         p = ops._ptr
         _lib.check(_lib.load().zmoe_layer_decode(ctypes.byref(self._desc), p(x), x.stride(0), T, p(ws), ws.numel(),
                                                  p(self.weights), p(self.indices), p(dst), ops._stream()))
@@ -122,6 +138,8 @@ class MoELayer:
         ws = self._fused_ws.get(T) if self.fused else None
         if ws is None:
             return self.logits[:T]
+        if self.ep is not None:
+            T = T * int(self.ep["world"])  # the kernel routes every rank's tokens
         E = self.cfg.n_experts
         # the kernel keeps each logit in the low half of a 32-bit hand-over word
         words = ws[256:256 + T * E * 32].view(torch.int32)[::8]  # one 32-byte sector per logit
