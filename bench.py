@@ -65,6 +65,9 @@ def _args():
     ap.add_argument("--no-ep-segments", dest="ep_segments", action="store_false",
                     help="N>1: launch the kernels between the two collectives of a layer eagerly instead of "
                          "replaying them from one CUDA graph per layer")
+    ap.add_argument("--ep-nccl", action="store_true",
+                    help="N>1: NCCL collectives around the separate kernels even where the one-launch peer-store "
+                         "form covers the step")
     ap.add_argument("--check", action="store_true", help="N>1: compare the expert-parallel output with a 1-GPU layer")
     return ap.parse_args()
 
@@ -295,20 +298,66 @@ def main() -> None:
         args.layers = 6 if cfg.config_id == 5 else 24
     T, L = args.tokens, args.layers
     use_ep = world > 1 and not args.replicas
+    ep_peer = False  # expert parallel in one launch per rank (peer stores) instead of collectives around kernels
     if use_ep:
+        from zmlx_b200 import _lib as zlib
         from zmlx_b200 import ep
 
+        ep_peer = (not args.ep_nccl) and T * world <= MoELayer.FUSED_MAX_TOKENS and not args.no_fused
         layers = []
         for i in range(L):
             full = synthetic.make_layer(cfg, layer=i, device=dev)  # same seed on every rank: one model
             lo, hi = ep.expert_range(cfg.n_experts, world, rank)
-            layers.append(ep.EPMoELayer(cfg, ep.shard_params(full, lo, hi), rank=rank, world=world, max_tokens=T,
-                                        sharded=True, segment_graphs=args.ep_segments))
+            shard = ep.shard_params(full, lo, hi)
+            if ep_peer:
+                try:
+                    layers.append(ep.PeerMoELayer(cfg, shard, rank=rank, world=world, tokens=T, launch=args.launch))
+                except zlib.ZmoeError:  # the shape is outside the one-launch block: collectives around the kernels
+                    ep_peer = False
+            if not ep_peer:
+                layers.append(ep.EPMoELayer(cfg, shard, rank=rank, world=world, max_tokens=T, sharded=True,
+                                            segment_graphs=args.ep_segments))
             if args.check and i == 0:
                 ref_layer = MoELayer(cfg, full, max_tokens=T)
             else:
                 del full
         torch.cuda.empty_cache()
+    elif args.via_patch:
+        # the drop-in surface: torch modules with the attribute contract the reference patches, rewritten by patch()
+        from zmlx_b200 import nn as znn
+        from zmlx_b200.patch import patch
+
+        class _Stack(torch.nn.Module):
+            def __init__(self, blocks):
+                super().__init__()
+                self.layers = torch.nn.ModuleList(blocks)
+
+        model = _Stack([znn.block_from_params(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev))
+                        for i in range(L)])
+        patch(model)
+
+        class _Patched:  # the step loop's view of a patched block
+            def __init__(self, blk):
+                self.blk, self.fast = blk, blk._zmlx_fast_layer
+                if self.fast is None:
+                    raise RuntimeError("patch() did not build the fused layer for this block")
+                self.fast.launch = args.launch
+                self.fast._desc = self.fast._describe()
+                self.fused, self.out = True, None
+
+            def forward(self, h):
+                self.out = self.blk(h)
+                return self.out
+
+            indices = property(lambda self: self.fast.indices)
+
+            def fused_workspace_bytes(self, t):
+                return self.fast.fused_workspace_bytes(t)
+
+            def check_status(self):
+                self.fast.check_status()
+
+        layers = [_Patched(b) for b in model.layers]
     else:
         layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T,
                            fused=not args.no_fused, launch=args.launch)
@@ -325,7 +374,8 @@ def main() -> None:
         diff = (got.float() - want.float()).abs().max().item()
         scale = want.float().abs().max().item()
         rec = {"max_abs_diff": diff, "max_abs": scale, "equal_frac": (got == want).float().mean().item(),
-               "indices_equal": bool(torch.equal(layers[0].inner.indices[rank * T:(rank + 1) * T],
+               "indices_equal": bool(torch.equal(layers[0].indices[:T] if ep_peer else
+                                                 layers[0].inner.indices[rank * T:(rank + 1) * T],
                                                  ref_layer.indices[:T]))}
         flags = [None] * world
         dist.all_gather_object(flags, rec)
@@ -346,15 +396,22 @@ def main() -> None:
     if use_ep:
         distinct = []
         for ly in layers:
-            idx = ly.inner.indices[:T * world].reshape(-1)
+            if ep_peer:  # a rank knows the routing of its own tokens: gather the others'
+                parts = [torch.empty_like(ly.indices[:T]) for _ in range(world)]
+                dist.all_gather(parts, ly.indices[:T].contiguous())
+                idx = torch.cat(parts).reshape(-1)
+            else:
+                idx = ly.inner.indices[:T * world].reshape(-1)
             distinct.append(int(torch.unique(idx[(idx >= ly.lo) & (idx < ly.hi)]).numel()))
         # bytes this rank must move: its local experts, the replicated router over all gathered tokens, rows in/out
         alg_bytes_step = sum(dn * cfg.expert_bytes + cfg.n_shared * cfg.expert_bytes + cfg.router_bytes
                              + 4 * T * world * cfg.d_model for dn in distinct)
-        # The collectives run eagerly between the kernels: capturing them in a CUDA graph together with the kernels
-        # stalled twice on this software stack (default and thread-local capture error mode; both calls ran into
-        # their time limit without a GPU fault), so the expert-parallel step is not captured.
-        args.no_graph = True
+        # With collectives between the kernels the step runs eagerly: capturing NCCL calls in a CUDA graph together
+        # with the kernels stalled twice on this software stack (default and thread-local capture error mode; both
+        # calls ran into their time limit without a GPU fault).  The peer-store form has no collective and is
+        # captured like the one-GPU step.
+        if not ep_peer:
+            args.no_graph = True
     else:
         distinct = [int(torch.unique(ly.indices[:T]).numel()) for ly in layers]
         alg_bytes_step = sum(cfg.algorithmic_bytes(dn, T) for dn in distinct)
@@ -389,7 +446,7 @@ def main() -> None:
     # launches per layer: fused router (linear + top-k + plan), gate/up, down, combine (+3 for a shared expert);
     # expert parallel adds the local plan kernel (the NCCL and torch kernels are not counted)
     launches_per_layer = 4 + (3 if cfg.n_shared else 0) + (1 if use_ep else 0)
-    one_launch = (not use_ep) and layers[0].fused and layers[0].fused_workspace_bytes(T) > 0
+    one_launch = ep_peer or ((not use_ep) and layers[0].fused and layers[0].fused_workspace_bytes(T) > 0)
     if one_launch:
         launches_per_layer = 1  # zmoe_layer_decode: the whole block, shared expert included
 
@@ -466,7 +523,11 @@ def main() -> None:
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
                        "block_launch": args.launch if one_launch else None,
-                       "parallelism": (f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
+                       "via_patch": bool(args.via_patch),
+                       "parallelism": (f"ep{world}: experts sharded; one launch per rank and layer, token rows and "
+                                       "projected rows exchanged by peer stores inside the kernel (no collective)"
+                                       if ep_peer else
+                                       f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "
                                        "reduce-scattered (NCCL)"
                                        + ("; kernels between the collectives replayed from per-layer CUDA graphs"
                                           if args.ep_segments else "")) if use_ep else f"replicas x{world}"},
@@ -476,7 +537,7 @@ def main() -> None:
                          "algorithmic_bytes_per_launch": (alg_bytes_step / L) if one_launch else None,
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
-                                  "whole block in one cooperative launch (zmoe_layer_decode)" if one_launch else
+                                  "whole block in one launch (zmoe_layer_decode)" if one_launch else
                                   "whole layer pass (4 kernels)")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2,
                     "d2h_bytes_per_step": T * cfg.d_model * 2},

@@ -25,13 +25,13 @@ def _layer(name):
 # fused: the one-launch path (zmoe_layer_decode) takes the block; otherwise the separate kernels do
 @pytest.mark.parametrize("name,T,fused", [("c1", 1, False), ("c1", 5, False), ("c2", 1, False), ("c2", 4, False),
                                           ("c2", 16, False), ("c2", 64, False), ("c2", 200, False), ("c3", 1, False), ("c3", 3, False),
-                                          ("c3", 16, False), ("c5", 1, False), ("c5", 9, False),
+                                          ("c3", 16, False), ("c5", 1, False), ("c5", 9, False), ("c5", 64, False), ("c5", 512, False),
                                           ("c1", 1, True), ("c1", 2, True), ("c1", 5, True), ("c1", 8, True),
                                           ("c2", 1, True), ("c2", 2, True), ("c2", 3, True), ("c2", 4, True),
                                           ("c2", 7, True), ("c2", 8, True), ("c5", 1, True), ("c5", 2, True)])
 def test_layer_matches_oracle(name, T, fused):
     cfg, params = _layer(name)
-    layer = MoELayer(cfg, params, max_tokens=64, fused=fused)
+    layer = MoELayer(cfg, params, max_tokens=max(64, T), fused=fused)
     assert (layer.fused_workspace_bytes(T) > 0) or not fused
     x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
     out = layer(x).clone()

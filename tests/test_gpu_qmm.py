@@ -108,6 +108,30 @@ def test_token_sorted_grouping_many_rows_per_expert(T):
         assert_close_rel(t2n(out), ref, REL, f"gather_qmm_combine {cmode}")
 
 
+@pytest.mark.parametrize("T,d,f", [(300, 512, 384), (96, 1024, 768), (1024, 256, 256)])
+def test_tensor_memory_path_many_rows_per_expert(T, d, f):
+    """Hundreds of rows per expert take the tcgen05 / tensor-memory kernel (128 weight rows x up to 128 token rows
+    per tile, several token blocks per expert, ragged last block, weight tiles that end beyond N); gate/up +
+    SwiGLU and the down projection against the oracle."""
+    E, K_ = 4, 2
+    gate, up, down = _bank(E, f, d, 21), _bank(E, f, d, 22), _bank(E, d, f, 23)
+    g = torch.Generator().manual_seed(T + d)
+    x = torch.randn((T, d), generator=g).to(torch.bfloat16)
+    idx = torch.randint(0, E, (T, K_), generator=g, dtype=torch.int32)
+    idx[:, 0] = 1  # one expert owns T rows
+    h = fused_moe.gather_qmm_swiglu(x.reshape(T, 1, 1, d).to(DEV), *_to(DEV, *gate), *_to(DEV, *up),
+                                    rhs_indices=idx.to(DEV))
+    lhs = np.repeat(np.arange(T, dtype=np.int32), K_)
+    ref_h = _oracle_swiglu(t2n(x), gate, up, lhs, t2n(idx).reshape(-1))
+    assert_close_rel(t2n(h).reshape(T * K_, f), ref_h, REL, "tensor-memory gate/up + SwiGLU")
+    hk = h.reshape(T, K_, f)
+    gw = torch.rand((T, K_), generator=g)
+    out = moe.gather_qmm_combine_quantized(hk, *_to(DEV, *down), gw.to(DEV), idx.to(DEV).view(torch.uint32),
+                                           output_dtype=torch.float32, no_fma=True)
+    ref = S.gather_qmm_combine_quantized(t2n(hk), *[t2n(t) for t in down], t2n(gw), t2n(idx), combine="fp32_no_fma")
+    assert_close_rel(t2n(out), ref, REL, "tensor-memory down projection + combine")
+
+
 def test_empty_and_single_expert_cases():
     E, d, f = 4, 128, 32
     gate, up = _bank(E, f, d, 10), _bank(E, f, d, 11)

@@ -14,7 +14,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libzmoe.so")
-SOURCES = ["api.cu", "router.cu", "qmm.cu", "qmm_mxfp4.cu", "combine.cu", "layer_decode.cu"]
+SOURCES = ["api.cu", "router.cu", "qmm.cu", "qmm_tc.cu", "qmm_mxfp4.cu", "combine.cu", "layer_decode.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

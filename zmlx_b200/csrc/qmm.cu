@@ -25,6 +25,8 @@
 
 namespace zmoe {
 
+// Many rows per expert: tcgen05 / tensor-memory kernel (qmm_tc.cu).
+int qmm_tc_launch(const QmmParams& q, int nmat, int rows_hint, int max_groups, cudaStream_t st, const char* who);
 // mxfp4 weights (qmm_mxfp4.cu).
 int qmm_mxfp4_launch(QmmParams p, int nmat, int rows_hint, int max_groups, cudaStream_t st, const char* who);
 
@@ -532,6 +534,16 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
     int mg = rows < E ? rows : E;
     if (mg > 65535) mg = 65535;
     return qmm_mxfp4_launch(p, nmat, rows_hint, mg, (cudaStream_t)stream, who);
+  }
+  // From about eight rows per expert on average the contraction is dense enough for the 5th-generation tensor
+  // cores (tcgen05, accumulator in tensor memory): the expert's codes are expanded once per 128-row tile and
+  // reused by up to 128 token rows.
+  if ((long long)rows >= 8ll * E && rows_hint >= 16 && ((uintptr_t)w[0] % 16) == 0 &&
+      (nmat == 1 || ((uintptr_t)w[1] % 16) == 0)) {
+    int mg = rows < E ? rows : E;
+    if (mg > 65535) mg = 65535;
+    p.rs = 0;
+    return qmm_tc_launch(p, nmat, rows_hint, mg, (cudaStream_t)stream, who);
   }
   QmmChoice c = choose_config(p.ngroups, rows_hint);
   // keep the staged token rows within ~96 KB so that several CTAs share an SM
