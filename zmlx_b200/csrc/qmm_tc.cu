@@ -7,13 +7,14 @@
 //
 //   * the packed codes of the CTA's 128 rows arrive by plain 32-byte loads, one group ahead, in registers
 //     (thread = weight row); scales and biases of the group come with them;
-//   * the group is expanded ONCE into a bf16 tile in shared memory, K-major with the 128-byte swizzle that
-//     tcgen05 reads: code pair -> bf16x2 (128 + q) by shift + lop3, minus 136 (exact), then one bf16 FMA
-//     (q - 8) * s + (b + 8 s).  b + 8 s is the middle of the group's range, small, so rounding it to bf16 costs
-//     nothing; the FMA rounds once: the tile holds bf16(q s + b);
-//   * the token rows of the block (gathered through the plan) are copied into a second swizzled tile with
-//     16-byte cp.async, one group ahead;
-//   * one thread issues four tcgen05.mma (M 128 x N tokens x K 16, kind::f16, bf16 x bf16 -> fp32) per matrix
+//   * the group is expanded ONCE into an fp16 tile in shared memory, K-major with the 128-byte swizzle that
+//     tcgen05 reads: code pair -> half2 (1024 + q) by shift + or, minus 1032 (exact), then one fp16 FMA
+//     (q - 8) * s + (b + 8 s).  b + 8 s is the middle of the group's range, small, so rounding it to fp16 costs
+//     nothing; the FMA rounds once: the tile holds fp16(q s + b), 11 significant bits (a bf16 tile, 8 bits,
+//     measurably widens the error of the SwiGLU output);
+//   * the token rows of the block (gathered through the plan) are fetched one group ahead, converted to fp16 and
+//     written into a second swizzled tile;
+//   * one thread issues four tcgen05.mma (M 128 x N tokens x K 16, kind::f16, fp16 x fp16 -> fp32) per matrix
 //     and group, accumulating in tensor memory (gate and up side by side: 2 x N columns), then
 //     tcgen05.commit onto an mbarrier; tiles are double-buffered, so expanding group g+1 overlaps the MMAs of g;
 //   * the epilogue reads the accumulators with tcgen05.ld (thread = weight row, 16 token columns at a time),
@@ -22,6 +23,8 @@
 // Weights are the M side (128 rows fill the tensor-core tile whatever the token count), tokens the N side
 // (16..128 per block).  Every wait on an mbarrier is bounded; a wait that runs out sets the error word, and the
 // CTA frees its tensor memory and returns.
+#include <cuda_fp16.h>
+
 #include "qmm_common.cuh"
 
 namespace zmoe {
@@ -62,9 +65,9 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
          (2ull << 61);
 }
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = n.
+// Instruction descriptor: D fp32, A and B fp16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t tc_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
 }
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
   asm volatile(
@@ -84,16 +87,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-// Eight codes of a packed word -> four bf16x2 (q0 s + b, q1 s + b), ... in K order.
-__device__ __forceinline__ void tc_expand_word(uint32_t w, __nv_bfloat162 s2, __nv_bfloat162 b2, uint32_t (&out)[4]) {
-  const __nv_bfloat162 k136 = __floats2bfloat162_rn(136.0f, 136.0f);
+// Eight codes of a packed word -> four half2 (q0 s + b, q1 s + b), ... in K order.
+__device__ __forceinline__ void tc_expand_word(uint32_t w, __half2 s2, __half2 b2, uint32_t (&out)[4]) {
+  const __half2 k1032 = __floats2half2_rn(1032.0f, 1032.0f);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    // codes 2i (bits 8i..8i+3) and 2i+1 (bits 8i+4..8i+7) -> low / high half of a bf16x2 = (128 + q)
+    // codes 2i (bits 8i..8i+3) and 2i+1 (bits 8i+4..8i+7) -> low / high half of a half2 = (1024 + q)
     const uint32_t lo = (w >> (8 * i)) & 0xFu, hi = (w >> (8 * i + 4)) & 0xFu;
-    const uint32_t pair = 0x43004300u | lo | (hi << 16);
-    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&pair);
-    v = __hfma2(__hsub2(v, k136), s2, b2);  // (q - 8) s + (b + 8 s), one rounding
+    const uint32_t pair = 0x64006400u | lo | (hi << 16);
+    __half2 v = *reinterpret_cast<const __half2*>(&pair);
+    v = __hfma2(__hsub2(v, k1032), s2, b2);  // (q - 8) s + (b + 8 s), one rounding
     out[i] = *reinterpret_cast<const uint32_t*>(&v);
   }
 }
@@ -165,23 +168,47 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
         sv[m] = srow[m][0];
         bv[m] = brow[m][0];
       }
-      // token tile of group g: token t's 128 bytes at row t of the tile, 16-byte piece c at position c ^ (t % 8)
-      auto copy_tokens = [&](int g, int buf) {
-        unsigned char* bt = b_tiles + buf * kTcBTile;
-        for (int i = tid; i < NB * 8; i += kTcThreads) {
+      // Token tile of group g: token t's 64 values at row t of the tile, 16-byte piece c at position c ^ (t % 8),
+      // as fp16 (tcgen05 wants both operands of one 16-bit type; fp16 keeps every bit of a bfloat16 inside
+      // +-65504, beyond which the value is clamped -- normalised activations are orders of magnitude below).
+      // The pieces are fetched into registers one group ahead and converted when the tile is free.
+      constexpr int kXr = kTcMaxTok * 8 / kTcThreads;  // pieces per thread at most
+      uint4 xr[kXr];
+      auto load_tokens = [&](int g) {
+#pragma unroll
+        for (int u = 0; u < kXr; ++u) {
+          const int i = tid + u * kTcThreads;
           const int t = i >> 3, c = i & 7;
-          const uint32_t dst = tc_smem_u32(bt + (t >> 3) * 1024 + (t & 7) * 128 + ((c ^ (t & 7)) << 4));
-          if (t < nt) {
+          xr[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (i < NB * 8 && t < nt) {
             const int src = p.x_by_dst ? pv.row_dst[off + t0 + t] : pv.row_src[off + t0 + t];
-            const void* g_src = p.x + (size_t)src * p.ldx + g * 64 + c * 8;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(g_src) : "memory");
-          } else {
-            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u) : "memory");
+            xr[u] = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx + g * 64) + c);
           }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
       };
-      copy_tokens(0, 0);
+      auto store_tokens = [&](int buf) {
+        unsigned char* bt = b_tiles + buf * kTcBTile;
+#pragma unroll
+        for (int u = 0; u < kXr; ++u) {
+          const int i = tid + u * kTcThreads;
+          const int t = i >> 3, c = i & 7;
+          if (i < NB * 8) {
+            const uint32_t q[4] = {xr[u].x, xr[u].y, xr[u].z, xr[u].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float lo = fminf(fmaxf(bf16_bits_to_float(q[k] & 0xffffu), -65504.0f), 65504.0f);
+              const float hi = fminf(fmaxf(bf16_bits_to_float(q[k] >> 16), -65504.0f), 65504.0f);
+              const __half2 h = __floats2half2_rn(lo, hi);
+              o[k] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(bt + (t >> 3) * 1024 + (t & 7) * 128 + ((c ^ (t & 7)) << 4)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      };
+      load_tokens(0);
+      store_tokens(0);
 
       bool ok = true;
       for (int g = 0; g < ngroups; ++g) {
@@ -189,13 +216,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
         // the MMAs that read this buffer two groups ago must be done before it is overwritten
         if (uses[buf] > 0 && g >= 2 && ok) ok = tc_mbar_wait(bars + buf * 8, (uses[buf] - 1) & 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (g + 1 < ngroups) load_tokens(g + 1);  // lands while the weights are expanded
         // ---- expand this thread's row of the group into the weight tile(s)
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
           unsigned char* at = a_tiles + (buf * NMAT + m) * kTcATile + (tid >> 3) * 1024 + (tid & 7) * 128;
           const float sf = __bfloat162float(sv[m]), bf = __bfloat162float(bv[m]);
-          const __nv_bfloat162 s2 = __bfloat162bfloat162(sv[m]);
-          const __nv_bfloat162 b2 = __float2bfloat162_rn(fmaf(8.0f, sf, bf));
+          const __half2 s2 = __float2half2_rn(sf);  // a bfloat16 scale is exact in fp16 (inside its normal range)
+          const __half2 b2 = __float2half2_rn(fmaf(8.0f, sf, bf));
           const uint32_t words[8] = {wq[m][0].x, wq[m][0].y, wq[m][0].z, wq[m][0].w,
                                      wq[m][1].x, wq[m][1].y, wq[m][1].z, wq[m][1].w};
 #pragma unroll
@@ -215,16 +243,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
             bv[m] = brow[m][g + 1];
           }
         }
-        // the token tile of this group has landed (its copies were issued one group ago)
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        if (g + 1 < ngroups) {
-          // the other token buffer is free once the MMAs of group g-1 are done
-          if (uses[buf ^ 1] > 0 && g >= 1 && ok) ok = tc_mbar_wait(bars + (buf ^ 1) * 8, (uses[buf ^ 1] - 1) & 1);
-          copy_tokens(g + 1, buf ^ 1);
-        }
         if (tid == 0 && ok) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t bdesc = tc_desc(tc_smem_u32(b_tiles + buf * kTcBTile));
@@ -236,6 +257,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
               tc_mma(tmem_base + m * kTcMaxTok, adesc + 2 * k, bdesc + 2 * k, idesc, (g > 0) || (k > 0));
           }
           tc_commit(bars + buf * 8);
+        }
+        if (g + 1 < ngroups) {
+          // the other token buffer is free once the MMAs of group g-1 are done
+          if (uses[buf ^ 1] > 0 && g >= 1 && ok) ok = tc_mbar_wait(bars + (buf ^ 1) * 8, (uses[buf ^ 1] - 1) & 1);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          store_tokens(buf ^ 1);
         }
         ++uses[buf];
       }
