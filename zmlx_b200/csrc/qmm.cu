@@ -538,7 +538,7 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
   // From about eight rows per expert on average the contraction is dense enough for the 5th-generation tensor
   // cores (tcgen05, accumulator in tensor memory): the expert's codes are expanded once per 128-row tile and
   // reused by up to 128 token rows.
-  if ((long long)rows >= 8ll * E && rows_hint >= 16 && (p.ngroups & 3) == 0 && ((uintptr_t)w[0] % 16) == 0 &&
+  if ((long long)rows >= 8ll * E && rows_hint >= 16 && (p.ngroups & 3) == 0 && E <= 1024 && ((uintptr_t)w[0] % 16) == 0 &&
       (nmat == 1 || ((uintptr_t)w[1] % 16) == 0)) {
     int mg = rows < E ? rows : E;
     if (mg > 65535) mg = 65535;
