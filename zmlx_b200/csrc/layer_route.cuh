@@ -114,6 +114,29 @@ __device__ __forceinline__ float router_logit_warp(const uint4* wrow, const uint
   return total;
 }
 
+// The logits of one weight row against TB token rows at once: the same arithmetic per token as
+// router_logit_warp (segment partials, then one warp sum per segment, added in segment order), with the TB
+// independent chains interleaved so that their loads and shuffles overlap.
+template <int TB>
+__device__ __forceinline__ void router_logit_warp_multi(const uint4* wrow, const uint4* const (&xrow)[TB], int nvec,
+                                                        int lane, float (&total)[TB]) {
+#pragma unroll
+  for (int t = 0; t < TB; ++t) total[t] = 0.0f;
+  const int nseg = min(kRouterSegs, (nvec + 31) >> 5);
+  for (int s = 0; s < nseg; ++s) {
+    float acc[TB];
+#pragma unroll
+    for (int t = 0; t < TB; ++t) acc[t] = 0.0f;
+    for (int i = s * 32 + lane; i < nvec; i += 32 * kRouterSegs) {
+      const uint4 wv = __ldg(wrow + i);
+#pragma unroll
+      for (int t = 0; t < TB; ++t) acc[t] = router_fma8(wv, __ldg(xrow[t] + i), acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < TB; ++t) total[t] += warp_sum(acc[t]);
+  }
+}
+
 // ------------------------------------------------------------------ routing of the T token rows
 // Same arithmetic as the per-row router functions (softmax_topk_row / sigmoid_topk_row: the order of every
 // floating-point sum is kept, so scores, indices and weights are bit-identical).  A single warp is slow at

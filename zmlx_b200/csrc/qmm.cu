@@ -545,7 +545,13 @@ int qmm_launch(int nmat, const void* x, int x_rows, int ldx, const uint32_t* con
     p.rs = 0;
     return qmm_tc_launch(p, nmat, rows_hint, mg, (cudaStream_t)stream, who);
   }
-  QmmChoice c = choose_config(p.ngroups, rows_hint);
+  // The token slots of a pass are sized for twice the average task, not for the largest possible one: with
+  // top-k routing most experts see far fewer rows than there are tokens, and a task with more rows takes
+  // another pass over its (L2-resident) weights.
+  long long typical = (2ll * rows + E - 1) / E;
+  if (typical > rows_hint) typical = rows_hint;
+  if (typical < 1) typical = 1;
+  QmmChoice c = choose_config(p.ngroups, (int)typical);
   // keep the staged token rows within ~96 KB so that several CTAs share an SM
   int rs = (c.nt == 1) ? c.tt : 8 * c.nt;
   while (rs > 1 && (size_t)rs * qmm_xs_stride(K) > 96 * 1024) rs = rs / 2;

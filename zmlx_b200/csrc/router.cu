@@ -58,15 +58,21 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const __nv_bfloat16*
   const int t0 = blockIdx.y * 8;
   const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * d);
   const int nvec = d >> 3;
-  for (int t = t0; t < min(T, t0 + 8); ++t) {
-    const float s = router_logit_warp(wrow, reinterpret_cast<const uint4*>(x + (size_t)t * d), nvec, lane);
-    if (lane == 0) {
-      const size_t o = (size_t)t * E + e;
-      if (out_dtype == ZMOE_F32)
-        reinterpret_cast<float*>(logits)[o] = s;
-      else
-        reinterpret_cast<__nv_bfloat16*>(logits)[o] = __float2bfloat16_rn(s);
-    }
+  const uint4* xrow[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) xrow[j] = reinterpret_cast<const uint4*>(x + (size_t)min(t0 + j, T - 1) * d);
+  float s[8];
+  router_logit_warp_multi<8>(wrow, xrow, nvec, lane, s);
+  if (lane < 8 && t0 + lane < T) {
+    float mine = s[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+      if (lane == j) mine = s[j];
+    const size_t o = (size_t)(t0 + lane) * E + e;
+    if (out_dtype == ZMOE_F32)
+      reinterpret_cast<float*>(logits)[o] = mine;
+    else
+      reinterpret_cast<__nv_bfloat16*>(logits)[o] = __float2bfloat16_rn(mine);
   }
 }
 
