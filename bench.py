@@ -303,18 +303,27 @@ def main() -> None:
         from zmlx_b200 import _lib as zlib
         from zmlx_b200 import ep
 
-        ep_peer = (not args.ep_nccl) and T * world <= MoELayer.FUSED_MAX_TOKENS and not args.no_fused
+        # Expert-parallel degree: all ranks when the one-launch block takes T rows of every rank (its shared
+        # memory holds all of them); otherwise the largest divisor of the rank count that fits, with the groups
+        # running side by side as data-parallel replicas (every group holds all experts).
+        ep_deg, ep_group = world, None
         layers = []
+        if not args.ep_nccl and not args.no_fused:
+            for g in [g for g in (world, world // 2, world // 4) if g >= 2 and world % g == 0]:
+                if ep.peer_block_supported(cfg, T, g):
+                    # every rank takes part in creating every group
+                    groups = [dist.new_group(list(range(b, b + g))) for b in range(0, world, g)] if g < world else [None]
+                    ep_peer, ep_deg, ep_group = True, g, groups[rank // g]
+                    break
+        ep_rank = rank % ep_deg
         for i in range(L):
             full = synthetic.make_layer(cfg, layer=i, device=dev)  # same seed on every rank: one model
-            lo, hi = ep.expert_range(cfg.n_experts, world, rank)
+            lo, hi = ep.expert_range(cfg.n_experts, ep_deg, ep_rank)
             shard = ep.shard_params(full, lo, hi)
             if ep_peer:
-                try:
-                    layers.append(ep.PeerMoELayer(cfg, shard, rank=rank, world=world, tokens=T, launch=args.launch))
-                except zlib.ZmoeError:  # the shape is outside the one-launch block: collectives around the kernels
-                    ep_peer = False
-            if not ep_peer:
+                layers.append(ep.PeerMoELayer(cfg, shard, rank=ep_rank, world=ep_deg, tokens=T, group=ep_group,
+                                              launch=args.launch))
+            else:
                 layers.append(ep.EPMoELayer(cfg, shard, rank=rank, world=world, max_tokens=T, sharded=True,
                                             segment_graphs=args.ep_segments))
             if args.check and i == 0:
@@ -396,16 +405,16 @@ def main() -> None:
     if use_ep:
         distinct = []
         for ly in layers:
-            if ep_peer:  # a rank knows the routing of its own tokens: gather the others'
-                parts = [torch.empty_like(ly.indices[:T]) for _ in range(world)]
-                dist.all_gather(parts, ly.indices[:T].contiguous())
+            if ep_peer:  # a rank knows the routing of its own tokens: gather the others' (of its group)
+                parts = [torch.empty_like(ly.indices[:T]) for _ in range(ep_deg)]
+                dist.all_gather(parts, ly.indices[:T].contiguous(), group=ep_group)
                 idx = torch.cat(parts).reshape(-1)
             else:
                 idx = ly.inner.indices[:T * world].reshape(-1)
             distinct.append(int(torch.unique(idx[(idx >= ly.lo) & (idx < ly.hi)]).numel()))
         # bytes this rank must move: its local experts, the replicated router over all gathered tokens, rows in/out
         alg_bytes_step = sum(dn * cfg.expert_bytes + cfg.n_shared * cfg.expert_bytes + cfg.router_bytes
-                             + 4 * T * world * cfg.d_model for dn in distinct)
+                             + 4 * T * ep_deg * cfg.d_model for dn in distinct)
         # With collectives between the kernels the step runs eagerly: capturing NCCL calls in a CUDA graph together
         # with the kernels stalled twice on this software stack (default and thread-local capture error mode; both
         # calls ran into their time limit without a GPU fault).  The peer-store form has no collective and is
@@ -524,7 +533,8 @@ def main() -> None:
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
                        "block_launch": args.launch if one_launch else None,
                        "via_patch": bool(args.via_patch),
-                       "parallelism": (f"ep{world}: experts sharded; one launch per rank and layer, token rows and "
+                       "parallelism": (f"ep{ep_deg}" + (f" x dp{world // ep_deg}" if ep_deg < world else "")
+                                       + ": experts sharded; one launch per rank and layer, token rows and "
                                        "projected rows exchanged by peer stores inside the kernel (no collective)"
                                        if ep_peer else
                                        f"ep{world}: experts sharded, tokens all-gathered, per-slot rows "

@@ -28,7 +28,8 @@ def _layer(name):
                                           ("c3", 16, False), ("c5", 1, False), ("c5", 9, False), ("c5", 64, False), ("c5", 512, False),
                                           ("c1", 1, True), ("c1", 2, True), ("c1", 5, True), ("c1", 8, True),
                                           ("c2", 1, True), ("c2", 2, True), ("c2", 3, True), ("c2", 4, True),
-                                          ("c2", 7, True), ("c2", 8, True), ("c5", 1, True), ("c5", 2, True)])
+                                          ("c2", 7, True), ("c2", 8, True), ("c5", 1, True), ("c5", 2, True),
+                                          ("c5", 4, True), ("c5", 8, True)])
 def test_layer_matches_oracle(name, T, fused):
     cfg, params = _layer(name)
     layer = MoELayer(cfg, params, max_tokens=max(64, T), fused=fused)
@@ -47,7 +48,7 @@ def test_layer_matches_oracle(name, T, fused):
 
 
 @pytest.mark.parametrize("name,T", [("c1", 1), ("c1", 6), ("c2", 1), ("c2", 2), ("c2", 4), ("c2", 8), ("c5", 1),
-                                    ("c5", 2)])
+                                    ("c5", 2), ("c5", 8)])
 def test_one_launch_block_agrees_with_the_separate_kernels(name, T):
     """Same routing bit for bit; outputs differ by the summation order of the K split only."""
     cfg, params = _layer(name)
@@ -116,10 +117,10 @@ def test_one_launch_block_rejects_what_it_does_not_cover():
     cfg2, params2 = _layer("c2")
     layer2 = MoELayer(cfg2, params2, max_tokens=16)
     assert layer2.fused_workspace_bytes(9) == 0 and layer2.fused_workspace_bytes(8) > 0
-    cfg5, params5 = _layer("c5")  # four tokens of h rows no longer fit in shared memory
-    layer5 = MoELayer(cfg5, params5, max_tokens=8)
-    assert layer5.fused_workspace_bytes(4) == 0 and layer5.fused_workspace_bytes(2) > 0
-    assert torch.isfinite(layer5(synthetic.make_tokens(cfg5, 4, device="cpu").to(DEV)).float()).all()
+    cfg5, params5 = _layer("c5")  # the widest shape: eight token rows leave one stage per team
+    layer5 = MoELayer(cfg5, params5, max_tokens=16)
+    assert layer5.fused_workspace_bytes(8) > 0 and layer5.fused_workspace_bytes(9) == 0
+    assert torch.isfinite(layer5(synthetic.make_tokens(cfg5, 9, device="cpu").to(DEV)).float()).all()
 
 
 def test_router_logits_match_a_float64_matmul():

@@ -137,8 +137,6 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   a += ld_align16(nr * 4);
   m.rowmax = a;
   a += ld_align16(nr * 4);
-  m.route = a;  // per row: sort keys, scores, logits, group scratch, winners
-  a += ld_align16(T * (4 * E + 64 + kLdMaxK) * 4);
   m.rbias = a;  // the router's selection bias (a constant: copied in before the dependency wait)
   a += ld_align16(E * 4);
   m.meta = a;
@@ -155,6 +153,10 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   m.ring = a;
   a += slots * kLdSlotBytes;
   m.total = a;
+  // Routing scratch (per row: sort keys, scores, logits, group scratch, winners) lives in the stages of teams
+  // 1..3: before the routing is known only team 0's producer copies anything (the shared expert's first tiles),
+  // and the scratch is dead once the task list is published.
+  m.route = m.ring + (slots / kLdTeams + (slots % kLdTeams ? 1 : 0)) * kLdSlotBytes;
   return m;
 }
 
@@ -1282,7 +1284,10 @@ static const char* ld_plan(const zmoe_layer_desc* L, int T_own, int sms, LdPlan*
   const LdSmem fixed = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, hrows, 0);
   int slots = (kLdSmemLimit - fixed.total) / kLdSlotBytes;
   if (slots > kLdTeams * kLdMaxDepth) slots = kLdTeams * kLdMaxDepth;
-  if (slots < 2 * kLdTeams) return "needs more shared memory than an SM has";
+  if (slots < kLdTeams) return "needs more shared memory than an SM has";
+  const int route_bytes = ld_align16(T * (4 * L->E + 64 + kLdMaxK) * 4);
+  if ((slots - (slots / kLdTeams + (slots % kLdTeams ? 1 : 0))) * kLdSlotBytes < route_bytes)
+    return "needs more shared memory than an SM has";
   out->hrows = hrows;
   out->slots = slots;
   out->lay = ld_smem(T, L->top_k, L->E, L->d_model, L->d_ff, hrows, slots);

@@ -243,6 +243,20 @@ def open_inboxes(nbytes: int, rank: int, world: int, group=None) -> tuple[int, l
     return own.value, ptrs, mapped
 
 
+def peer_block_supported(cfg: MoEConfig, tokens: int, world: int) -> bool:
+    """Whether the one-launch block takes ``tokens`` rows from each of ``world`` ranks for this shape (its shared
+    memory holds the rows of all ranks).  Reads shapes only: no allocation, no exchange."""
+    if tokens * world > MoELayer.FUSED_MAX_TOKENS or cfg.n_experts % world != 0:
+        return False
+    d = _lib.LayerDesc()
+    d.E, d.d_model, d.d_ff, d.top_k = cfg.n_experts, cfg.d_model, cfg.d_ff, cfg.top_k
+    d.group_size = 32 if cfg.mode == "mxfp4" else cfg.group_size
+    d.qmode = _lib.Q_MXFP4 if cfg.mode == "mxfp4" else _lib.Q_AFFINE4
+    d.n_shared = int(cfg.n_shared)
+    d.ep_world, d.ep_rank = int(world), 0
+    return int(_lib.load().zmoe_layer_decode_workspace_bytes(ctypes.byref(d), int(tokens))) > 0
+
+
 class PeerMoELayer:
     """Expert-parallel block in one launch per rank.  ``params`` hold this rank's shard of the expert banks
     (``shard_params``), the replicated router and shared expert.  Every rank must call ``forward`` the same number
@@ -287,10 +301,13 @@ class PeerMoELayer:
         self.inner.check_status()
 
     def close(self) -> None:
+        """Collective over the layer's group: no rank frees its inbox while a peer still has it mapped."""
         lib = _lib.load()
         for ptr in self._mapped:
             lib.zmoe_ep_unmap(ctypes.c_void_p(ptr))
         self._mapped = []
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
         if self._own:
             lib.zmoe_ep_free(ctypes.c_void_p(self._own))
             self._own = 0
