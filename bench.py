@@ -65,6 +65,8 @@ def _args():
     ap.add_argument("--no-ep-segments", dest="ep_segments", action="store_false",
                     help="N>1: launch the kernels between the two collectives of a layer eagerly instead of "
                          "replaying them from one CUDA graph per layer")
+    ap.add_argument("--ep-degree", type=int, default=0,
+                    help="N>1: ranks per expert-parallel group (the groups run side by side); 0 = choose")
     ap.add_argument("--ep-nccl", action="store_true",
                     help="N>1: NCCL collectives around the separate kernels even where the one-launch peer-store "
                          "form covers the step")
@@ -303,13 +305,15 @@ def main() -> None:
         from zmlx_b200 import _lib as zlib
         from zmlx_b200 import ep
 
-        # Expert-parallel degree: all ranks when the one-launch block takes T rows of every rank (its shared
-        # memory holds all of them); otherwise the largest divisor of the rank count that fits, with the groups
-        # running side by side as data-parallel replicas (every group holds all experts).
+        # Expert-parallel degree: groups of --ep-degree ranks share one set of experts and the groups run side by
+        # side as data-parallel replicas.  The default is pairs: a launch then carries 2 T token rows and keeps
+        # most of its shared memory for weight stages (measured on 8 GPUs, c5 T=1: ep2 x dp4 80.6k, ep4 x dp2
+        # 65.3k, ep8 56.7k layer-tokens/s); wider groups are for models whose experts do not fit in two GPUs.
         ep_deg, ep_group = world, None
         layers = []
         if not args.ep_nccl and not args.no_fused:
-            for g in [g for g in (world, world // 2, world // 4) if g >= 2 and world % g == 0]:
+            cands = [args.ep_degree] if args.ep_degree else [2, 4, 8]
+            for g in [g for g in cands if g >= 2 and world % g == 0]:
                 if ep.peer_block_supported(cfg, T, g):
                     # every rank takes part in creating every group
                     groups = [dist.new_group(list(range(b, b + g))) for b in range(0, world, g)] if g < world else [None]
