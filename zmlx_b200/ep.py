@@ -220,6 +220,28 @@ def home_of_row(row: int, T: int, top_k: int) -> tuple[int, int]:
     return home, local * top_k + slot
 
 
+def launch_tag(launch_count: int) -> int:
+    """Upper half of every hand-over word of launch number ``launch_count`` (counted from 0): never zero, so a
+    zeroed inbox holds no valid word, and different from the tag two launches earlier, whose words lie in the same
+    parity half of the inbox."""
+    return ((launch_count % 65535) + 1) << 16
+
+
+def pack_words(rows: torch.Tensor, launch_count: int) -> torch.Tensor:
+    """bfloat16 rows -> the 32-bit hand-over words the kernel stores into an inbox: {tag : 16 | bfloat16 bits : 16}.
+    A word is complete or absent (one 32-bit store), which is what lets the reader poll it without a lock."""
+    bits = rows.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+    return (bits | launch_tag(launch_count)).to(torch.int64)
+
+
+def unpack_words(words: torch.Tensor, launch_count: int) -> tuple[bool, torch.Tensor]:
+    """(all words carry this launch's tag, their bfloat16 payload).  The reader repeats this until it holds, a
+    bounded number of times: the kernel gives up after about a second and sets ``ZMOE_ERR_TIMEOUT``."""
+    w = words.to(torch.int64)
+    ok = bool(((w & 0xFFFF0000) == launch_tag(launch_count)).all())
+    return ok, (w & 0xFFFF).to(torch.int16).view(torch.bfloat16) if ok else None
+
+
 def open_inboxes(nbytes: int, rank: int, world: int, group=None) -> tuple[int, list[int], list[int]]:
     """Allocates this rank's inbox (zeroed, peer-mappable), exchanges handles with the group and maps the peers'.
     Returns (own pointer, pointers of every rank's inbox as seen from here, the mapped peer pointers to unmap)."""
