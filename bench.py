@@ -55,6 +55,9 @@ def _args():
     ap.add_argument("--via-patch", action="store_true",
                     help="drive the blocks as nn modules patched by zmlx_b200.patch.patch() instead of MoELayer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--stamps", action="store_true",
+                    help="one GPU, one-launch block: CTA 0 of the middle layer records its cycle counter at the phase "
+                         "boundaries; the phase table is printed to stderr after the timed run")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--launch", default="pdl", choices=["pdl", "cooperative"],
                     help="how the one-launch block is launched: 'pdl' = regular launch set up while the previous "
@@ -375,6 +378,9 @@ def main() -> None:
         layers = [MoELayer(cfg, synthetic.make_layer(cfg, layer=100 * rank + i, device=dev), max_tokens=T,
                            fused=not args.no_fused, launch=args.launch)
                   for i in range(L)]
+    stamps = None
+    if args.stamps and not use_ep and not args.via_patch:
+        stamps = layers[L // 2].enable_stamps()
     x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
     x_dev = x_host.to(dev)
     out_host = torch.empty((T, cfg.d_model), dtype=torch.bfloat16).pin_memory()
@@ -519,6 +525,15 @@ def main() -> None:
         for ly in layers:
             getattr(ly, "check_status", lambda: None)()
 
+    if stamps is not None and rank == 0:
+        v = stamps.cpu().tolist()
+        names = ["push/router linear", "stage x", "logits arrive + scores", "select top-k", "weights + task list",
+                 "gate/up + SwiGLU", "stage h", "down", "combine"]
+        print(json.dumps({"stamps": "SM cycles of CTA 0, middle layer, last launch",
+                          "total_cycles": v[9] - v[0],
+                          "phases": {n: v[i + 1] - v[i] for i, n in enumerate(names)},
+                          "ns_from_kernel_entry_to_dependency_wait_passed": v[11] - v[10],
+                          "ns_kernel_entry_to_exit": v[12] - v[10]}), file=sys.stderr)
     if rank == 0:
         peak, peak_kind = _peaks()
         traffic, traffic_source = _measured_traffic(cfg, T, one_launch, alg_bytes_step / L)

@@ -279,7 +279,9 @@ __device__ __forceinline__ uint4 ld_lds128(uint32_t addr) {
 // by the row's power of two, converts and permutes in place.  Eight-element block k of a row (the codes of one
 // packed word) becomes [x0, x4, x1/16, x5/16, x2, x6, x3/16, x7/16].  All consumer threads must call this;
 // returns false when a wait ran out (every thread of the CTA sees flags[0] set after the last barrier).
-template <bool TAGGED>
+// SYS: the words may have been written by another GPU (system-scope loads); words written on this GPU are read
+// with device-scope loads, which are measurably cheaper.
+template <bool TAGGED, bool SYS = false>
 __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float2* xsum, int rs, float* isig,
                                               int* rowmax, const void* src, int ld, const unsigned char* rowlist,
                                               int nrows, int K8, uint32_t tag, volatile int* flags, int* status) {
@@ -301,8 +303,8 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
         uint4 a, b;
         int spins = 0;
         for (;;) {
-          a = ld_relaxed_sys_v4(w32);
-          b = ld_relaxed_sys_v4(w32 + 4);
+          a = SYS ? ld_relaxed_sys_v4(w32) : ld_relaxed_v4(w32);
+          b = SYS ? ld_relaxed_sys_v4(w32 + 4) : ld_relaxed_v4(w32 + 4);
           const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
                                 (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
           if (bad == 0u) break;
@@ -616,7 +618,9 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int TT>
+// EP: the token rows come from, and the projected rows go to, the ranks' inboxes (expert parallel, or the one-GPU
+// test of that data path).  The plain instance carries none of that code: the kernel is sensitive to its size.
+template <int TT, bool EP>
 __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x;
@@ -624,7 +628,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   const int wid = tid >> 5;
   // To tokens are this rank's own; T = To * ranks are routed here (expert parallel: every rank routes every token
   // and computes the (token, slot) rows whose expert it holds); tok0 is the first own token
-  const int To = p.T, T = p.T * p.ep_world, tok0 = p.ep_rank * p.T;
+  const int To = p.T, T = EP ? p.T * p.ep_world : p.T, tok0 = EP ? p.ep_rank * p.T : 0;
   const int K = p.K, E = p.E, d = p.d, f = p.f;
   const int R = T * K;
   const int nblocks = gridDim.x;
@@ -821,9 +825,9 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   // never overwrites words a slower rank still reads)
   const size_t xwords = (size_t)T * d, ywords = (size_t)(To * K + To) * d;
   const size_t x_off = (size_t)(epoch & 1) * xwords, y_off = 2 * xwords + (size_t)(epoch & 1) * ywords;
-  const uint32_t* xin = p.use_inbox ? p.inbox[p.ep_rank] + x_off : nullptr;
-  uint32_t* yown = p.use_inbox ? p.inbox[p.ep_rank] + y_off : p.y;  // where this rank's projected rows arrive
-  if (p.use_inbox && (int)blockIdx.x < p.ep_world) {
+  const uint32_t* xin = EP ? p.inbox[p.ep_rank] + x_off : nullptr;
+  uint32_t* yown = EP ? p.inbox[p.ep_rank] + y_off : p.y;  // where this rank's projected rows arrive
+  if (EP && (int)blockIdx.x < p.ep_world) {
     // ---- this rank's token rows go to rank blockIdx.x's inbox as tagged words (plain peer stores)
     uint32_t* dst = p.inbox[blockIdx.x] + x_off + (size_t)tok0 * d;
     for (int i = tid; i < To * nvec; i += kLdConsumers) {
@@ -837,7 +841,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   // eight token values from wherever the tokens come from: the caller's rows, or the inbox (re-read until the
   // words carry this launch's tag; gives zeros and flags the launch when that wait runs out)
   auto x8 = [&](int t, int v) -> uint4 {
-    if (!p.use_inbox) return __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx) + v);
+    if (!EP) return __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx) + v);
     const uint32_t* w32 = xin + (size_t)t * d + v * 8;
     uint4 a, b;
     for (int spins = 0;; ++spins) {
@@ -919,8 +923,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   }
 
   // ---- token rows -> shared memory (fp16, fragment order, group sums), while the logits travel
-  if (p.use_inbox)
-    ld_stage_rows<true>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, xin, d, nullptr, T, d >> 3, tag, flags,
+  if (EP)
+    ld_stage_rows<true, true>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, xin, d, nullptr, T, d >> 3, tag, flags,
                         p.sync + 3);
   else
     ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
@@ -1154,13 +1158,18 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
               // the row goes to its token's home rank: routed row of token tg, slot i -> row tl * K + i there
               // (tl = the token's number on that rank); a shared row stays here, after the routed rows
               uint32_t* yrow;
-              if (dst >= R) {
-                yrow = yown + (size_t)(To * K + dst - R) * d;
+              if (!EP || dst >= R) {
+                yrow = yown + (size_t)dst * d;  // (a shared row: To * K + dst - R, and R = To * K without peers)
+                if (EP && dst >= R) yrow = yown + (size_t)(To * K + dst - R) * d;
               } else {
                 const int tg = dst / K, home = tg / To;
                 yrow = (p.ep_world > 1 ? p.inbox[home] + y_off : yown) + (size_t)((tg - home * To) * K + dst - tg * K) * d;
               }
-              st_relaxed_sys_u32(yrow + n0 + m * 16 + g + ((j >> 1) ? 8 : 0), tag | float_to_bf16_bits(v));
+              uint32_t* yw = yrow + n0 + m * 16 + g + ((j >> 1) ? 8 : 0);
+              if (EP)
+                st_relaxed_sys_u32(yw, tag | float_to_bf16_bits(v));
+              else
+                st_relaxed_u32(yw, tag | float_to_bf16_bits(v));
             }
           }
       }
@@ -1173,6 +1182,7 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   if (flags[0] == 0) {
     const int units = (To * d) >> 6;
     const int mode = p.combine_mode;
+    const bool sys_words = EP;  // peers store into this rank's inbox: system-scope polls
     for (int u = (int)blockIdx.x + nblocks * (tid >> 6); u < units; u += nblocks * (kLdConsumers >> 6)) {
       const int o = (u << 6) + (tid & 63);
       const int t = o / d, n = o - t * d;
@@ -1184,8 +1194,10 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
 #pragma unroll
         for (int i = 0; i < kLdMaxK + 1; ++i) {
           yw[i] = tag;
-          if (i < K) yw[i] = ld_relaxed_sys_u32(yown + (size_t)(t * K + i) * d + n);
-          if (i == kLdMaxK && p.n_shared) yw[i] = ld_relaxed_sys_u32(yown + (size_t)(To * K + t) * d + n);
+          const uint32_t* src = nullptr;
+          if (i < K) src = yown + (size_t)(t * K + i) * d + n;
+          if (i == kLdMaxK && p.n_shared) src = yown + (size_t)(To * K + t) * d + n;
+          if (src != nullptr) yw[i] = sys_words ? ld_relaxed_sys_u32(src) : ld_relaxed_u32(src);
           okc = okc && ((yw[i] & 0xffff0000u) == tag);
         }
         ++spins;
@@ -1303,9 +1315,9 @@ static size_t ld_ws_y_off(const zmoe_layer_desc* L, int T_own) {
   return (ld_ws_h_off(L, T_own) + rows * L->d_ff * 4 + 255) & ~(size_t)255;
 }
 
-template <int TT>
+template <int TT, bool EP>
 static int ld_launch(const LdParams& p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = layer_decode_kernel<TT>;
+  auto kern = layer_decode_kernel<TT, EP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess)
     return fail(ZMOE_ERR_CUDA, "zmoe_layer_decode: shared memory of %zu bytes refused: %s", smem_bytes,
@@ -1495,10 +1507,16 @@ int zmoe_layer_decode(const zmoe_layer_desc* L, const void* x, int ldx, int T, v
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem_bytes = (size_t)plan.lay.total;
   const int Tt = T * world;  // rows of one task at most
-  if (Tt == 1) return ld_launch<1>(p, sms, smem_bytes, st);
-  if (Tt <= 2) return ld_launch<2>(p, sms, smem_bytes, st);
-  if (Tt <= 4) return ld_launch<4>(p, sms, smem_bytes, st);
-  return ld_launch<8>(p, sms, smem_bytes, st);
+  if (p.use_inbox) {
+    if (Tt == 1) return ld_launch<1, true>(p, sms, smem_bytes, st);
+    if (Tt <= 2) return ld_launch<2, true>(p, sms, smem_bytes, st);
+    if (Tt <= 4) return ld_launch<4, true>(p, sms, smem_bytes, st);
+    return ld_launch<8, true>(p, sms, smem_bytes, st);
+  }
+  if (Tt == 1) return ld_launch<1, false>(p, sms, smem_bytes, st);
+  if (Tt <= 2) return ld_launch<2, false>(p, sms, smem_bytes, st);
+  if (Tt <= 4) return ld_launch<4, false>(p, sms, smem_bytes, st);
+  return ld_launch<8, false>(p, sms, smem_bytes, st);
 }
 
 }  // extern "C"
