@@ -79,7 +79,12 @@ def _args():
 
 # DRAM bytes per launch of the one-launch block measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum),
 # as a ratio to the algorithmic bytes of the captured launches; the summaries that hold the figures are named.
-_TRAFFIC_RATIO = {}
+_TRAFFIC_RATIO = {
+    (5, 1): (1.020, "profiles/layer_decode_kernel_c5_T1.md: 223.62 MB read + 4.38 MB written per launch over "
+                    "223.44 MB algorithmic, 32-expert bank; scaled by the algorithmic bytes of this launch"),
+    (2, 1): (1.008, "profiles/layer_decode_kernel_c2_T1.md: 21.54 MB read per launch over 21.37 MB algorithmic, "
+                    "32-expert bank; scaled by the algorithmic bytes of this launch"),
+}
 
 
 def _measured_traffic(cfg, T, one_launch, alg_bytes_per_launch):
