@@ -198,7 +198,8 @@ int zmoe_swiglu(const void* gate, const void* up, long long n, int swiglu_mode, 
  * gather_qmm_combine_quantized: out[t] = sum_k gate[t,k] * T(act[t,k] @ W[idx[t,k]].T).
  * Replaces moe.py:2043-2174 (and the K-vectorised form moe.py:1198-1236).
  * act (T*K, Kin) T; plan built over rhs = idx (T*K pairs, lhs = identity);
- * scratch must hold T*K*N T values.
+ * scratch must hold T*K*N T values; the call clears it first, so a pair whose expert id lies
+ * outside 0..E-1 (dropped by the plan) contributes zero.
  */
 int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w, const void* scales, const void* biases,
                             int E, int N, int Kin, int group_size, int qmode, const void* plan, int T, int K,

@@ -201,6 +201,12 @@ int zmoe_gather_qmm_combine(const void* act, int ldx, const uint32_t* w_, const 
   const uint32_t* w[2] = {w_, nullptr};
   const void* s[2] = {scales, nullptr};
   const void* b[2] = {biases, nullptr};
+  // Pairs whose expert id the plan dropped (outside 0..E-1) get no projected row: they count as zero, as in the
+  // allocation-free entry point, instead of whatever the caller's scratch held.
+  if (T > 0) {
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)T * K * N * sizeof(__nv_bfloat16), (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(ZMOE_ERR_CUDA, "zmoe_gather_qmm_combine: clearing the scratch: %s", cudaGetErrorString(e));
+  }
   int rc = qmm_launch(1, act, T * K, ldx, w, s, b, E, N, Kin, group_size, qmode, plan, T * K, T, scratch, 0, 1, stream,
                       "zmoe_gather_qmm_combine");
   if (rc != ZMOE_OK) return rc;
