@@ -473,6 +473,9 @@ def main() -> None:
     one_launch = ep_peer or ((not use_ep) and layers[0].fused and layers[0].fused_workspace_bytes(T) > 0)
     if one_launch:
         launches_per_layer = 1  # zmoe_layer_decode: the whole block, shared expert included
+    elif (not use_ep) and layers[0].fused and getattr(layers[0], "_chunked_ok", lambda t: False)(T):
+        one_launch = True  # consecutive one-launch passes over eight rows each
+        launches_per_layer = len(layers[0]._chunks(T))
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
@@ -555,6 +558,7 @@ def main() -> None:
                        "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
+                       "launches_per_layer": launches_per_layer,
                        "block_launch": args.launch if one_launch else None,
                        "via_patch": bool(args.via_patch),
                        "parallelism": (f"ep{ep_deg}" + (f" x dp{world // ep_deg}" if ep_deg < world else "")
@@ -568,7 +572,7 @@ def main() -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
                          "peak_kind": f"of {peak_kind}",
-                         "algorithmic_bytes_per_launch": (alg_bytes_step / L) if one_launch else None,
+                         "algorithmic_bytes_per_launch": (alg_bytes_step / L / launches_per_layer) if one_launch else None,
                          "algorithmic_bytes_per_step": alg_bytes_step,
                          "note": ("rank 0's bytes over the step time (per-GPU fraction)" if use_ep else
                                   "whole block in one launch (zmoe_layer_decode)" if one_launch else

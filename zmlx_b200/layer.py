@@ -104,11 +104,30 @@ class MoELayer:
             return 0
         return int(_lib.load().zmoe_layer_decode_workspace_bytes(ctypes.byref(self._desc), T))
 
-    def forward_fused(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """The whole block in one launch (``zmoe_layer_decode``); raises if the shape is outside it."""
+    def _chunks(self, T: int) -> list[tuple[int, int]]:
+        """(first row, rows) of the one-launch passes that cover T rows."""
+        M = self.FUSED_MAX_TOKENS
+        return [(r, min(M, T - r)) for r in range(0, T, M)]
+
+    def _chunked_ok(self, T: int) -> bool:
+        """More rows than one launch takes, but still fewer than two per expert on average: the block runs as
+        consecutive one-launch passes over eight rows each.  Every pass streams only its own rows' experts, and
+        measured against the separate kernels it wins up to about that density (c2 T=16: 79 vs 121 us, c5 T=64:
+        2.3 vs 3.5 ms per layer); beyond it the experts are shared by enough rows for the grouped matmuls."""
+        cfg = self.cfg
+        if self.ep is not None or T <= self.FUSED_MAX_TOKENS or T * cfg.top_k > 2 * cfg.n_experts:
+            return False
+        return all(self.fused_workspace_bytes(n) > 0 for n in {n for _, n in self._chunks(T)})
+
+    def forward_fused(self, x: torch.Tensor, out: torch.Tensor | None = None, *, row0: int = 0,
+                      key=None) -> torch.Tensor:
+        """The whole block in one launch (``zmoe_layer_decode``); raises if the shape is outside it.  ``row0``:
+        first row of ``out``, ``weights`` and ``indices`` this pass writes; ``key``: which workspace it uses (one per
+        pass of a chunked call, so that every pass keeps its logits and status)."""
         T = x.shape[0]
         dst = self.out if out is None else out
-        ws = self._fused_ws.get(T)
+        key = T if key is None else key
+        ws = self._fused_ws.get(key)
         if ws is None:
             if torch.cuda.is_current_stream_capturing():
                 # a workspace zeroed inside the graph would be zeroed again at every replay, and with it the launch
@@ -118,15 +137,16 @@ class MoELayer:
             if need == 0:
                 raise _lib.ZmoeError(_lib.ERR_UNSUPPORTED, f"no one-launch path for this block at T={T}")
             ws = torch.zeros(need, dtype=torch.uint8, device=self.device)  # the sync words start at zero
-            self._fused_ws[T] = ws
+            self._fused_ws[key] = ws
             if (self._debug_flags & _lib.DEBUG_FORCE_INBOX) and self._inbox is None:
                 nb = int(_lib.load().zmoe_layer_decode_inbox_bytes(ctypes.byref(self._desc), self.FUSED_MAX_TOKENS))
                 self._inbox = torch.zeros(nb, dtype=torch.uint8, device=self.device)
                 self._desc = self._describe()
         p = ops._ptr
         _lib.check(_lib.load().zmoe_layer_decode(ctypes.byref(self._desc), p(x), x.stride(0), T, p(ws), ws.numel(),
-                                                 p(self.weights), p(self.indices), p(dst), ops._stream()))
-        return dst[:T]
+                                                 p(self.weights[row0:]), p(self.indices[row0:]), p(dst[row0:]),
+                                                 ops._stream()))
+        return dst[row0:row0 + T]
 
     def launch_count(self, T: int) -> int:
         """How many one-launch passes the T-token workspace has seen (the kernel's own launch counter)."""
@@ -135,6 +155,12 @@ class MoELayer:
 
     def router_logits(self, T: int) -> torch.Tensor:
         """The (T, E) bf16 router logits of the last forward pass over T tokens (whichever path ran it)."""
+        if self.fused and self._fused_ok.get(T) == "chunks":
+            parts = []
+            for ci, (_, n) in enumerate(self._chunks(T)):
+                words = self._fused_ws[(T, ci)][256:256 + n * self.cfg.n_experts * 32].view(torch.int32)[::8]
+                parts.append((words & 0xFFFF).to(torch.int16).view(torch.bfloat16).view(n, self.cfg.n_experts))
+            return torch.cat(parts)
         ws = self._fused_ws.get(T) if self.fused else None
         if ws is None:
             return self.logits[:T]
@@ -147,6 +173,9 @@ class MoELayer:
 
     def fused_status(self, T: int) -> int:
         """The status word of the T-token workspace: non-zero after a bounded wait of the one-launch block ran out."""
+        if self._fused_ok.get(T) == "chunks":
+            return max(int(self._fused_ws[(T, ci)][:16].view(torch.int32)[3].item())
+                       for ci in range(len(self._chunks(T))))
         ws = self._fused_ws.get(T)
         return 0 if ws is None else int(ws[:16].view(torch.int32)[3].item())
 
@@ -292,7 +321,13 @@ class MoELayer:
             if self.fused:
                 ok = self._fused_ok.get(T)
                 if ok is None:
-                    ok = self._fused_ok[T] = self.fused_workspace_bytes(T) > 0
+                    ok = self.fused_workspace_bytes(T) > 0 or ("chunks" if self._chunked_ok(T) else False)
+                    self._fused_ok[T] = ok
+                if ok == "chunks":
+                    dst = self.out if out is None else out
+                    for ci, (r, n) in enumerate(self._chunks(T)):
+                        self.forward_fused(x[r:r + n], dst, row0=r, key=(T, ci))
+                    return dst[:T]
                 if ok:
                     return self.forward_fused(x, out)
             residual = None
