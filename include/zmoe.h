@@ -53,8 +53,11 @@ enum zmoe_qmode {
 /* Rounding contract of the SwiGLU epilogue. */
 enum zmoe_swiglu_mode {
   ZMOE_SWIGLU_CPU = 0,   /* gate, up rounded to T; g*1/(1+exp(-g))*u in float; one rounding (patch:47-55) */
-  ZMOE_SWIGLU_PER_OP = 1 /* every elementwise op rounded to T, sigmoid as 1/(1+exp|g|) (src/zmlx/msl.py:20-24,
-                            src/zmlx/kernels/transformer.py:882-897) */
+  ZMOE_SWIGLU_PER_OP = 1, /* every elementwise op rounded to T, sigmoid as 1/(1+exp|g|) (src/zmlx/msl.py:20-24,
+                             src/zmlx/kernels/transformer.py:882-897) */
+  ZMOE_SWIGLU_FP32 = 2    /* gate and up stay in float through g*sigmoid(g)*u, sigmoid as 1/(1+exp|g|); one
+                             rounding at the store (the dense fused GEMV, src/zmlx/kernels/quant.py:103-124).
+                             zmoe_gather_qmm_swiglu with affine weights only. */
 };
 
 /* Rounding contract of the weighted combine (slots summed in order 0..K-1). */

@@ -211,6 +211,25 @@ def gather_qmm_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_b
     raise ValueError(swiglu)
 
 
+def fused_quantized_swiglu_gemv(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, *,
+                                group_size: int = 64) -> np.ndarray:
+    """Dense fused GEMV + SwiGLU: out[m, n] = T(silu(x_m . deq(Wg[n])) * (x_m . deq(Wu[n]))).
+
+    src/zmlx/kernels/quant.py:103-124 (called from the dense MLP pattern, src/zmlx/patch/patterns/swiglu_mlp.py:
+    281-317): both dot products are accumulated in float and stay in float through `acc_gate *
+    kk_sigmoid(acc_gate) * acc_up` (sigmoid in the |x| form, src/zmlx/msl.py:20-24); one rounding at the store.
+    x (M, K); weights (N, K/8) uint32; scales, biases (N, K/group_size).
+    """
+    wg = dequant_affine(np.asarray(gate_w)[None], np.asarray(gate_scales)[None], np.asarray(gate_biases)[None],
+                        group_size)[0]
+    wu = dequant_affine(np.asarray(up_w)[None], np.asarray(up_scales)[None], np.asarray(up_biases)[None],
+                        group_size)[0]
+    xf = np.asarray(x, dtype=np.float32)
+    g = (xf.astype(np.float64) @ wg.astype(np.float64).T).astype(np.float32)
+    u = (xf.astype(np.float64) @ wu.astype(np.float64).T).astype(np.float32)
+    return bf16((g * sigmoid_stable(g)) * u)
+
+
 # ---------------------------------------------------------------------------
 # Routers
 # ---------------------------------------------------------------------------

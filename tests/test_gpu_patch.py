@@ -30,7 +30,9 @@ def test_patched_block_matches_oracle_and_unpatched(base, family):
     x = synthetic.make_tokens(cfg, 6, device="cpu").reshape(2, 3, cfg.d_model).to(DEV)
     y_ref_torch = blk(x)
     patch(m)
-    assert m._zmlx_patch_result.patched_count == 1
+    # the block itself, and -- as in the reference's default selection -- its dense shared expert (swiglu_mlp)
+    want = {"moe_mlp": 1, "swiglu_mlp": 1} if cfg.n_shared else {"moe_mlp": 1}
+    assert m._zmlx_patch_result.pattern_counts == want
     y = blk(x)
     assert y.shape == x.shape and y.dtype == torch.bfloat16
     pn = params_to_numpy(p)
@@ -94,3 +96,33 @@ def test_deepseek_router_pattern_fires_on_a_256_expert_gate():
     # the unpatched gate picks the same experts (as sets: torch.topk orders ties differently)
     assert np.array_equal(np.sort(t2n(idx_ref).reshape(15, 8), -1), np.sort(t2n(idx).reshape(15, 8), -1))
     unpatch(m)
+
+
+@pytest.mark.parametrize("T", [1, 5, 64])
+def test_dense_swiglu_mlp_pattern_matches_the_fused_gemv_restatement(T):
+    """The `swiglu_mlp` pattern on a dense quantised MLP (a one-expert bank): gate/up + SwiGLU in one kernel with
+    gate and up kept in float (the contract of src/zmlx/kernels/quant.py:103-124), then the quantised down
+    projection; T = 64 takes the tensor-memory matmul."""
+    cfg = synthetic.CONFIGS["c3"].scaled(mode="affine", group_size=64)  # d 2048, f 1536, one shared expert
+    p = synthetic.make_layer(cfg, device=DEV)["shared"]
+    mlp = znn.mlp_from_params(p).to(DEV)
+
+    class _M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = mlp
+
+    m = _M()
+    patch(m, patterns=["swiglu_mlp"])
+    assert m._zmlx_patch_result.pattern_counts == {"swiglu_mlp": 1}
+    x = synthetic.make_tokens(cfg, T, device="cpu").to(DEV)
+    got = m.mlp(x.reshape(1, T, -1)).reshape(T, -1)
+    pn = params_to_numpy(p)
+    h = S.fused_quantized_swiglu_gemv(t2n(x), pn["gate_w"][0], pn["gate_s"][0], pn["gate_b"][0], pn["up_w"][0],
+                                      pn["up_s"][0], pn["up_b"][0])
+    ref = S.gather_qmm(h[:, None, :], pn["down_w"], pn["down_s"], pn["down_b"],
+                       rhs_indices=np.zeros(T, dtype=np.uint32))[:, 0, :]
+    assert_close_rel(t2n(got), ref, 2e-2, f"dense MLP T={T}")
+    unpatch(m)
+    assert type(m.mlp) is znn.MLP
+    assert_close_rel(t2n(m.mlp(x)), ref, 3e-2, f"stock dense MLP T={T}")  # torch ops round op by op in bfloat16

@@ -25,7 +25,7 @@ class _Model(torch.nn.Module):
 
 
 def test_registry_and_types():
-    assert list_patterns() == ["deepseek_router", "moe_mlp"]
+    assert list_patterns() == ["deepseek_router", "moe_mlp", "swiglu_mlp"]
     assert get_pattern("moe_mlp").name == "moe_mlp"
     with pytest.raises(KeyError):
         get_pattern("nope")
@@ -149,3 +149,26 @@ def test_can_fuse_rules():
     sw.activation = torch.nn.GELU()
     assert not mm._can_fuse_switch_mlp(sw)
     assert not mm._MoEMLPPattern().matches(torch.nn.Linear(2, 2), "x")
+
+
+def test_swiglu_mlp_pattern_matches_dense_mlps_only():
+    """src/zmlx/patch/patterns/swiglu_mlp.py:222-236: gate/up/down layout; not the switch bank, not a child of a
+    MoE block unless it is `shared_experts`.  On CPU tensors the patched call is the module's own."""
+    pat = get_pattern("swiglu_mlp")
+    cfg, p = _tiny("glm", n_shared=1)
+    blk = znn.block_from_params(cfg, p)
+    dense = znn.mlp_from_params(p["shared"])
+    assert pat.matches(dense, "mlp", None)
+    assert not pat.matches(blk.switch_mlp, "switch_mlp", blk)
+    assert pat.matches(blk.shared_experts, "shared_experts", blk)
+    assert not pat.matches(dense, "mlp", blk)  # some other child of a block with a gate
+    assert not pat.matches(torch.nn.Linear(4, 4), "proj", None)
+
+    m = _Model([dense])
+    x = torch.randn(2, 3, 128).bfloat16()
+    y0 = dense(x)
+    patch(m, patterns=["swiglu_mlp"])
+    assert m._zmlx_patch_result.pattern_counts == {"swiglu_mlp": 1}
+    assert type(dense) is not znn.MLP and torch.equal(dense(x), y0)
+    unpatch(m)
+    assert type(dense) is znn.MLP

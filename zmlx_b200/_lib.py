@@ -21,7 +21,7 @@ DEBUG_FORCE_INBOX = 2
 ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 Q_AFFINE4, Q_MXFP4 = 0, 1
-SWIGLU_CPU, SWIGLU_PER_OP = 0, 1
+SWIGLU_CPU, SWIGLU_PER_OP, SWIGLU_FP32 = 0, 1, 2
 COMBINE_FP32, COMBINE_FP32_NO_FMA, COMBINE_T, COMBINE_NO_FMA, COMBINE_EXACT, COMBINE_STREAM_T = range(6)
 ROUTER_TOPK_THEN_SOFTMAX, ROUTER_SOFTMAX_THEN_TOPK = 0, 1
 

@@ -405,8 +405,7 @@ __global__ void __launch_bounds__(32 * WK * WM, (NT == 1) ? 512 / (32 * WK * WM)
             if (writer && t < nrow && n < N) {
               float v;
               if (NMAT == 2) {
-                v = (p.epilogue == 2) ? swiglu_per_op(acc[0][nt][j], acc[NMAT - 1][nt][j])
-                                      : swiglu_cpu_contract(acc[0][nt][j], acc[NMAT - 1][nt][j]);
+                v = swiglu_epilogue(p.epilogue, acc[0][nt][j], acc[NMAT - 1][nt][j]);
               } else {
                 v = acc[0][nt][j];
               }
@@ -581,13 +580,16 @@ int zmoe_gather_qmm_swiglu(const void* x, int x_rows, int ldx, const uint32_t* g
                            const void* gate_biases, const uint32_t* up_w, const void* up_scales,
                            const void* up_biases, int E, int N, int K, int group_size, int qmode,
                            const void* plan, int rows, int rows_hint, void* out, int swiglu_mode, void* stream) {
-  ZMOE_REQUIRE(swiglu_mode == ZMOE_SWIGLU_CPU || swiglu_mode == ZMOE_SWIGLU_PER_OP, ZMOE_ERR_UNSUPPORTED,
+  ZMOE_REQUIRE(swiglu_mode == ZMOE_SWIGLU_CPU || swiglu_mode == ZMOE_SWIGLU_PER_OP ||
+                   (swiglu_mode == ZMOE_SWIGLU_FP32 && qmode == ZMOE_Q_AFFINE4),
+               ZMOE_ERR_UNSUPPORTED,
                "zmoe_gather_qmm_swiglu: swiglu_mode %d", swiglu_mode);
   const uint32_t* w[2] = {gate_w, up_w};
   const void* s[2] = {gate_scales, up_scales};
   const void* b[2] = {gate_biases, up_biases};
   return qmm_launch(2, x, x_rows, ldx, w, s, b, E, N, K, group_size, qmode, plan, rows, rows_hint, out,
-                    swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : 2, 0, stream, "zmoe_gather_qmm_swiglu");
+                    swiglu_mode == ZMOE_SWIGLU_CPU ? 1 : (swiglu_mode == ZMOE_SWIGLU_PER_OP ? 2 : 3), 0, stream,
+                    "zmoe_gather_qmm_swiglu");
 }
 
 int zmoe_gather_qmm(const void* x, int x_rows, int ldx, const uint32_t* w_, const void* scales, const void* biases,

@@ -96,6 +96,17 @@ __device__ __forceinline__ float swiglu_per_op(float g, float u) {
   return round_bf16(g * sig) * u;
 }
 
+// gate and up stay in float (the reference's dense fused GEMV, src/zmlx/kernels/quant.py:103-124)
+__device__ __forceinline__ float swiglu_fp32(float g, float u) {
+  const float y = 1.0f / (1.0f + expf(fabsf(g)));
+  const float sig = (g < 0.0f) ? y : 1.0f - y;
+  return (g * sig) * u;
+}
+
+__device__ __forceinline__ float swiglu_epilogue(int epilogue, float g, float u) {
+  return epilogue == 2 ? swiglu_per_op(g, u) : (epilogue == 3 ? swiglu_fp32(g, u) : swiglu_cpu_contract(g, u));
+}
+
 // Warp wk owns the quads (4 consecutive groups) wk, wk+WK, ...; item gi of its
 // stream is group (wk + (gi/4)*WK)*4 + gi%4.
 template <int WK>

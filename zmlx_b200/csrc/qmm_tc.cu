@@ -413,8 +413,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
             if (tok < it.nt) {
               float v;
               if (NMAT == 2)
-                v = (p.epilogue == 2) ? swiglu_per_op(acc[0][j], acc[NMAT - 1][j])
-                                      : swiglu_cpu_contract(acc[0][j], acc[NMAT - 1][j]);
+                v = swiglu_epilogue(p.epilogue, acc[0][j], acc[NMAT - 1][j]);
               else
                 v = acc[0][j];
               const int dst = pv.row_dst[it.off + it.t0 + tok];

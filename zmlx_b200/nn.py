@@ -78,6 +78,46 @@ class QuantizedMLP(nn.Module):
         return self.down_proj(h, z).squeeze(-2).squeeze(-2)
 
 
+class QuantizedLinear(nn.Module):
+    """One quantised linear layer, ``y = x @ dequant(W).T`` (mlx.nn.QuantizedLinear): weight (N, K/8) uint32,
+    scales and biases (N, K/group_size)."""
+
+    def __init__(self, weight, scales, biases=None, *, group_size: int = 64, bits: int = 4, mode: str = "affine"):
+        super().__init__()
+        self.register_buffer("weight", weight)
+        self.register_buffer("scales", scales)
+        self.register_buffer("biases", biases)
+        self.group_size, self.bits, self.mode = group_size, bits, mode
+
+    def get(self, name, default=None):
+        return getattr(self, name, default)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w = quant.dequantize_affine(self.weight.view(torch.uint32)[None], self.scales[None], self.biases[None],
+                                    self.group_size)[0]
+        return torch.matmul(x.to(torch.float32), w.T).to(x.dtype)
+
+
+class MLP(nn.Module):
+    """Dense SwiGLU MLP with quantised projections (the Llama / Qwen ``mlp`` module)."""
+
+    def __init__(self, gate_proj, up_proj, down_proj):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
+        self.hidden_act = "silu"
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+def mlp_from_params(p: dict, *, group_size: int = 64) -> MLP:
+    """Builds a dense MLP from a one-expert bank dict (``gate_w`` (1, N, K/8) ...), e.g. ``make_layer(...)["shared"]``."""
+    def lin(name):
+        return QuantizedLinear(p[f"{name}_w"][0].contiguous(), p[f"{name}_s"][0].contiguous(),
+                               p[f"{name}_b"][0].contiguous(), group_size=group_size)
+    return MLP(lin("gate"), lin("up"), lin("down"))
+
+
 class Qwen3MoeSparseMoeBlock(nn.Module):
     """Softmax router over raw logits, top-k, optional renormalisation (mlx_lm qwen3_moe)."""
 

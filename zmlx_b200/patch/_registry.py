@@ -37,4 +37,4 @@ def _ensure_loaded() -> None:
     if _LOADED:
         return
     _LOADED = True
-    from .patterns import deepseek_router, moe_mlp  # noqa: F401
+    from .patterns import deepseek_router, moe_mlp, swiglu_mlp  # noqa: F401
