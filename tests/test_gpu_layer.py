@@ -148,3 +148,18 @@ def test_inbox_data_path_gives_the_same_bits(name, T):
         assert torch.equal(a, b), f"step {step}"
         assert torch.equal(plain.indices[:T], boxed.indices[:T]) and torch.equal(plain.weights[:T], boxed.weights[:T])
     boxed.check_status()
+
+
+def test_block_loaded_from_an_mlx_format_checkpoint_gives_the_same_bits(tmp_path):
+    """safetensors under the mlx-community names -> `checkpoint.load_moe_params` -> `MoELayer`: same output as the
+    layer built from the tensors that were written."""
+    from zmlx_b200 import checkpoint
+
+    cfg = synthetic.CONFIGS["c5"].scaled(n_experts=32, d_model=512, d_ff=256, top_k=4, n_group=4, topk_group=2)
+    params = synthetic.make_layer(cfg, device=DEV)
+    checkpoint.save_moe_params(params, str(tmp_path / "model.safetensors"), "model.layers.7.mlp")
+    loaded = checkpoint.load_moe_params(str(tmp_path), checkpoint.moe_block_prefixes(str(tmp_path))[0], device=DEV)
+    x = synthetic.make_tokens(cfg, 3, device="cpu").to(DEV)
+    a = MoELayer(cfg, params, max_tokens=8)(x).clone()
+    b = MoELayer(cfg, loaded, max_tokens=8)(x).clone()
+    assert torch.equal(a, b)
