@@ -55,13 +55,13 @@ def test_greedy_tokens_match_the_cpu_restatement(family):
 NEAR_TIE = 4e-3
 
 
-def _assert_same_tokens(got, want, gaps, what) -> int:
+def _assert_same_tokens(got, want, gaps, what, tie=NEAR_TIE) -> int:
     """Token identity per sequence up to (excluding) the first position where the restatement itself sees a
     near tie between its two best logits.  Returns the number of positions compared."""
     compared = 0
     for b in range(want.shape[0]):
         for t in range(want.shape[1]):
-            if gaps[b, t] < NEAR_TIE:
+            if gaps[b, t] < tie:
                 break
             assert got[b, t] == want[b, t], (f"{what}: sequence {b} position {t}: token {got[b, t]} vs "
                                              f"{want[b, t]} (top-2 gap {gaps[b, t]:.3g})\n{got}\n{want}")
@@ -84,3 +84,33 @@ def test_cache_overflow_is_refused():
     model = StackedDecoder(cfg, make_decoder_params(cfg, device=DEV), max_batch=1, max_seq=8)
     with pytest.raises(ValueError):
         model.forward(torch.zeros((1, 9), dtype=torch.int64, device=DEV))
+
+
+def test_torch_reference_of_the_fidelity_check_matches_the_cpu_restatement():
+    """`DequantMoE` (bfloat16-dequantised banks, torch ops) is the baseline of `zmlx_b200.validate`; before it is
+    trusted at full size it has to reproduce the CPU restatement where that is affordable: the toy model, and a
+    two-layer slice at the full width of the stacked configuration (d 2048, d_ff 768, top-8) with a trimmed bank."""
+    from zmlx_b200.validate import compare, greedy_with_margins, teacher_forced
+
+    wide = DecoderConfig("slice-qwen3", 2, 2048, 32, 4, 128, 1024,
+                         moe=synthetic.CONFIGS["c2"].scaled(n_experts=16))
+    for cfg, n_prompt, n_new in ((_small("qwen3"), 10, 8), (_small("deepseek"), 10, 8), (wide, 6, 5)):
+        cpu = make_decoder_params(cfg, device="cpu")
+        gpu = {k: (_to_device(v, DEV) if not isinstance(v, list) else [_to_device(l, DEV) for l in v])
+               for k, v in cpu.items()}
+        g = torch.Generator().manual_seed(11)
+        prompt = torch.randint(0, cfg.vocab, (2, n_prompt), generator=g)
+        want, gaps = OM.greedy(cfg, _tonp(cpu), prompt.numpy(), n_new)
+        ref = StackedDecoder(cfg, gpu, max_batch=2, max_seq=32, moe_impl="torch")
+        ref_tok, ref_gap = greedy_with_margins(ref, prompt.to(DEV), n_new)
+        # its weights are rounded to bfloat16, which moves a logit by up to ~1e-2: ties are wider for it
+        compared = _assert_same_tokens(ref_tok.cpu().numpy(), want, gaps, f"{cfg.name}: torch reference", tie=2e-2)
+        assert compared >= n_new // 2
+        # and the candidate against that reference, through the same reports the full-size run prints
+        fast = StackedDecoder(cfg, gpu, max_batch=2, max_seq=32)
+        got_tok, _ = greedy_with_margins(fast, prompt.to(DEV), n_new)
+        rep = compare(ref_tok.cpu(), got_tok.cpu(), ref_gap.cpu(), near_tie=2e-2)
+        assert rep["divergences_elsewhere"] == 0, rep
+        tf = teacher_forced(ref, fast, prompt.to(DEV), n_new)
+        assert tf["argmax_agree_on_those"] == tf["steps_with_margin_above_2x_diff"], tf
+        assert tf["max_abs_logit_diff"] < 0.1 * tf["logit_std"] + 5e-2, tf

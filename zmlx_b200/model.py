@@ -138,6 +138,74 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos0: int, *,
     return out
 
 
+class DequantMoE:
+    """GPU-side reference of one MoE block: the packed banks dequantised once to bfloat16, torch ops only (none of
+    this package's kernels).  It plays the role of the unpatched model in the reference's fidelity check
+    (src/zmlx/validate.py:211-225); its arithmetic follows the per-family recipe the kernels implement (router in
+    float32 on bfloat16 logits, gate/up rounded to bfloat16, SwiGLU, down rounded to bfloat16, weighted sum over the
+    slots in float32), with two differences that make it an independent check rather than a copy: the weights are
+    ROUNDED to bfloat16 (the kernels use q * s + b exactly) and the sums run in cuBLAS order."""
+
+    def __init__(self, cfg: MoEConfig, p: dict):
+        from . import quant
+
+        if cfg.mode != "affine":
+            raise ValueError("the dequantised reference takes affine banks")
+        self.cfg = cfg
+        self.router_w = p["router_w"]
+        self.bias = p.get("expert_bias")
+
+        def deq(d, name):
+            return quant.dequantize_affine(d[f"{name}_w"], d[f"{name}_s"], d[f"{name}_b"], cfg.group_size).to(torch.bfloat16)
+
+        self.w = {n: deq(p, n) for n in ("gate", "up", "down")}  # (E, N, K) bfloat16
+        self.shared = {n: deq(p["shared"], n)[0] for n in ("gate", "up", "down")} if p.get("shared") else None
+
+    def _route(self, logits: torch.Tensor):
+        cfg = self.cfg
+        lg = logits.float()
+        if cfg.family == "qwen3":
+            probs = torch.softmax(lg, dim=-1)
+            w, idx = probs.topk(cfg.top_k, dim=-1)
+            if cfg.norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True)
+            return idx, w
+        if cfg.family in ("glm", "deepseek"):
+            aff = torch.sigmoid(lg)
+            sc = aff + self.bias
+            E = sc.shape[-1]
+            if cfg.n_group > 1:
+                g = sc.reshape(-1, cfg.n_group, E // cfg.n_group)
+                gs = g.topk(2, dim=-1).values.sum(-1)
+                keep = torch.zeros_like(gs).scatter_(-1, gs.topk(cfg.topk_group, dim=-1).indices, 1.0)
+                sc = (g * keep[..., None]).reshape(sc.shape)
+            idx = sc.topk(cfg.top_k, dim=-1).indices
+            w = torch.gather(aff, -1, idx)
+            return idx, w / w.sum(-1, keepdim=True) * cfg.routed_scaling_factor
+        w, idx = lg.topk(cfg.top_k, dim=-1)  # generic: top-k of the logits, softmax over the k
+        return idx, torch.softmax(w, dim=-1)
+
+    @staticmethod
+    def _mlp(x, wg, wu, wd):
+        g, u = x @ wg.T, x @ wu.T  # bfloat16 out, float32 accumulation
+        h = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+        return h @ wd.T
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        idx, w = self._route(x @ self.router_w.T)
+        T, K = idx.shape
+        y = torch.zeros((T, K, cfg.d_model), dtype=torch.bfloat16, device=x.device)
+        flat = idx.reshape(-1)
+        for e in torch.unique(flat).tolist():  # one expert at a time over all of its rows
+            rows = (flat == e).nonzero(as_tuple=True)[0]
+            y.view(T * K, -1)[rows] = self._mlp(x[rows // K], self.w["gate"][e], self.w["up"][e], self.w["down"][e])
+        out = (y.float() * w[..., None]).sum(1).to(torch.bfloat16)
+        if self.shared is not None:
+            out = out + self._mlp(x, self.shared["gate"], self.shared["up"], self.shared["down"])
+        return out
+
+
 class StackedDecoder:
     """The model on one GPU (``world == 1``) or with expert-parallel MoE blocks (one process per GPU; every
     rank runs the attention side of its own sequences and the experts are sharded, see zmlx_b200/ep.py)."""
@@ -146,7 +214,7 @@ class StackedDecoder:
     EP_CHUNK = 256
 
     def __init__(self, cfg: DecoderConfig, params: dict, *, max_batch: int, max_seq: int, fused: bool = True,
-                 world: int = 1, rank: int = 0, group=None):
+                 world: int = 1, rank: int = 0, group=None, moe_impl: str = "zmoe"):
         self.cfg = cfg
         self.p = params
         dev = params["embed"].device
@@ -160,7 +228,10 @@ class StackedDecoder:
         self.k_cache = torch.zeros((L, max_batch, hk, max_seq, hd), dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.pos = 0
-        if world > 1:
+        if moe_impl == "torch":  # the dequantised torch reference in place of the kernels (fidelity check)
+            self.chunk = 1 << 30
+            self.moe = [DequantMoE(cfg.moe, lp["moe"]) for lp in params["layers"]]
+        elif world > 1:
             from . import ep
 
             self.chunk = self.EP_CHUNK
