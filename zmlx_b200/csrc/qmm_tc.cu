@@ -305,10 +305,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const TcParams tp
 #pragma unroll 1
     for (int s = 0; s < n_steps; ++s) {
       const int buf = s & 1;
-      // the buffer's previous group must be through the tensor core AND folded by the finishers
+      // the buffer's previous group must be folded by the finishers, who had waited for its MMAs before that
       if (s >= 2 && ok) {
-        const int par = ((s >> 1) - 1) & 1;
-        ok = tc_mbar_wait(bars + buf * 8, par) && tc_mbar_wait(bars + 16 + buf * 8, par);
+        ok = tc_mbar_wait(bars + 16 + buf * 8, ((s >> 1) - 1) & 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
       tc_cp_wait<kTcRing - 2>();  // this thread's copies of step s have landed
