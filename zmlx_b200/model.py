@@ -235,6 +235,7 @@ class StackedDecoder:
         self.k_cache = torch.zeros((L, max_batch, hk, max_seq, hd), dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.pos = 0
+        self.peer, self.peer_tokens = None, 0
         if moe_impl == "torch":  # the dequantised torch reference in place of the kernels (fidelity check)
             self.chunk = 1 << 30
             self.moe = [DequantMoE(cfg.moe, lp["moe"]) for lp in params["layers"]]
@@ -244,6 +245,14 @@ class StackedDecoder:
             self.chunk = self.EP_CHUNK
             self.moe = [ep.EPMoELayer(cfg.moe, lp["moe"], rank=rank, world=world, max_tokens=self.chunk,
                                       group=group) for lp in params["layers"]]
+            # decode steps (max_batch rows per rank) take the one-launch block with the peer-store exchange when
+            # the rows of all ranks fit one launch; prefill chunks keep the collectives
+            if ep.peer_block_supported(cfg.moe, max_batch, world):
+                lo, hi = ep.expert_range(cfg.moe.n_experts, world, rank)
+                self.peer_tokens = max_batch
+                self.peer = [ep.PeerMoELayer(cfg.moe, ep.shard_params(lp["moe"], lo, hi), rank=rank, world=world,
+                                             tokens=max_batch, group=group, launch="pdl")
+                             for lp in params["layers"]]
         else:
             self.chunk = self.MOE_CHUNK
             self.moe = [MoELayer(cfg.moe, lp["moe"], max_tokens=max(max_batch, 64), fused=fused)
@@ -254,6 +263,8 @@ class StackedDecoder:
 
     def _moe(self, i: int, x: torch.Tensor) -> torch.Tensor:
         """x (N, d) bfloat16 -> (N, d); long prefills go through in chunks."""
+        if self.peer is not None and x.shape[0] == self.peer_tokens:
+            return self.peer[i].forward(x if x.is_contiguous() else x.contiguous())
         if x.shape[0] <= self.chunk:
             return self.moe[i].forward(x)
         return torch.cat([self.moe[i].forward(x[s:s + self.chunk]).clone()
