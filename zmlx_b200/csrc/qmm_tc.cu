@@ -464,12 +464,10 @@ int qmm_tc_launch(const QmmParams& q, int nmat, int rows_hint, int max_groups, c
   tp.nmat = nmat;
   const size_t smem = 1024 + (size_t)2 * nmat * kTcATile + 2 * kTcBTile + (size_t)kTcRing * (nmat * kTcRawW + kTcRawX) +
                       (size_t)kTcScSlots * nmat * 2 * kTcScArr;
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return fail(ZMOE_ERR_CUDA, "%s: SM count query failed", who);
   // one CTA per SM, fewer when the work list is shorter: token blocks <= rows / 32 + tasks
   const long long ntiles = (q.N + kTcRows - 1) / kTcRows;
   const long long items = ntiles * ((long long)q.rows / kTcTok + max_groups);
