@@ -22,7 +22,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("name,T", [("c2", 1), ("c2", 2), ("c1", 3)])
+@pytest.mark.parametrize("name,T", [("c2", 1), ("c2", 2), ("c1", 3), ("c5", 1)])
 def test_expert_parallel_block_matches_the_one_gpu_block(name, T):
     world = min(torch.cuda.device_count(), 8 // T)
     world = 1 << (world.bit_length() - 1)  # the expert count must split evenly
