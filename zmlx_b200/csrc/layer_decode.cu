@@ -932,6 +932,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
   LD_STAMP(2);
   // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
   // so this is also where the CTA waits for the router threads of the other CTAs
+  // the sigmoid family with no groups, or with groups of 32 experts, is routed by one warp per row in registers
+  const bool warp_route = p.family == 2 && E <= 256 && (p.n_group == 1 || E == 32 * p.n_group);
   if (wid < T) {
     const bool okr = ld_route_scores(p.logits + (size_t)wid * E * 8, tag, E, p.family, rbias, vals + wid * E,
                                      lgs + wid * E, keys + wid * E, lane);
@@ -939,18 +941,24 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       flags[0] = 1;
       atomicExch(p.sync + 3, 1);
     }
+    if (okr && warp_route) {
+      __syncwarp();
+      ld_sigmoid_route_warp(E, K, rbias, p.n_group, p.topk_group, lgs + wid * E, sel_idx + wid * K, lane);
+    }
   }
   ld_csync();
   LD_STAMP(3);
-  if (p.family == 2) {
-    ld_sigmoid_scores(T, E, rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
+  if (!warp_route) {
+    if (p.family == 2) {
+      ld_sigmoid_scores(T, E, rbias, p.n_group, p.topk_group, vals, lgs, keys, gsc);
+      ld_csync();
+    }
+    if (T * E <= 128)  // uniform over the CTA
+      ld_rank_select(keys, T, E, K, sel_idx);
+    else
+      ld_topk_select(keys, T, E, K, reinterpret_cast<uint32_t*>(red), reinterpret_cast<int*>(red) + T * 64, sel_idx);
     ld_csync();
   }
-  if (T * E <= 128)  // uniform over the CTA
-    ld_rank_select(keys, T, E, K, sel_idx);
-  else
-    ld_topk_select(keys, T, E, K, reinterpret_cast<uint32_t*>(red), reinterpret_cast<int*>(red) + T * 64, sel_idx);
-  ld_csync();
   LD_STAMP(4);
   if (wid < T && flags[0] == 0)
     ld_finish_row(vals + wid * E, lgs + wid * E, K, p.family, p.renorm, p.scale, sel_idx + wid * K, meta->w + wid * K,

@@ -272,6 +272,71 @@ __device__ __forceinline__ void ld_sigmoid_scores(int T, int E, const float* bia
     keys[i] = make_uint2(~(uint32_t)(i % E), ld_order_key(vals[i] + 0.0f));
 }
 
+// Steps 1b and 2 of the sigmoid family by ONE warp per row, in registers: no consumer-wide barrier and no pass
+// through shared memory between the score, the group-limited selection and the top-k.  For E <= 256 with either no
+// groups or groups of exactly 32 experts (E == 32 * n_group: expert lane + 32 j belongs to group j, so a group's
+// members are one register across the warp).  The arithmetic is that of ld_sigmoid_scores + ld_topk_select:
+// maxima, the sum of a group's two largest scores, ranks under (value descending, index ascending) and order keys
+// do not depend on evaluation order, so indices are bit-identical.
+__device__ __forceinline__ void ld_sigmoid_route_warp(int E, int K, const float* bias, int n_group, int topk_group,
+                                                      const float* lgs, int* sel_idx, int lane) {
+  constexpr int NJ = 8;
+  float v[NJ];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int idx = lane + 32 * j;
+    v[j] = idx < E ? sigmoid_stable(lgs[idx]) + bias[idx] : -CUDART_INF_F;
+  }
+  if (n_group > 1) {
+    float gs[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      float t1 = v[j], t2 = -CUDART_INF_F;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {  // merge the lanes' (largest, second largest) pairs
+        const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
+        const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
+        const float hi = fmaxf(t1, o1);
+        t2 = fmaxf(fminf(t1, o1), fmaxf(t2, o2));
+        t1 = hi;
+      }
+      gs[j] = t1 + t2;
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      int rank = 0;
+#pragma unroll
+      for (int h = 0; h < NJ; ++h)
+        if (h < n_group) rank += (gs[h] > gs[j]) || (gs[h] == gs[j] && h < j);
+      if (j < n_group && rank >= topk_group) v[j] = 0.0f;
+    }
+  }
+  uint32_t kv[NJ];
+  unsigned live = 0u;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    kv[j] = ld_order_key(v[j] + 0.0f);
+    if (lane + 32 * j < E) live |= 1u << j;
+  }
+#pragma unroll 1
+  for (int r = 0; r < K; ++r) {
+    uint32_t bk = 0u;
+    int bj = -1;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (((live >> j) & 1u) && (bj < 0 || kv[j] > bk)) {
+        bk = kv[j];
+        bj = j;
+      }
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, bj >= 0 ? bk : 0u);
+    const unsigned none = 0x7fffffffu;
+    const unsigned win = __reduce_min_sync(0xffffffffu, (bj >= 0 && bk == mx) ? (unsigned)(lane + 32 * bj) : none);
+    if (lane == 0) sel_idx[r] = win == none ? 0 : (int)win;
+    if (win != none && (int)(win & 31u) == lane) live &= ~(1u << (win >> 5));
+  }
+  __syncwarp();
+}
+
 // Step 2, small expert counts: rank of every score under (score descending, expert id ascending) by all
 // consumer threads -- one unsigned 64-bit comparison of the sort keys per pair.  The ranks of a row are a
 // permutation, so the experts ranked below K write themselves into slot order.
