@@ -115,7 +115,10 @@ class MoELayer:
         measured against the separate kernels it wins up to about that density (c2 T=16: 79 vs 121 us, c5 T=64:
         2.3 vs 3.5 ms per layer); beyond it the experts are shared by enough rows for the grouped matmuls."""
         cfg = self.cfg
-        if self.ep is not None or T <= self.FUSED_MAX_TOKENS or T * cfg.top_k > 2 * cfg.n_experts:
+        # blocks so wide that the register-fed matmul cannot stage eight token rows (its 96 KB budget) keep the
+        # passes up to four rows per expert: measured c5 T=128, 4.6 ms in 16 passes against 5.7 ms
+        dense = 4 if cfg.d_model * 2 * 8 > 96 * 1024 else 2
+        if self.ep is not None or T <= self.FUSED_MAX_TOKENS or T * cfg.top_k > dense * cfg.n_experts:
             return False
         return all(self.fused_workspace_bytes(n) > 0 for n in {n for _, n in self._chunks(T)})
 
