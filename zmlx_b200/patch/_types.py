@@ -1,44 +1,52 @@
-"""Patch configuration and result records (src/zmlx/patch/_types.py:7-51)."""
+"""Records and the pattern protocol of the patch framework.
+
+The field names, defaults and method names are the interface of src/zmlx/patch/_types.py:7-51, which callers of
+``patch()`` and writers of patterns rely on; everything else here is this package's own.
+"""
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import dataclasses
 from typing import Any, Protocol, runtime_checkable
 
 
-@dataclass(frozen=True)
+@dataclasses.dataclass(frozen=True)
 class PatchConfig:
-    """Configuration for model patching."""
+    """What ``patch()`` hands to every pattern's ``apply``."""
 
     compute_dtype: str = "float32"
-    threadgroup: int | str = 256
+    threadgroup: int | str = 256  # kept for signature compatibility: CUDA launch shapes are chosen by the library
     verbose: bool = False
     moe_fused_swiglu_max_tokens: int | None = None
 
 
-@dataclass
+@dataclasses.dataclass
 class PatchResult:
-    """Summary of what was patched."""
+    """What ``patch()`` did: modules rewritten in total and per pattern, modules a pattern gave up on."""
 
     patched_count: int = 0
-    pattern_counts: dict[str, int] = field(default_factory=dict)
-    skipped: list[str] = field(default_factory=list)
-    benchmarks: dict[str, float] = field(default_factory=dict)
+    pattern_counts: dict[str, int] = dataclasses.field(default_factory=dict)
+    skipped: list[str] = dataclasses.field(default_factory=list)
+    benchmarks: dict[str, float] = dataclasses.field(default_factory=dict)  # pattern -> measured speed-up, if any
 
     def summary(self) -> str:
-        lines = [f"Patched {self.patched_count} modules:"]
-        for name, count in sorted(self.pattern_counts.items()):
-            bench = self.benchmarks.get(name)
-            suffix = f" ({bench:.3f}x)" if bench is not None else ""
-            lines.append(f"  {name}: {count}{suffix}")
+        """Human-readable report, one line per pattern in alphabetical order."""
+
+        def line(pattern: str) -> str:
+            text = f"  {pattern}: {self.pattern_counts[pattern]}"
+            if pattern in self.benchmarks:
+                text += f" ({self.benchmarks[pattern]:.3f}x)"
+            return text
+
+        report = [f"Patched {self.patched_count} modules:", *map(line, sorted(self.pattern_counts))]
         if self.skipped:
-            lines.append(f"  Skipped: {len(self.skipped)}")
-        return "\n".join(lines)
+            report.append(f"  Skipped: {len(self.skipped)}")
+        return "\n".join(report)
 
 
 @runtime_checkable
 class PatchPattern(Protocol):
-    """Protocol for a single patch pattern."""
+    """A pattern names itself, says whether a module is its business, and rewrites it in place."""
 
     @property
     def name(self) -> str: ...
