@@ -384,8 +384,8 @@ def main() -> None:
                            fused=not args.no_fused, launch=args.launch)
                   for i in range(L)]
     stamps = None
-    if args.stamps and not use_ep and not args.via_patch:
-        stamps = layers[L // 2].enable_stamps()
+    if args.stamps and not args.via_patch and (ep_peer or not use_ep):
+        stamps = (layers[L // 2].inner if use_ep else layers[L // 2]).enable_stamps()
     x_host = synthetic.make_tokens(cfg, T, step=rank).pin_memory()
     x_dev = x_host.to(dev)
     out_host = torch.empty((T, cfg.d_model), dtype=torch.bfloat16).pin_memory()
