@@ -120,3 +120,33 @@ def test_nan_scores_rank_below_every_number():
     np.testing.assert_array_equal(S._topk_desc_stable(row, 6), [[3, 0, 5, 2, 1, 4]])
     _, idx = S.topk_gating_softmax(np.full((1, 8), np.nan, dtype=np.float32), 3)
     np.testing.assert_array_equal(idx, [[0, 1, 2]])
+
+
+def test_dense_fused_gemv_restatement_against_a_scalar_loop():
+    """`fused_quantized_swiglu_gemv` (src/zmlx/kernels/quant.py:103-124) as the kernel source spells it: one scalar
+    loop per output element, dequantising code by code, float accumulators, `acc_gate * sigmoid(acc_gate) * acc_up`,
+    one rounding at the store."""
+    from zmlx_b200 import quant
+    import torch
+
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 2, 5, 128
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    gw, gs, gb = quant.quantize_affine(torch.randn(N, K, generator=g) * 0.05)
+    uw, us, ub = quant.quantize_affine(torch.randn(N, K, generator=g) * 0.05)
+    npy = lambda t: t.view(torch.int32).numpy().view(np.uint32) if t.dtype == torch.uint32 else t.float().numpy()
+    got = S.fused_quantized_swiglu_gemv(npy(x), npy(gw), npy(gs), npy(gb), npy(uw), npy(us), npy(ub))
+    want = np.zeros((M, N), dtype=np.float32)
+    for m in range(M):
+        for n in range(N):
+            ag = au = 0.0
+            for i in range(K):
+                qg = (int(npy(gw)[n, i // 8]) >> (4 * (i % 8))) & 15
+                qu = (int(npy(uw)[n, i // 8]) >> (4 * (i % 8))) & 15
+                wg = qg * float(npy(gs)[n, i // 64]) + float(npy(gb)[n, i // 64])
+                wu = qu * float(npy(us)[n, i // 64]) + float(npy(ub)[n, i // 64])
+                ag += wg * float(npy(x)[m, i])
+                au += wu * float(npy(x)[m, i])
+            y = 1.0 / (1.0 + np.exp(abs(ag)))
+            want[m, n] = ag * (y if ag < 0 else 1.0 - y) * au
+    assert np.abs(got - S.bf16(want)).max() <= np.abs(want).max() * 2.0 ** -7  # at most one bfloat16 ulp apart
