@@ -281,10 +281,12 @@ __device__ __forceinline__ uint4 ld_lds128(uint32_t addr) {
 // returns false when a wait ran out (every thread of the CTA sees flags[0] set after the last barrier).
 // SYS: the words may have been written by another GPU (system-scope loads); words written on this GPU are read
 // with device-scope loads, which are measurably cheaper.
+// Pass 1: raw bfloat16 rows into shared memory (row t at xs + t * xs_stride, as stored) and each row's largest
+// magnitude.
 template <bool TAGGED, bool SYS = false>
-__device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float2* xsum, int rs, float* isig,
-                                              int* rowmax, const void* src, int ld, const unsigned char* rowlist,
-                                              int nrows, int K8, uint32_t tag, volatile int* flags, int* status) {
+__device__ __forceinline__ void ld_stage_pass1(unsigned char* xs, int xs_stride, int* rowmax, const void* src, int ld,
+                                               const unsigned char* rowlist, int nrows, int K8, uint32_t tag,
+                                               volatile int* flags, int* status) {
   const int tid = threadIdx.x, lane = tid & 31;
   const int total = nrows * K8;
   if (tid < nrows) rowmax[tid] = 0;
@@ -339,6 +341,13 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
     }
   }
   ld_csync();
+}
+
+// Pass 2: scale by the row's power of two, convert, permute in place; group sums.
+__device__ __forceinline__ void ld_stage_pass2(unsigned char* xs, int xs_stride, float2* xsum, int rs, float* isig,
+                                               const int* rowmax, int nrows, int K8) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int total = nrows * K8;
 #pragma unroll 1
   for (int base = (int)(tid & ~31u); base < total; base += kLdConsumers) {
     const int i = base + lane;
@@ -386,6 +395,14 @@ __device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, 
     if (ok && (lane & 7) == 0) xsum[(blk >> 3) * rs + t] = make_float2(fmaf(16.0f, so, se), 1024.0f * (se + so));
   }
   ld_csync();
+}
+
+template <bool TAGGED, bool SYS = false>
+__device__ __forceinline__ void ld_stage_rows(unsigned char* xs, int xs_stride, float2* xsum, int rs, float* isig,
+                                              int* rowmax, const void* src, int ld, const unsigned char* rowlist,
+                                              int nrows, int K8, uint32_t tag, volatile int* flags, int* status) {
+  ld_stage_pass1<TAGGED, SYS>(xs, xs_stride, rowmax, src, ld, rowlist, nrows, K8, tag, flags, status);
+  ld_stage_pass2(xs, xs_stride, xsum, rs, isig, rowmax, nrows, K8);
 }
 
 // ------------------------------------------------------------------ what a consumer warp carries around
@@ -838,27 +855,14 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
       st_relaxed_sys_v4(o + 4, make_uint4(tag | (xv.z & 0xffffu), tag | (xv.z >> 16), tag | (xv.w & 0xffffu), tag | (xv.w >> 16)));
     }
   }
-  // eight token values from wherever the tokens come from: the caller's rows, or the inbox (re-read until the
-  // words carry this launch's tag; gives zeros and flags the launch when that wait runs out)
-  auto x8 = [&](int t, int v) -> uint4 {
-    if (!EP) return __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * p.ldx) + v);
-    const uint32_t* w32 = xin + (size_t)t * d + v * 8;
-    uint4 a, b;
-    for (int spins = 0;; ++spins) {
-      a = ld_relaxed_sys_v4(w32);
-      b = ld_relaxed_sys_v4(w32 + 4);
-      const uint32_t bad = ((a.x ^ tag) | (a.y ^ tag) | (a.z ^ tag) | (a.w ^ tag) | (b.x ^ tag) | (b.y ^ tag) |
-                            (b.z ^ tag) | (b.w ^ tag)) & 0xffff0000u;
-      if (bad == 0u) break;
-      if (spins >= kLdSpinLimit || ((spins & 1023) == 1023 && flags[0])) {
-        flags[0] = 1;
-        atomicExch(p.sync + 3, 1);
-        return make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-    return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16),
-                      (b.z & 0xffffu) | (b.w << 16));
-  };
+  // ---- token rows -> shared memory as stored (pass 1 of the staging; in the expert-parallel form this is where
+  // the launch waits for the other ranks' rows); the router reads them from there
+  if (EP)
+    ld_stage_pass1<true, true>(xs, qmm_xs_stride(d), rowmax, xin, d, nullptr, T, d >> 3, tag, flags, p.sync + 3);
+  else
+    ld_stage_pass1<false>(xs, qmm_xs_stride(d), rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags, p.sync + 3);
+  const int xs_stride_x = qmm_xs_stride(d);
+  auto x8 = [&](int t, int v) -> uint4 { return *reinterpret_cast<const uint4*>(xs + t * xs_stride_x + v * 16); };
   // ---- router linear: the CTA's rows blockIdx.x, blockIdx.x + grid, ...; warp w sums segment w of a row
   {
     int n_mine = 0;
@@ -922,13 +926,8 @@ __global__ void __launch_bounds__(kLdThreads, 1) layer_decode_kernel(const LdPar
     }
   }
 
-  // ---- token rows -> shared memory (fp16, fragment order, group sums), while the logits travel
-  if (EP)
-    ld_stage_rows<true, true>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, xin, d, nullptr, T, d >> 3, tag, flags,
-                        p.sync + 3);
-  else
-    ld_stage_rows<false>(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, p.x, p.ldx, nullptr, T, d >> 3, 0u, flags,
-                         p.sync + 3);
+  // ---- the staged rows become fp16 in fragment order with their group sums (pass 2), while the logits travel
+  ld_stage_pass2(xs, qmm_xs_stride(d), xsum, T, isig, rowmax, T, d >> 3);
   LD_STAMP(2);
   // ---- routing of every row, repeated by every CTA (one warp per row); the logits arrive as hand-over words,
   // so this is also where the CTA waits for the router threads of the other CTAs
