@@ -554,7 +554,7 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{cfg.name}: d_model={cfg.d_model}, {cfg.n_experts} experts, top-{cfg.top_k}, "
                                    f"d_ff={cfg.d_ff}, {cfg.mode} 4-bit; T={T} decode tokens per step through "
-                                   f"L={L} independent layers",
+                                   f"L={L} chained layers with distinct weights",
                        "tokens": T, "layers": L, "l2_policy": "inputs larger than L2: each step streams "
                        f"{alg_bytes_step / 1e6:.0f} MB of distinct expert weights across {L} layers",
                        "cuda_graph": graph is not None, "one_launch_block": bool(one_launch),
