@@ -31,7 +31,7 @@ def _layer(name):
                                           ("c2", 7, True), ("c2", 8, True), ("c5", 1, True), ("c5", 2, True),
                                           ("c5", 4, True), ("c5", 8, True),
                                           # more rows than one launch takes: consecutive passes of eight
-                                          ("c2", 16, True), ("c2", 29, True), ("c5", 24, True), ("c5", 64, True)])
+                                          ("c2", 16, True), ("c2", 29, True), ("c5", 20, True), ("c5", 24, True), ("c5", 64, True)])
 def test_layer_matches_oracle(name, T, fused):
     cfg, params = _layer(name)
     layer = MoELayer(cfg, params, max_tokens=max(64, T), fused=fused)

@@ -21,15 +21,17 @@
 //             an element, combine them in slot order under the block's rounding contract.
 //
 // The matmul core: a stage holds 32 row segments of up to 512 bytes (16 groups of 64 codes).  A lane reads
-// 8 bytes of rows g and g+8 and turns each packed word into four half2 operands with four lop3 and ONE shift:
-//     (w & 0x000F000F) | 0x64006400 = (1024 + q0, 1024 + q4)        (w & 0x00F000F0) | 0x64006400 =
-//     (1024 + 16 q1, 1024 + 16 q5), and the same on w >> 8 for q2, q6, q3, q7
+// 8 bytes of rows g and g+8 and turns each packed word into four half2 operands with four lop3, ONE shift and two
+// exact fp16 subtractions:
+//     (w & 0x000F000F) | 0x64006400 = (1024 + q0, 1024 + q4), minus 1024 = (q0, q4)
+//     (w & 0x00F000F0) | 0x64006400 = (1024 + 16 q1, 1024 + 16 q5), and the same on w >> 8 for q2, q6, q3, q7
 // (fp16 has ten mantissa bits, so a code at bit 4 still lands inside the mantissa of 1024).  The token rows are
 // staged in shared memory as fp16 in the matching order, the odd positions pre-divided by 16, after a
 // per-row power-of-two scale that puts the row maximum in [2^14, 2^15) (exact for every element within 2^-24
 // of the maximum; bf16 has 8 significant bits, fp16 11).  Products are exact, accumulation is fp32
-// (mma.sync m16n8k16).  The 1024 offsets, the group scale and the group bias are applied per group in fp32:
-//     sum_k x_k (q_k s + b) = s * (D - C) + b * X,   D = the mma sum, C = 1024 sum_even x + 64 sum_odd x, X = sum x.
+// (mma.sync m16n8k16).  The offset left on the odd positions, the group scale and the group bias are applied per
+// group in fp32:
+//     sum_k x_k (q_k s + b) = s * (D - C) + b * X,   D = the mma sum, C = 64 sum_odd x, X = sum x.
 // Spare mma columns carry other groups (column multiplexing, see qmm.cu).  Scales and biases are read straight
 // from L1/L2 into registers one block of groups ahead.
 //
@@ -129,7 +131,7 @@ __host__ __device__ inline LdSmem ld_smem(int T, int K, int E, int d, int f, int
   m.xs = a;  // token rows (gate/up), later the staged h rows (down): fp16, fragment order
   const int xs1 = T * qmm_xs_stride(d), xs2 = hrows * qmm_xs_stride(f);
   a += ld_align16(xs1 > xs2 ? xs1 : xs2);
-  m.xsum = a;  // per (group, row): {sum x, 1024 sum_even x + 64 sum_odd x}
+  m.xsum = a;  // per (group, row): {sum x, 64 sum_odd x}
   const int su1 = ngd * T, su2 = ngf * hrows;
   a += ld_align16((su1 > su2 ? su1 : su2) * 8);
   const int nr = T > hrows ? T : hrows;
@@ -235,12 +237,18 @@ __device__ __forceinline__ void mma_f16_m16n8k16(float (&d)[4], uint32_t a0, uin
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// codes at bits [0,4) and [16,20) -> half2 (1024 + q, 1024 + q'); codes at bits [4,8) and [20,24) -> half2
-// (1024 + 16 q, 1024 + 16 q').  One LOP3 each: (w & mask) | 0x64006400.
+// codes at bits [0,4) and [16,20) -> half2 (q, q'); codes at bits [4,8) and [20,24) -> half2
+// (1024 + 16 q, 1024 + 16 q').  One LOP3 each, (w & mask) | 0x64006400, and one exact subtraction for the former.
 __device__ __forceinline__ uint32_t deq_h_lo(uint32_t w) {
   uint32_t r;
   asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(r) : "r"(w));
-  return r;
+  // (1024 + q) - 1024, exact: these codes reach the tensor core as the plain integers q.  Left as 1024 + q the
+  // offset would ride through the fp32 accumulator as 1024 * sum(x) and cost the group sum several bits (measured:
+  // six times more outputs beyond 1e-2 of the oracle, one of 143,360 beyond 2e-2); the other half of the codes
+  // carries 64 * sum(x) only, like the bfloat16 form of the register-fed kernels.
+  const __half2 k = __floats2half2_rn(1024.0f, 1024.0f);
+  const __half2 v = __hsub2(*reinterpret_cast<__half2*>(&r), k);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 __device__ __forceinline__ uint32_t deq_h_hi(uint32_t w) {
   uint32_t r;
@@ -392,7 +400,7 @@ __device__ __forceinline__ void ld_stage_pass2(unsigned char* xs, int xs_stride,
     so += __shfl_xor_sync(0xffffffffu, so, 2);
     se += __shfl_xor_sync(0xffffffffu, se, 4);
     so += __shfl_xor_sync(0xffffffffu, so, 4);
-    if (ok && (lane & 7) == 0) xsum[(blk >> 3) * rs + t] = make_float2(fmaf(16.0f, so, se), 1024.0f * (se + so));
+    if (ok && (lane & 7) == 0) xsum[(blk >> 3) * rs + t] = make_float2(fmaf(16.0f, so, se), 1024.0f * so);
   }
   ld_csync();
 }
