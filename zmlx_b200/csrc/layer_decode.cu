@@ -271,6 +271,16 @@ __device__ __forceinline__ uint4 ld_lds128(uint32_t addr) {
   return v;
 }
 
+// the same under a predicate: zeros, and no shared-memory access at all, where it is false
+template <int OFF>
+__device__ __forceinline__ uint4 ld_lds128_if(uint32_t addr, bool pred) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("{ .reg .pred p; setp.ne.b32 p, %5, 0; @p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6]; }"
+               : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+               : "r"(addr), "r"((int)pred), "n"(OFF));
+  return v;
+}
+
 #define LD_STAMP_NS(i)                                                                         \
   do {                                                                                         \
     if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[i] = (long long)ld_now_ns(); \
@@ -493,6 +503,7 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
                                         bool tok_ok, int slot_g, const float2* xsum, int rs,
                                         const int (&srow_c)[2]) {
   constexpr int GPB = 8 / TT;  // groups multiplexed into one accumulator
+  (void)zaddr;
   const int ng = K8 >> 3;
   const int rb = K8 << 2;  // bytes of a weight row
   const int nch = (rb + kLdSegBytes - 1) / kLdSegBytes;
@@ -535,11 +546,11 @@ __device__ __forceinline__ void ld_item(LdCtx& c, float (&acc)[2][4], int K8, ui
         const int slot = (GPB > kLdGW) ? slot0 + j : (j % GPB);
         const int pos = ch * kLdGW + j;
         if (slot == qlane) ld_load_sb<TT>(sb, stage + kLdScOff, g, wk * kLdGW + j);
-        // lanes whose column carries another group (or no token) read the zero page
+        // lanes whose column carries another group (or no token) feed zeros and skip the load
         const bool mine = tok_ok && (TT == 8 || slot_g == slot);
-        const uint32_t xa = mine ? xchunk + j * 128 : zaddr;
-        const uint4 xb0 = ld_lds128<0>(xa);
-        const uint4 xb1 = ld_lds128<16>(xa);
+        const uint32_t xa = xchunk + j * 128;
+        const uint4 xb0 = ld_lds128_if<0>(xa, mine);
+        const uint4 xb1 = ld_lds128_if<16>(xa, mine);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           const uint2 wa = (m == 0) ? ld_lds64<j * 32>(wbase) : ld_lds64<16 * kLdSegStride + j * 32>(wbase);
